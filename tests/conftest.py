@@ -1,0 +1,20 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def golden():
+    """Fixtures produced by tests/golden/make_golden.py from the reference's own Python code."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "genbmm_golden.npz")
+    return dict(np.load(path))
