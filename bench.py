@@ -1,0 +1,334 @@
+"""Benchmark of the semiring batched-matmul hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one logbmm forward + backward (loss = c.sum()) over a batch of `--batch` problems of
+size 1024x1024x1024 per GPU (the "1024^3 per batch element" throughput configuration); the
+metric is semiring multiply-accumulates per second, 3*B*M*K*N per step (forward, grad_a and
+grad_b each touch every (m,k,n) triple once).  The same step for maxbmm is timed beside it and
+reported under "also".  Inputs are seeded synthetic tensors, larger than the L2 cache.
+
+With N > 1 (torchrun, one process per GPU) every rank runs the same per-GPU workload on its own
+batch shard; there is no data-path collective.  The time is the maximum over ranks of the
+CUDA-event duration, the value the total over ranks.
+
+`--impl reference` times the reference's own CPU formulation of logbmm — the broadcast-reduce
+PyTorch expression of its README and tests — on the host cores, on a bounded sample of the
+same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SIZE = 1024
+N_SMS = 148
+SFU_PER_SM_CLK = 16     # ex2 results per SM per clock
+FP32_PER_SM_CLK = 128   # FP32 lanes per SM per clock
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p.get("hbm_gbs", 6650.0), "sm_max_mhz": p.get("sm_max_mhz", 1965.0), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, reasons, mx = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                mx = float(s[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, s[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def cpu_logbmm_sample(rows, chunk, repeats=1):
+    """The reference's CPU formulation (broadcast-reduce expression + autograd), timed on `rows` rows
+    of one 1024^3 batch element, in chunks of `chunk` rows.  Returns (MAC/s, seconds, threads)."""
+    import oracle
+    gen = torch.Generator().manual_seed(5)
+    a = torch.randn(1, rows, SIZE, generator=gen)
+    b = torch.randn(1, SIZE, SIZE, generator=gen)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for s in range(0, rows, chunk):
+            oracle.expr_fwd_bwd(oracle.MODE_LOG, a[:, s:s + chunk], b)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    macs = 3.0 * rows * SIZE * SIZE
+    return macs / best, best, torch.get_num_threads()
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    rows, chunk = 512, 64
+    for _ in range(args.warmup):
+        cpu_logbmm_sample(chunk, chunk)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        value, _, threads = cpu_logbmm_sample(rows, chunk)
+    dt = (time.perf_counter() - t0) / args.steps
+    macs = 3.0 * rows * SIZE * SIZE
+    value = macs / dt
+    sample = "per step: %d rows of one 1024x1024x1024 batch element, forward + autograd backward, %d-row chunks" % (
+        rows, chunk)
+    line = {
+        "impl": "reference", "metric": "logbmm fwd+bwd semiring MAC/s", "value": value, "unit": "MAC/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args),
+        "cpu_baseline": {"value": value, "unit": "MAC/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "MAC/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args):
+    return {"workload": "logbmm fwd+bwd, a,b:(%d,%d,%d) fp32 N(0,1) seed 5 per GPU, loss=c.sum()" % (
+        args.batch, SIZE, SIZE), "batch_per_gpu": args.batch, "M": SIZE, "K": SIZE, "N": SIZE,
+        "parallelism": "batch-sharded, no collective", "l2": "working set %d MB per GPU, larger than L2" % (
+            6 * args.batch * 4 * SIZE * SIZE >> 20)}
+
+
+def time_steps(fn, steps, warmup, sync):
+    """CUDA-event time of `steps` calls of fn on the current stream, after `warmup` untimed calls."""
+    for _ in range(warmup):
+        fn()
+    sync()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    sync()
+    return start.elapsed_time(stop) / 1e3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=16, help="1024^3 problems per GPU per step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import genbmm_b200 as gb
+    from genbmm_b200 import _native
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    def sync():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    B = args.batch
+    gen = torch.Generator().manual_seed(5 + rank)
+    a_h = torch.randn(B, SIZE, SIZE, generator=gen).pin_memory()
+    b_h = torch.randn(B, SIZE, SIZE, generator=gen).pin_memory()
+    a = a_h.to(dev).requires_grad_(True)
+    b = b_h.to(dev).requires_grad_(True)
+    ones = torch.ones(B, SIZE, SIZE, device=dev)
+    macs_log = 3.0 * B * SIZE ** 3
+
+    def step_log():
+        c = gb.logbmm(a, b)
+        return torch.autograd.grad(c, (a, b), ones)
+
+    def step_max():
+        c = gb.maxbmm(a, b)
+        return torch.autograd.grad(c, (a, b), ones)
+
+    # ---- headline: device-resident inputs ------------------------------------------------
+    sampler = ClockSampler(local)
+    for _ in range(args.warmup):
+        step_log()
+    sync()
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step_log()
+    stop.record()
+    sync()
+    clocks = sampler.stop()
+    t_log = torch.tensor([start.elapsed_time(stop) / 1e3], device=dev)
+    if dist is not None:
+        dist.all_reduce(t_log, op=dist.ReduceOp.MAX)
+    t_log = float(t_log.item())
+
+    # ---- the same step for maxbmm ---------------------------------------------------------
+    t_max = torch.tensor([time_steps(step_max, args.steps, args.warmup, sync)], device=dev)
+    if dist is not None:
+        dist.all_reduce(t_max, op=dist.ReduceOp.MAX)
+    t_max = float(t_max.item())
+    macs_max = (1.0 * B * SIZE ** 3) + 2.0 * B * SIZE * SIZE
+
+    # ---- end to end: pinned host inputs in, gradients and loss back to the host ----------
+    ga_h = torch.empty(B, SIZE, SIZE).pin_memory()
+    gb_h = torch.empty(B, SIZE, SIZE).pin_memory()
+
+    def step_e2e():
+        ad = a_h.to(dev, non_blocking=True).requires_grad_(True)
+        bd = b_h.to(dev, non_blocking=True).requires_grad_(True)
+        c = gb.logbmm(ad, bd)
+        loss = c.sum()
+        ga, gb_ = torch.autograd.grad(loss, (ad, bd))
+        ga_h.copy_(ga, non_blocking=True)
+        gb_h.copy_(gb_, non_blocking=True)
+        return float(loss.item())
+
+    e2e_steps = max(2, min(args.steps, 5))
+    t_e2e = torch.tensor([time_steps(step_e2e, e2e_steps, 1, sync) / e2e_steps], device=dev)
+    if dist is not None:
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    t_e2e = float(t_e2e.item())
+    h2d = 2 * B * SIZE * SIZE * 4
+    d2h = 2 * B * SIZE * SIZE * 4 + 4
+
+    # ---- per-kernel durations for the roofline (rank 0's GPU) ----------------------------
+    ad, bd = a.detach(), b.detach()
+    out = _native.forward(ad, bd, 0, want_maxes=False)[0]
+
+    def k_fwd():
+        _native.load().gbmm_dense_forward_f32(0, ad.data_ptr(), bd.data_ptr(), None, out.data_ptr(), None, B, SIZE,
+                                               SIZE, SIZE, torch.cuda.current_stream().cuda_stream)
+
+    ga_d, gb_d = torch.empty_like(ad), torch.empty_like(bd)
+
+    def k_bwd_a():
+        _native.load().gbmm_dense_backward_f32(0, ad.data_ptr(), bd.data_ptr(), ones.data_ptr(), out.data_ptr(),
+                                                None, ga_d.data_ptr(), None, B, SIZE, SIZE, SIZE,
+                                                torch.cuda.current_stream().cuda_stream)
+
+    def k_bwd_b():
+        _native.load().gbmm_dense_backward_f32(0, ad.data_ptr(), bd.data_ptr(), ones.data_ptr(), out.data_ptr(),
+                                                None, None, gb_d.data_ptr(), B, SIZE, SIZE, SIZE,
+                                                torch.cuda.current_stream().cuda_stream)
+
+    kernels = {}
+    for name, fn in (("dense_log_fwd_kernel", k_fwd), ("dense_log_bwd_a_kernel", k_bwd_a),
+                     ("dense_log_bwd_b_kernel", k_bwd_b)):
+        kernels[name] = time_steps(fn, args.steps, 3, torch.cuda.synchronize) / args.steps
+    dominant = max(kernels, key=kernels.get)
+    peaks = read_peaks()
+    exps = 1.0 * B * SIZE ** 3  # one exponential per (m,k,n) triple in each of the three kernels
+    sfu_peak = N_SMS * SFU_PER_SM_CLK * peaks["sm_max_mhz"] * 1e6
+    achieved = exps / kernels[dominant]
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            t = json.load(f).get(dominant)
+        if t:
+            traffic = t["dram_bytes_per_launch"] * (B / t["batch"])
+
+    line = {
+        "metric": "logbmm fwd+bwd semiring MAC/s", "value": world * macs_log * args.steps / t_log, "unit": "MAC/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_log / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args), "clocks": clocks,
+        "e2e": {"value": world * macs_log / t_e2e, "unit": "MAC/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e * 1e3},
+        "gpu_launches": 3 * args.steps,
+        "roofline": {
+            "bound": "sfu", "kernel": dominant, "achieved": achieved / 1e9, "peak": sfu_peak / 1e9, "unit": "Gexp/s",
+            "frac": achieved / sfu_peak, "traffic": traffic,
+            "peak_source": "148 SMs x 16 ex2/clk x sm_max_mhz of MEASURED_PEAKS.json (%s)" % peaks["source"],
+            "kernel_ms": {k: v * 1e3 for k, v in kernels.items()},
+            "fwd_bwd_frac_of_sfu_bound": (2.0 * exps / sfu_peak) / (t_log / args.steps),
+        },
+        "also": {"maxbmm_fwd_bwd_mac_per_s": world * macs_max * args.steps / t_max,
+                 "maxbmm_ms_per_step": t_max / args.steps * 1e3,
+                 "maxbmm_frac_of_fp32_bound": (macs_max * 2 / (N_SMS * FP32_PER_SM_CLK * peaks["sm_max_mhz"] * 1e6))
+                 / (t_max / args.steps)},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        value, secs, threads = cpu_logbmm_sample(512, 64)
+        line["cpu_baseline"] = {
+            "value": value, "unit": "MAC/s", "cores": threads, "kind": "port",
+            "sample": "512 rows of one 1024x1024x1024 batch element, forward + autograd backward of the "
+                      "broadcast-reduce expression in 64-row chunks, %.1f s" % secs}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,220 @@
+"""Host-side binding of the C-ABI library, shaped like the reference's `_genbmm` module.
+
+The reference's Python code calls a pybind11 extension `_genbmm` with six functions
+(matmul_cuda.cpp:165-172) that take torch tensors, allocate their outputs and return lists of
+tensors.  This module offers the same functions with the same argument order and the same
+error messages for the same mistakes, implemented by allocating the outputs with torch and
+passing raw device pointers plus the current CUDA stream to libgenbmm_b200.so through ctypes.
+
+There is no CPU path: a tensor that is not on a CUDA device is rejected exactly as the
+reference's CHECK_CUDA does, and a missing library is an ImportError.
+"""
+import ctypes
+import os
+
+import torch
+
+from . import build as _build
+
+_P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+
+_SIGNATURES = {
+    "gbmm_status_string": ([_I], ctypes.c_char_p),
+    "gbmm_abi_version": ([], _I),
+    "gbmm_dense_forward_f32": ([_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
+    "gbmm_dense_backward_f32": ([_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
+    "gbmm_band_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L, _P], _I),
+    "gbmm_band_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P], _I),
+}
+
+_lib = None
+
+
+def library_path():
+    return _build.LIB
+
+
+def load():
+    """dlopen libgenbmm_b200.so (building it first when a toolkit is present and it is stale)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB
+    try:
+        if _build.stale():
+            _build.build()
+    except Exception as exc:  # no nvcc, or a compile error
+        if not os.path.exists(path):
+            raise ImportError(
+                "genbmm_b200: the CUDA library %s is missing and could not be built (%s). "
+                "There is no CPU fallback; run `python -m genbmm_b200.build`." % (path, exc))
+    lib = ctypes.CDLL(path)
+    for name, (args, res) in _SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = library and header out of step
+        fn.argtypes = args
+        fn.restype = res
+    _lib = lib
+    return lib
+
+
+def exported_symbols():
+    return sorted(_SIGNATURES)
+
+
+def _check(status, what):
+    if status != 0:
+        msg = load().gbmm_status_string(status).decode()
+        raise RuntimeError("%s failed: %s (status %d)" % (what, msg, status))
+
+
+def _check_input(x, name, dtype=torch.float32):
+    # same conditions and messages as CHECK_CUDA / CHECK_CONTIGUOUS, matmul_cuda.cpp:65-67
+    if not x.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor" % name)
+    if not x.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % name)
+    if x.dtype != dtype:
+        raise RuntimeError("%s must be %s (got %s)" % (name, dtype, x.dtype))
+
+
+def _stream(dev):
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _ptr(x):
+    return None if x is None else x.data_ptr()
+
+
+MODE_LOG, MODE_MAX, MODE_SAMPLE, MODE_PRODMAX = 0, 1, 2, 3
+BAND_LOG, BAND_MAX, BAND_MUL = 0, 1, 3
+
+
+def forward(a, b, mode, u=None, want_maxes=True):
+    """`_genbmm.forward(a, b, mode)` -> [out, aux]; aux = maxes (mode 0) or int32 indices.
+
+    Mode 2 (sample) takes the uniforms `u`:(B,M,N); when None they are drawn with torch.rand
+    on the device, as the reference does inside its dispatcher (matmul_cuda_kernel.cu:517).
+    """
+    _check_input(a, "a")
+    _check_input(b, "b")
+    if a.dim() != 3 or b.dim() != 3 or a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1]:
+        raise RuntimeError("expected a:(B,M,K) and b:(B,K,N), got %s and %s" % (tuple(a.shape), tuple(b.shape)))
+    if b.device != a.device:
+        raise RuntimeError("a and b must be on the same device")
+    if mode not in (0, 1, 2, 3):
+        raise RuntimeError("unknown mode %r" % (mode,))
+    B, M, K = a.shape
+    N = b.shape[2]
+    with torch.cuda.device(a.device):
+        out = torch.empty((B, M, N), dtype=a.dtype, device=a.device)
+        if mode == MODE_LOG:
+            aux = torch.empty_like(out) if want_maxes else None
+        else:
+            aux = torch.empty((B, M, N), dtype=torch.int32, device=a.device)
+        if mode == MODE_SAMPLE:
+            if u is None:
+                u = torch.rand((B, M, N), dtype=a.dtype, device=a.device)
+            _check_input(u, "u")
+            if tuple(u.shape) != (B, M, N):
+                raise RuntimeError("u must have shape %s" % ((B, M, N),))
+        st = load().gbmm_dense_forward_f32(mode, _ptr(a), _ptr(b), _ptr(u) if mode == MODE_SAMPLE else None,
+                                           _ptr(out), _ptr(aux), B, M, K, N, _stream(a.device))
+    _check(st, "gbmm_dense_forward_f32")
+    return [out, aux]
+
+
+def backward(a, b, grad_output, part, maxes, mode):
+    """`_genbmm.backward(a, b, grad_output, part, maxes, mode)` -> [grad_a, grad_b].
+
+    mode 0: `part` is the forward output; `maxes` is accepted for signature compatibility and
+    not read.  Modes 1-3: `part` holds the saved indices (int32, or the float copy the
+    reference's Python passes, genmul.py:63).  Unlike the reference, mode 0 fills grad_b too.
+    """
+    _check_input(a, "a")
+    _check_input(b, "b")
+    _check_input(grad_output, "grad_output")
+    B, M, K = a.shape
+    N = b.shape[2]
+    if tuple(grad_output.shape) != (B, M, N):
+        raise RuntimeError("grad_output must have shape %s" % ((B, M, N),))
+    with torch.cuda.device(a.device):
+        if mode == MODE_LOG:
+            _check_input(part, "part")
+            pf, aux = part, None
+        else:
+            if part.dtype != torch.int32:
+                part = part.to(torch.int32)
+            _check_input(part, "part", torch.int32)
+            pf, aux = None, part
+        if tuple(part.shape) != (B, M, N):
+            raise RuntimeError("part must have shape %s" % ((B, M, N),))
+        grad_a = torch.empty_like(a)
+        grad_b = torch.empty_like(b)
+        st = load().gbmm_dense_backward_f32(mode, _ptr(a), _ptr(b), _ptr(grad_output), _ptr(pf), _ptr(aux),
+                                            _ptr(grad_a), _ptr(grad_b), B, M, K, N, _stream(a.device))
+    _check(st, "gbmm_dense_backward_f32")
+    return [grad_a, grad_b]
+
+
+def _check_band(a, a_lu, a_lb, b, b_lu, b_lb):
+    _check_input(a, "a")
+    _check_input(b, "b")
+    if a.dim() != 3 or b.dim() != 3 or a.shape[:2] != b.shape[:2]:
+        raise RuntimeError("expected a:(B,n,Wa) and b:(B,n,Wb), got %s and %s" % (tuple(a.shape), tuple(b.shape)))
+    if a.shape[2] != a_lu + a_lb + 1 or b.shape[2] != b_lu + b_lb + 1:
+        raise RuntimeError("band widths do not match lu + ld + 1")
+    if b.device != a.device:
+        raise RuntimeError("a and b must be on the same device")
+
+
+def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode):
+    """`_genbmm.forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode)` -> [out, indices, maxes].
+
+    Only the outputs the mode defines are produced (the reference allocates and zero-fills all
+    three every call, banded_cuda_kernel.cu:373-387); the others are returned as None.
+    """
+    _check_band(a, a_lu, a_lb, b, b_lu, b_lb)
+    if mode not in (BAND_LOG, BAND_MAX, BAND_MUL):
+        raise RuntimeError("unknown banded mode %r" % (mode,))
+    B, n, Wa = a.shape
+    Wo = Wa + b.shape[2] - 1
+    with torch.cuda.device(a.device):
+        out = torch.empty((B, n, Wo), dtype=a.dtype, device=a.device)
+        idx = torch.empty((B, n, Wo), dtype=torch.int32, device=a.device) if mode == BAND_MAX else None
+        maxes = torch.empty_like(out) if mode == BAND_LOG else None
+        st = load().gbmm_band_forward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), _ptr(idx),
+                                          _ptr(maxes), B, n, _stream(a.device))
+    _check(st, "gbmm_band_forward_f32")
+    return [out, idx, maxes]
+
+
+def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=False):
+    """`_genbmm.backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode)` -> [grad_a].
+
+    With both=True returns [grad_a, grad_b], grad_b computed directly by a second kernel rather
+    than by the reference's swap-and-transpose route (sparse.py:436-446).  `part` is the forward
+    output (mode 0), the int32 or float indices in a's band coordinate (mode 1), ignored (mode 3).
+    """
+    _check_band(a, a_lu, a_lb, b, b_lu, b_lb)
+    _check_input(grad_output, "grad_output")
+    B, n, Wa = a.shape
+    Wo = Wa + b.shape[2] - 1
+    if tuple(grad_output.shape) != (B, n, Wo):
+        raise RuntimeError("grad_output must have shape %s" % ((B, n, Wo),))
+    with torch.cuda.device(a.device):
+        if mode == BAND_MAX:
+            if part.dtype != torch.int32:
+                part = part.to(torch.int32)
+            _check_input(part, "part", torch.int32)
+        elif mode == BAND_LOG:
+            _check_input(part, "part")
+        else:
+            part = None
+        if part is not None and tuple(part.shape) != (B, n, Wo):
+            raise RuntimeError("part must have shape %s" % ((B, n, Wo),))
+        grad_a = torch.empty_like(a)
+        grad_b = torch.empty_like(b) if both else None
+        st = load().gbmm_band_backward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(grad_output),
+                                           _ptr(part), _ptr(grad_a), _ptr(grad_b), B, n, _stream(a.device))
+    _check(st, "gbmm_band_backward_f32")
+    return [grad_a, grad_b] if both else [grad_a]

@@ -1,0 +1,400 @@
+// Banded semiring products in the reference's diagonal storage:
+//   data:(B,n,W), W = lu+ld+1, data[b,i,j] = Dense[b, i+j-lu, i].
+//
+// Index algebra (banded_cuda_kernel.cu:28-36,48-49,123,132-133), with Wa, Wb the operand
+// widths, r_lu = a_lu+b_ld, Wo = Wa+Wb-1: a triple (i, ja, jo) couples
+//   a[i][ja],  b[o][k2],  out[i][jo]   with  o = i+jo-r_lu,  k2 = ja-jo+Wb-1,
+// and exists when 0 <= o < n, 0 <= k2 < Wb and the shared dense index p = i+ja-a_lu lies in
+// [0,n).  Forward reduces over ja, grad_a over jo, grad_b (cell (o,k2)) over i.
+//
+// Replaces banded_cuda_forward_kernel_mul / banded_cuda_backward_kernel_mul
+// (banded_cuda_kernel.cu:13-152), which map lanes to rows (every load strided by W) and get
+// grad_b from a second launch on band-transposed copies.  Here lanes run along the contiguous
+// band axis, a CTA stages the rows it needs in shared memory (the b rows with an even pitch,
+// so that the skewed access b[o(j)][k2(j)] of consecutive lanes hits distinct banks), only
+// the outputs a mode needs are written, and grad_b is computed directly.
+// When the rows of a CTA do not fit in shared memory the same code reads global memory.
+#include "common.cuh"
+
+namespace gbmm {
+namespace {
+
+constexpr int NT = 256;
+constexpr int kSmemBudget = 200 * 1024;
+
+// A window of consecutive matrix rows, either staged in shared memory or the tensor itself.
+template <typename T>
+struct Rows {
+  const T* p;
+  int pitch;
+  int64_t row0;
+  __device__ __forceinline__ T at(int64_t row, int col) const { return p[(row - row0) * pitch + col]; }
+};
+
+// Cooperative copy of rows [row0, row0+cnt) of a (n, W) matrix into shared memory with the
+// given pitch; rows outside [0,n) are zero-filled.  One warp per row, lanes along the row.
+template <typename T>
+__device__ __forceinline__ void stage_rows(T* dst, int pitch, const T* src, int W, int64_t row0, int cnt,
+                                           int64_t n) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  for (int r = warp; r < cnt; r += NT / 32) {
+    const int64_t row = row0 + r;
+    const bool ok = row >= 0 && row < n;
+    for (int c = lane; c < W; c += 32) dst[r * pitch + c] = ok ? __ldg(src + row * W + c) : T(0);
+  }
+}
+
+struct BandDims {
+  int64_t n;
+  int a_lu, a_ld, b_lu, b_ld;
+  __host__ __device__ int Wa() const { return a_lu + a_ld + 1; }
+  __host__ __device__ int Wb() const { return b_lu + b_ld + 1; }
+  __host__ __device__ int r_lu() const { return a_lu + b_ld; }
+  __host__ __device__ int Wo() const { return Wa() + Wb() - 1; }
+};
+
+// even pitch for b rows: consecutive lanes step by pitch-1 floats, which must be odd
+__host__ __device__ inline int b_pitch(int Wb) { return (Wb & 1) ? Wb + 1 : Wb; }
+
+// ------------------------------------------------------------------ forward
+template <int MODE>
+__global__ void __launch_bounds__(NT) band_fwd_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                      float* __restrict__ out, int* __restrict__ idx,
+                                                      float* __restrict__ maxes, BandDims d, int TI,
+                                                      int tiles_i, int staged) {
+  extern __shared__ float smem[];
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
+  const int64_t n = d.n;
+  const int64_t bt = blockIdx.x / tiles_i;
+  const int64_t i0 = (int64_t)(blockIdx.x % tiles_i) * TI;
+  const float* ab = a + bt * n * Wa;
+  const float* bb = b + bt * n * Wb;
+  Rows<float> va{ab, Wa, 0}, vb{bb, Wb, 0};
+  if (staged) {
+    float* sa = smem;
+    float* sb = smem + TI * Wa;
+    const int ldb = b_pitch(Wb);
+    stage_rows(sa, Wa, ab, Wa, i0, TI, n);
+    stage_rows(sb, ldb, bb, Wb, i0 - r_lu, TI + Wo - 1, n);
+    __syncthreads();
+    va = Rows<float>{sa, Wa, i0};
+    vb = Rows<float>{sb, ldb, i0 - r_lu};
+  }
+  const int total = TI * Wo;
+  for (int e = threadIdx.x; e < total; e += NT) {
+    const int il = e / Wo, jo = e - il * Wo;
+    const int64_t i = i0 + il;
+    if (i >= n) break;
+    const int64_t oi = (bt * n + i) * Wo + jo;
+    const int64_t o = i + jo - r_lu;
+    if (o < 0 || o >= n) {  // outside the matrix: the reference leaves its zero fill
+      out[oi] = 0.f;
+      if (MODE == GBMM_BAND_MAX && idx) idx[oi] = 0;
+      if (MODE == GBMM_BAND_LOG && maxes) maxes[oi] = 0.f;
+      continue;
+    }
+    // valid ja: k2 = ja-jo+Wb-1 in [0,Wb) and p = i+ja-a_lu in [0,n)
+    int lo = max(0, jo - (Wb - 1));
+    int hi = min(Wa - 1, jo);
+    lo = (int)max((int64_t)lo, (int64_t)d.a_lu - i);
+    hi = (int)min((int64_t)hi, n - 1 - i + d.a_lu);
+    const int kofs = Wb - 1 - jo;
+    if (MODE == GBMM_BAND_MUL) {
+      float val = 0.f;
+      for (int ja = lo; ja <= hi; ++ja) val = fmaf(va.at(i, ja), vb.at(o, ja + kofs), val);
+      out[oi] = val;
+    } else if (MODE == GBMM_BAND_MAX) {
+      float m = kFloor;
+      int ind = -1;
+      for (int ja = lo; ja <= hi; ++ja) {
+        const float v = __fadd_rn(va.at(i, ja), vb.at(o, ja + kofs));
+        if (v > m) {
+          m = v;
+          ind = ja;
+        }
+      }
+      out[oi] = m;
+      if (idx) idx[oi] = ind;
+    } else {
+      float m = kFloor;
+      for (int ja = lo; ja <= hi; ++ja) m = fmaxf(m, va.at(i, ja) + vb.at(o, ja + kofs));
+      float s = 0.f;
+      for (int ja = lo; ja <= hi; ++ja) s += exp_sfu((va.at(i, ja) + vb.at(o, ja + kofs)) - m);
+      out[oi] = logf(s) + m;
+      if (maxes) maxes[oi] = m;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ grad_a
+template <int MODE>
+__global__ void __launch_bounds__(NT) band_bwd_a_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                        const float* __restrict__ g, const void* __restrict__ part,
+                                                        float* __restrict__ grad_a, BandDims d, int TI,
+                                                        int tiles_i, int staged) {
+  extern __shared__ float smem[];
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
+  const int64_t n = d.n;
+  const int64_t bt = blockIdx.x / tiles_i;
+  const int64_t i0 = (int64_t)(blockIdx.x % tiles_i) * TI;
+  const float* ab = a + bt * n * Wa;
+  const float* bb = b + bt * n * Wb;
+  const float* gb = g + bt * n * Wo;
+  const float* pf = (MODE == GBMM_BAND_LOG) ? static_cast<const float*>(part) + bt * n * Wo : nullptr;
+  const int* pi = (MODE == GBMM_BAND_MAX) ? static_cast<const int*>(part) + bt * n * Wo : nullptr;
+  Rows<float> vb{bb, Wb, 0}, vg{gb, Wo, 0}, vpf{pf, Wo, 0};
+  Rows<int> vpi{pi, Wo, 0};
+  if (staged) {
+    const int ldb = b_pitch(Wb);
+    float* sb = smem;
+    float* sg = sb + (TI + Wo - 1) * ldb;
+    float* sp = sg + TI * Wo;
+    stage_rows(sb, ldb, bb, Wb, i0 - r_lu, TI + Wo - 1, n);
+    stage_rows(sg, Wo, gb, Wo, i0, TI, n);
+    if (MODE == GBMM_BAND_LOG) stage_rows(sp, Wo, pf, Wo, i0, TI, n);
+    if (MODE == GBMM_BAND_MAX) stage_rows(reinterpret_cast<int*>(sp), Wo, pi, Wo, i0, TI, n);
+    __syncthreads();
+    vb = Rows<float>{sb, ldb, i0 - r_lu};
+    vg = Rows<float>{sg, Wo, i0};
+    vpf = Rows<float>{sp, Wo, i0};
+    vpi = Rows<int>{reinterpret_cast<int*>(sp), Wo, i0};
+  }
+  const int total = TI * Wa;
+  for (int e = threadIdx.x; e < total; e += NT) {
+    const int il = e / Wa, ja = e - il * Wa;
+    const int64_t i = i0 + il;
+    if (i >= n) break;
+    const int64_t ai = (bt * n + i) * Wa + ja;
+    const int64_t p = i + ja - d.a_lu;
+    float val = 0.f;
+    if (p >= 0 && p < n) {
+      // valid jo: k2 = ja-jo+Wb-1 in [0,Wb) and o = i+jo-r_lu in [0,n)
+      int lo = ja, hi = min(Wo - 1, ja + Wb - 1);
+      lo = (int)max((int64_t)lo, (int64_t)r_lu - i);
+      hi = (int)min((int64_t)hi, n - 1 - i + r_lu);
+      const float av = (MODE == GBMM_BAND_LOG) ? __ldg(ab + (i * Wa + ja)) : 0.f;
+      for (int jo = lo; jo <= hi; ++jo) {
+        const int64_t o = i + jo - r_lu;
+        const int k2 = ja - jo + Wb - 1;
+        if (MODE == GBMM_BAND_MUL) {
+          val = fmaf(vb.at(o, k2), vg.at(i, jo), val);
+        } else if (MODE == GBMM_BAND_MAX) {
+          if (vpi.at(i, jo) == ja) val = __fadd_rn(val, vg.at(i, jo));
+        } else {
+          val = fmaf(exp_sfu((av + vb.at(o, k2)) - vpf.at(i, jo)), vg.at(i, jo), val);
+        }
+      }
+    }
+    grad_a[ai] = val;
+  }
+}
+
+// ------------------------------------------------------------------ grad_b
+// CTA owns TO consecutive rows o of b; the contributing rows i = o-jo+r_lu span
+// [o0-(Wo-1-r_lu), o0+TO-1+r_lu] and are walked in ascending chunks of TI rows.
+template <int MODE>
+__global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                        const float* __restrict__ g, const void* __restrict__ part,
+                                                        float* __restrict__ grad_b, BandDims d, int TO, int TI,
+                                                        int tiles_o, int staged) {
+  extern __shared__ float smem[];
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
+  const int r_ld = Wo - 1 - r_lu;
+  const int64_t n = d.n;
+  const int64_t bt = blockIdx.x / tiles_o;
+  const int64_t o0 = (int64_t)(blockIdx.x % tiles_o) * TO;
+  const float* ab = a + bt * n * Wa;
+  const float* bb = b + bt * n * Wb;
+  const float* gb = g + bt * n * Wo;
+  const float* pf = (MODE == GBMM_BAND_LOG) ? static_cast<const float*>(part) + bt * n * Wo : nullptr;
+  const int* pi = (MODE == GBMM_BAND_MAX) ? static_cast<const int*>(part) + bt * n * Wo : nullptr;
+  float* ob = grad_b + bt * n * Wb;
+
+  const int64_t i_begin = max((int64_t)0, o0 - r_ld);
+  const int64_t i_end = min(n, o0 + TO + r_lu);  // exclusive
+  const int total = TO * Wb;
+
+  float* acc = smem;             // [TO*Wb], staged mode only
+  float* sa = acc + TO * Wb;     // [TI*Wa]
+  float* sg = sa + TI * Wa;      // [TI*Wo]
+  float* sp = sg + TI * Wo;      // [TI*Wo]
+  if (staged) {
+    for (int e = threadIdx.x; e < total; e += NT) acc[e] = 0.f;
+  }
+  const int64_t step = staged ? TI : (i_end - i_begin > 0 ? i_end - i_begin : 1);
+  for (int64_t c0 = i_begin; c0 < i_end; c0 += step) {
+    const int64_t c1 = min(i_end, c0 + step);
+    Rows<float> va{ab, Wa, 0}, vg{gb, Wo, 0}, vpf{pf, Wo, 0};
+    Rows<int> vpi{pi, Wo, 0};
+    if (staged) {
+      __syncthreads();  // previous chunk fully consumed
+      stage_rows(sa, Wa, ab, Wa, c0, (int)(c1 - c0), n);
+      stage_rows(sg, Wo, gb, Wo, c0, (int)(c1 - c0), n);
+      if (MODE == GBMM_BAND_LOG) stage_rows(sp, Wo, pf, Wo, c0, (int)(c1 - c0), n);
+      if (MODE == GBMM_BAND_MAX) stage_rows(reinterpret_cast<int*>(sp), Wo, pi, Wo, c0, (int)(c1 - c0), n);
+      __syncthreads();
+      va = Rows<float>{sa, Wa, c0};
+      vg = Rows<float>{sg, Wo, c0};
+      vpf = Rows<float>{sp, Wo, c0};
+      vpi = Rows<int>{reinterpret_cast<int*>(sp), Wo, c0};
+    }
+    for (int e = threadIdx.x; e < total; e += NT) {
+      const int ol = e / Wb, k2 = e - ol * Wb;
+      const int64_t o = o0 + ol;
+      if (o >= n) break;
+      const int64_t p = o + k2 - d.b_lu;
+      float val = staged ? acc[e] : 0.f;
+      if (p >= 0 && p < n) {
+        // i = o - jo + r_lu with jo in [0,Wo) and ja = k2+jo-(Wb-1) in [0,Wa)
+        //   => jo in [Wb-1-k2, Wb-1-k2+Wa-1]  =>  i in [o+r_lu-(Wb-1-k2+Wa-1), o+r_lu-(Wb-1-k2)]
+        int64_t lo = o + r_lu - (Wb - 1 - k2 + Wa - 1);
+        int64_t hi = o + r_lu - (Wb - 1 - k2);
+        lo = max(lo, c0);
+        hi = min(hi, c1 - 1);
+        const float bv = (MODE == GBMM_BAND_LOG) ? __ldg(bb + (o * Wb + k2)) : 0.f;
+        for (int64_t i = lo; i <= hi; ++i) {
+          const int jo = (int)(o - i + r_lu);
+          const int ja = k2 + jo - (Wb - 1);
+          if (MODE == GBMM_BAND_MUL) {
+            val = fmaf(va.at(i, ja), vg.at(i, jo), val);
+          } else if (MODE == GBMM_BAND_MAX) {
+            if (vpi.at(i, jo) == ja) val = __fadd_rn(val, vg.at(i, jo));
+          } else {
+            val = fmaf(exp_sfu((va.at(i, ja) + bv) - vpf.at(i, jo)), vg.at(i, jo), val);
+          }
+        }
+      }
+      if (staged)
+        acc[e] = val;
+      else
+        ob[o * Wb + k2] = val;
+    }
+  }
+  if (staged) {
+    // each thread re-reads only the slots it wrote itself
+    for (int e = threadIdx.x; e < total; e += NT) {
+      const int ol = e / Wb;
+      if (o0 + ol >= n) break;
+      ob[(o0 + ol) * Wb + (e - ol * Wb)] = acc[e];
+    }
+  } else if (i_begin >= i_end) {
+    for (int e = threadIdx.x; e < total; e += NT) {
+      const int ol = e / Wb;
+      if (o0 + ol >= n) break;
+      ob[(o0 + ol) * Wb + (e - ol * Wb)] = 0.f;
+    }
+  }
+}
+
+int pick_rows(size_t fixed_floats, size_t per_row_floats) {
+  for (int t = 32; t >= 1; t >>= 1)
+    if ((fixed_floats + per_row_floats * t) * sizeof(float) <= (size_t)kSmemBudget) return t;
+  return 0;
+}
+
+template <typename KernelT>
+bool allow_smem(KernelT kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess;
+}
+
+int check_band(int mode, int64_t B, int64_t n, int a_lu, int a_ld, int b_lu, int b_ld) {
+  if (mode != GBMM_BAND_LOG && mode != GBMM_BAND_MAX && mode != GBMM_BAND_MUL) return GBMM_ERR_INVALID_ARG;
+  if (B < 0 || n < 0 || a_lu < 0 || a_ld < 0 || b_lu < 0 || b_ld < 0) return GBMM_ERR_INVALID_ARG;
+  const int64_t Wo = (int64_t)a_lu + a_ld + b_lu + b_ld + 1;
+  if (Wo >= (1 << 24) || n >= (1LL << 31) - 64) return GBMM_ERR_UNSUPPORTED;
+  return GBMM_OK;
+}
+
+}  // namespace
+}  // namespace gbmm
+
+using namespace gbmm;
+
+extern "C" int gbmm_band_forward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu,
+                                     int b_ld, float* out, int32_t* idx, float* maxes, int64_t B, int64_t n,
+                                     void* stream) {
+  const int st0 = check_band(mode, B, n, a_lu, a_ld, b_lu, b_ld);
+  if (st0 != GBMM_OK) return st0;
+  if (B == 0 || n == 0) return GBMM_OK;
+  if (!a || !b || !out) return GBMM_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const BandDims d{n, a_lu, a_ld, b_lu, b_ld};
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo();
+  const size_t ldb = b_pitch(Wb);
+  int TI = pick_rows((size_t)(Wo - 1) * ldb, (size_t)Wa + ldb);
+  const int staged = TI > 0;
+  if (!staged) TI = 8;
+  const size_t smem = staged ? ((size_t)TI * Wa + (size_t)(TI + Wo - 1) * ldb) * sizeof(float) : 0;
+  const int64_t tiles = ceil_div(n, TI), blocks = B * tiles;
+  if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+#define GBMM_LAUNCH_BAND_FWD(MODE)                                                                      \
+  do {                                                                                                  \
+    if (smem > 48 * 1024 && !allow_smem(band_fwd_kernel<MODE>, smem)) return GBMM_ERR_LAUNCH;           \
+    band_fwd_kernel<MODE><<<(unsigned)blocks, NT, smem, st>>>(a, b, out, idx, maxes, d, TI, (int)tiles, \
+                                                             staged);                                  \
+  } while (0)
+  if (mode == GBMM_BAND_MUL) GBMM_LAUNCH_BAND_FWD(GBMM_BAND_MUL);
+  else if (mode == GBMM_BAND_MAX) GBMM_LAUNCH_BAND_FWD(GBMM_BAND_MAX);
+  else GBMM_LAUNCH_BAND_FWD(GBMM_BAND_LOG);
+#undef GBMM_LAUNCH_BAND_FWD
+  return launch_status();
+}
+
+extern "C" int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu,
+                                      int b_ld, const float* grad_out, const void* part, float* grad_a,
+                                      float* grad_b, int64_t B, int64_t n, void* stream) {
+  const int st0 = check_band(mode, B, n, a_lu, a_ld, b_lu, b_ld);
+  if (st0 != GBMM_OK) return st0;
+  if (B == 0 || n == 0) return GBMM_OK;
+  if (!a || !b || !grad_out) return GBMM_ERR_INVALID_ARG;
+  if (mode != GBMM_BAND_MUL && !part) return GBMM_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const BandDims d{n, a_lu, a_ld, b_lu, b_ld};
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo();
+  const size_t ldb = b_pitch(Wb);
+  if (grad_a) {
+    int TI = pick_rows((size_t)(Wo - 1) * ldb, ldb + 2 * (size_t)Wo);
+    const int staged = TI > 0;
+    if (!staged) TI = 8;
+    const size_t smem = staged ? ((size_t)(TI + Wo - 1) * ldb + 2 * (size_t)TI * Wo) * sizeof(float) : 0;
+    const int64_t tiles = ceil_div(n, TI), blocks = B * tiles;
+    if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+#define GBMM_LAUNCH_BAND_BWD_A(MODE)                                                                      \
+  do {                                                                                                    \
+    if (smem > 48 * 1024 && !allow_smem(band_bwd_a_kernel<MODE>, smem)) return GBMM_ERR_LAUNCH;           \
+    band_bwd_a_kernel<MODE><<<(unsigned)blocks, NT, smem, st>>>(a, b, grad_out, part, grad_a, d, TI,      \
+                                                               (int)tiles, staged);                      \
+  } while (0)
+    if (mode == GBMM_BAND_MUL) GBMM_LAUNCH_BAND_BWD_A(GBMM_BAND_MUL);
+    else if (mode == GBMM_BAND_MAX) GBMM_LAUNCH_BAND_BWD_A(GBMM_BAND_MAX);
+    else GBMM_LAUNCH_BAND_BWD_A(GBMM_BAND_LOG);
+#undef GBMM_LAUNCH_BAND_BWD_A
+    if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+  }
+  if (grad_b) {
+    int TO = 32, TI = 0;
+    for (; TO >= 1 && TI == 0; TO >>= 1) {
+      TI = pick_rows((size_t)TO * Wb, (size_t)Wa + 2 * (size_t)Wo);
+      if (TI) break;
+    }
+    const int staged = TI > 0;
+    if (!staged) {
+      TO = 8;
+      TI = 1;
+    }
+    const size_t smem = staged ? ((size_t)TO * Wb + (size_t)TI * (Wa + 2 * (size_t)Wo)) * sizeof(float) : 0;
+    const int64_t tiles = ceil_div(n, TO), blocks = B * tiles;
+    if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+#define GBMM_LAUNCH_BAND_BWD_B(MODE)                                                                      \
+  do {                                                                                                    \
+    if (smem > 48 * 1024 && !allow_smem(band_bwd_b_kernel<MODE>, smem)) return GBMM_ERR_LAUNCH;           \
+    band_bwd_b_kernel<MODE><<<(unsigned)blocks, NT, smem, st>>>(a, b, grad_out, part, grad_b, d, TO, TI,  \
+                                                               (int)tiles, staged);                      \
+  } while (0)
+    if (mode == GBMM_BAND_MUL) GBMM_LAUNCH_BAND_BWD_B(GBMM_BAND_MUL);
+    else if (mode == GBMM_BAND_MAX) GBMM_LAUNCH_BAND_BWD_B(GBMM_BAND_MAX);
+    else GBMM_LAUNCH_BAND_BWD_B(GBMM_BAND_LOG);
+#undef GBMM_LAUNCH_BAND_BWD_B
+  }
+  return launch_status();
+}

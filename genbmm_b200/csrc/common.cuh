@@ -1,0 +1,35 @@
+// Shared device helpers for the genbmm_b200 kernels (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/genbmm_b200.h"
+
+namespace gbmm {
+
+// The reference starts every running maximum at -1e9 rather than -inf
+// (matmul_cuda_kernel.cu:31,62,93,139; banded_cuda_kernel.cu:44,79).
+constexpr float kFloor = -1e9f;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// exp(x) on the SFU: one FMUL + one MUFU.EX2.
+__device__ __forceinline__ float exp_sfu(float x) { return ex2_approx(x * kLog2e); }
+
+// 3-input maximum (one FMNMX3 on sm_100).  NaN operands are ignored, as with the
+// reference's `if (v > m)` which never selects a NaN.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+__host__ __device__ __forceinline__ int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? GBMM_OK : GBMM_ERR_LAUNCH; }
+
+}  // namespace gbmm

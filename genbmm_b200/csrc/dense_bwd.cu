@@ -1,0 +1,353 @@
+// Dense semiring backward kernels.
+//
+// log semiring (replaces matmul_cuda_kernel.cu:159-217 and the transposed copies of
+// genmul.py:38-41): the softmax weight w = exp(a[m,k] + b[k,n] - c[m,n]) is recomputed tile
+// by tile from the saved forward output; nothing of size B*M*K*N is stored.
+//   grad_a[m,k] = sum_n w * g[m,n]   (CTA owns a 128x64 tile of grad_a, walks n)
+//   grad_b[k,n] = sum_m w * g[m,n]   (CTA owns a 128x64 tile of grad_b, walks m)
+// Both read a, b, c, g in their natural layouts; no transposed copy is made.
+//
+// max / sample / prod-max (replaces matmul_cuda_kernel.cu:336-456, which scan all K*N
+// candidates per output): the saved int32 index routes each g[m,n] to one cell,
+//   grad_a[m,idx] += g[m,n] (* b[idx,n]),   grad_b[idx,n] += g[m,n] (* a[m,idx]),
+// accumulated in shared-memory rows/columns in ascending n (grad_a) and ascending m
+// (grad_b), the order of the reference's loops.  An index outside [0,K) routes nowhere.
+#include "tile.cuh"
+
+namespace gbmm {
+namespace {
+
+constexpr int BR = 128, BC = 64, BK = 16, NT = 256;
+constexpr int LDR = BR + 4, LDC = BC + 4;
+
+__device__ __forceinline__ float pinf_f() { return __int_as_float(0x7f800000); }
+
+struct TileCoord {
+  int bt, r0, c0;
+  __device__ __forceinline__ TileCoord(int tiles_r, int tiles_c) {
+    const int64_t id = blockIdx.x;
+    c0 = (int)(id % tiles_c) * BC;
+    r0 = (int)((id / tiles_c) % tiles_r) * BR;
+    bt = (int)(id / ((int64_t)tiles_c * tiles_r));
+  }
+};
+
+__device__ __forceinline__ void store_tile(float* __restrict__ dst, int64_t pitch, int rows, int cols,
+                                           const TileCoord& tc, const Micro8x4& mt, const float (&acc)[8][4]) {
+  const bool vec = aligned16(dst) && (pitch % 4 == 0);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = tc.r0 + mt.row(i);
+    if (r >= rows) continue;
+    const int cb = tc.c0 + mt.col(0);
+    if (vec && cb + 3 < cols) {
+      *reinterpret_cast<float4*>(dst + (int64_t)r * pitch + cb) =
+          make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (cb + j < cols) dst[(int64_t)r * pitch + cb + j] = acc[i][j];
+    }
+  }
+}
+
+// grad_a tile: rows m, columns k, reduction over n.
+__global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __restrict__ a,
+                                                             const float* __restrict__ b,
+                                                             const float* __restrict__ c,
+                                                             const float* __restrict__ g,
+                                                             float* __restrict__ grad_a, int M, int K, int N,
+                                                             int tiles_r, int tiles_c) {
+  __shared__ __align__(16) float sc[2][BK * LDR];
+  __shared__ __align__(16) float sg[2][BK * LDR];
+  __shared__ __align__(16) float sb[2][BK * LDC];
+  const TileCoord tc(tiles_r, tiles_c);
+  const Micro8x4 mt;
+  const float* ab = a + (int64_t)tc.bt * M * K;
+  const float* bb = b + (int64_t)tc.bt * K * N;
+  const float* cb = c + (int64_t)tc.bt * M * N;
+  const float* gb = g + (int64_t)tc.bt * M * N;
+  const bool vec_n = (N % 4 == 0);
+  const bool vec_b = vec_n && aligned16(bb), vec_c = vec_n && aligned16(cb), vec_g = vec_n && aligned16(gb);
+
+  float acc[8][4], av[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = tc.r0 + mt.row(i), k = tc.c0 + mt.col(j);
+      acc[i][j] = 0.f;
+      av[i][j] = (m < M && k < K) ? __ldg(ab + (int64_t)m * K + k) : 0.f;
+    }
+
+  TileLoader<BR, BK, NT, true> lc, lg;
+  TileLoader<BC, BK, NT, true> lb;
+  const int nt = (N + BK - 1) / BK;
+  // padding: c = +inf makes the weight exp(-inf) = 0 and g = 0 removes the term
+  lc.load(cb, N, 1, tc.r0, 0, M, N, vec_c, pinf_f());
+  lg.load(gb, N, 1, tc.r0, 0, M, N, vec_g, 0.f);
+  lb.load(bb, N, 1, tc.c0, 0, K, N, vec_b, 0.f);
+  lc.store(sc[0], LDR);
+  lg.store(sg[0], LDR);
+  lb.store(sb[0], LDC);
+  __syncthreads();
+
+  for (int t = 0; t < nt; ++t) {
+    const int cur = t & 1;
+    if (t + 1 < nt) {
+      lc.load(cb, N, 1, tc.r0, (t + 1) * BK, M, N, vec_c, pinf_f());
+      lg.load(gb, N, 1, tc.r0, (t + 1) * BK, M, N, vec_g, 0.f);
+      lb.load(bb, N, 1, tc.c0, (t + 1) * BK, K, N, vec_b, 0.f);
+    }
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float cv[8], gv[8], bv[4];
+      mt.load_x(sc[cur] + kk * LDR, LDR, cv);
+      mt.load_x(sg[cur] + kk * LDR, LDR, gv);
+      mt.load_y(sb[cur] + kk * LDC, bv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc[i][j] = fmaf(exp_sfu((av[i][j] + bv[j]) - cv[i]), gv[i], acc[i][j]);
+    }
+    if (t + 1 < nt) {
+      lc.store(sc[cur ^ 1], LDR);
+      lg.store(sg[cur ^ 1], LDR);
+      lb.store(sb[cur ^ 1], LDC);
+    }
+    __syncthreads();
+  }
+  store_tile(grad_a + (int64_t)tc.bt * M * K, K, M, K, tc, mt, acc);
+}
+
+// grad_b tile: rows k, columns n, reduction over m.
+__global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __restrict__ a,
+                                                             const float* __restrict__ b,
+                                                             const float* __restrict__ c,
+                                                             const float* __restrict__ g,
+                                                             float* __restrict__ grad_b, int M, int K, int N,
+                                                             int tiles_r, int tiles_c) {
+  __shared__ __align__(16) float sa[2][BK * LDR];
+  __shared__ __align__(16) float sc[2][BK * LDC];
+  __shared__ __align__(16) float sg[2][BK * LDC];
+  const TileCoord tc(tiles_r, tiles_c);
+  const Micro8x4 mt;
+  const float* ab = a + (int64_t)tc.bt * M * K;
+  const float* bb = b + (int64_t)tc.bt * K * N;
+  const float* cb = c + (int64_t)tc.bt * M * N;
+  const float* gb = g + (int64_t)tc.bt * M * N;
+  const bool vec_a = (K % 4 == 0) && aligned16(ab);
+  const bool vec_c = (N % 4 == 0) && aligned16(cb), vec_g = (N % 4 == 0) && aligned16(gb);
+
+  float acc[8][4], bv[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = tc.r0 + mt.row(i), n = tc.c0 + mt.col(j);
+      acc[i][j] = 0.f;
+      bv[i][j] = (k < K && n < N) ? __ldg(bb + (int64_t)k * N + n) : 0.f;
+    }
+
+  TileLoader<BR, BK, NT, false> la;
+  TileLoader<BC, BK, NT, false> lc, lg;
+  const int nt = (M + BK - 1) / BK;
+  la.load(ab, 1, K, tc.r0, 0, K, M, vec_a, 0.f);
+  lc.load(cb, 1, N, tc.c0, 0, N, M, vec_c, pinf_f());
+  lg.load(gb, 1, N, tc.c0, 0, N, M, vec_g, 0.f);
+  la.store(sa[0], LDR);
+  lc.store(sc[0], LDC);
+  lg.store(sg[0], LDC);
+  __syncthreads();
+
+  for (int t = 0; t < nt; ++t) {
+    const int cur = t & 1;
+    if (t + 1 < nt) {
+      la.load(ab, 1, K, tc.r0, (t + 1) * BK, K, M, vec_a, 0.f);
+      lc.load(cb, 1, N, tc.c0, (t + 1) * BK, N, M, vec_c, pinf_f());
+      lg.load(gb, 1, N, tc.c0, (t + 1) * BK, N, M, vec_g, 0.f);
+    }
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float xa[8], cv[4], gv[4];
+      mt.load_x(sa[cur] + kk * LDR, LDR, xa);
+      mt.load_y(sc[cur] + kk * LDC, cv);
+      mt.load_y(sg[cur] + kk * LDC, gv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc[i][j] = fmaf(exp_sfu((xa[i] + bv[i][j]) - cv[j]), gv[j], acc[i][j]);
+    }
+    if (t + 1 < nt) {
+      la.store(sa[cur ^ 1], LDR);
+      lc.store(sc[cur ^ 1], LDC);
+      lg.store(sg[cur ^ 1], LDC);
+    }
+    __syncthreads();
+  }
+  store_tile(grad_b + (int64_t)tc.bt * K * N, N, K, N, tc, mt, acc);
+}
+
+// ------------------------------------------------------------------ index routing
+constexpr int ROUTE_WARPS = 8;
+
+// grad_a: one warp per (batch, m) row.  hist holds KT buckets per warp; K larger than KT is
+// covered in passes.  Lanes take 32 consecutive n at a time; lanes that target the same bucket
+// add one after another in lane (= n) order so the sum is the reference's ascending-n sum.
+template <bool MUL>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_grad_a_kernel(const float* __restrict__ b,
+                                                                         const int* __restrict__ idx,
+                                                                         const float* __restrict__ g,
+                                                                         float* __restrict__ grad_a,
+                                                                         int64_t rows, int M, int K, int N,
+                                                                         int KT) {
+  extern __shared__ float hist_all[];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int64_t row = (int64_t)blockIdx.x * ROUTE_WARPS + warp;
+  if (row >= rows) return;  // whole warp leaves together
+  float* hist = hist_all + warp * KT;
+  const int bt = (int)(row / M);
+  const int* irow = idx + row * N;
+  const float* grow = g + row * N;
+  const float* bb = b + (int64_t)bt * K * N;
+  for (int kbase = 0; kbase < K; kbase += KT) {
+    const int kend = min(kbase + KT, K);
+    for (int k = lane; k < kend - kbase; k += 32) hist[k] = 0.f;
+    __syncwarp();
+    for (int n0 = 0; n0 < N; n0 += 32) {
+      const int n = n0 + lane;
+      int k = -1;
+      float gv = 0.f;
+      if (n < N) {
+        k = __ldg(irow + n);
+        gv = __ldg(grow + n);
+      }
+      const bool hit = k >= kbase && k < kend;
+      if (MUL && hit) gv = __fmul_rn(__ldg(bb + (int64_t)k * N + n), gv);
+      // lanes without a target get distinct negative keys so they group with nobody
+      const unsigned peers = __match_any_sync(0xffffffffu, hit ? k : -1 - lane);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
+      for (int r = 0; r <= last; ++r) {
+        if (hit && rank == r) hist[k - kbase] = __fadd_rn(hist[k - kbase], gv);
+        __syncwarp();
+      }
+    }
+    for (int k = lane; k < kend - kbase; k += 32) grad_a[row * K + kbase + k] = hist[k];
+    __syncwarp();
+  }
+}
+
+// grad_b: one warp per (batch, 32 consecutive n); each lane owns a column and walks m in
+// ascending order into its private column of the [KT][32] histogram.
+template <bool MUL>
+__global__ void __launch_bounds__(32) route_grad_b_kernel(const float* __restrict__ a,
+                                                          const int* __restrict__ idx,
+                                                          const float* __restrict__ g,
+                                                          float* __restrict__ grad_b, int M, int K, int N,
+                                                          int tiles_n, int KT) {
+  extern __shared__ float hist[];
+  const int lane = threadIdx.x;
+  const int bt = blockIdx.x / tiles_n;
+  const int n = (blockIdx.x % tiles_n) * 32 + lane;
+  const bool live = n < N;
+  const int* ib = idx + (int64_t)bt * M * N;
+  const float* gb = g + (int64_t)bt * M * N;
+  const float* ab = a + (int64_t)bt * M * K;
+  float* ob = grad_b + (int64_t)bt * K * N;
+  for (int kbase = 0; kbase < K; kbase += KT) {
+    const int kend = min(kbase + KT, K);
+    for (int k = 0; k < kend - kbase; ++k) hist[k * 32 + lane] = 0.f;
+    if (live) {
+#pragma unroll 4
+      for (int m = 0; m < M; ++m) {
+        const int k = __ldg(ib + (int64_t)m * N + n);
+        float gv = __ldg(gb + (int64_t)m * N + n);
+        if (k >= kbase && k < kend) {
+          if (MUL) gv = __fmul_rn(__ldg(ab + (int64_t)m * K + k), gv);
+          hist[(k - kbase) * 32 + lane] = __fadd_rn(hist[(k - kbase) * 32 + lane], gv);
+        }
+      }
+      for (int k = 0; k < kend - kbase; ++k) ob[(int64_t)(kbase + k) * N + n] = hist[k * 32 + lane];
+    }
+  }
+}
+
+}  // namespace
+}  // namespace gbmm
+
+using namespace gbmm;
+
+extern "C" int gbmm_dense_backward_f32(int mode, const float* a, const float* b, const float* grad_out,
+                                       const float* part, const void* aux, float* grad_a, float* grad_b,
+                                       int64_t B, int64_t M, int64_t K, int64_t N, void* stream) {
+  if (mode < 0 || mode > 3) return GBMM_ERR_INVALID_ARG;
+  if (B < 0 || M < 0 || K < 0 || N < 0) return GBMM_ERR_INVALID_ARG;
+  if (B == 0 || K == 0) return GBMM_OK;  // both gradients are empty
+  if (M >= (1LL << 31) - BR || K >= (1LL << 31) - BR || N >= (1LL << 31) - BR) return GBMM_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M == 0 || N == 0) {
+    // empty reduction: the non-empty gradient is all zeros
+    if (grad_a && M > 0 && cudaMemsetAsync(grad_a, 0, sizeof(float) * B * M * K, st) != cudaSuccess)
+      return GBMM_ERR_LAUNCH;
+    if (grad_b && N > 0 && cudaMemsetAsync(grad_b, 0, sizeof(float) * B * K * N, st) != cudaSuccess)
+      return GBMM_ERR_LAUNCH;
+    return GBMM_OK;
+  }
+  if (!a || !b || !grad_out) return GBMM_ERR_INVALID_ARG;
+  const int m = (int)M, k = (int)K, n = (int)N;
+  if (mode == GBMM_MODE_LOG) {
+    if (!part) return GBMM_ERR_INVALID_ARG;
+    if (grad_a) {
+      const int64_t tr = ceil_div(M, BR), tcn = ceil_div(K, BC), blocks = B * tr * tcn;
+      if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+      dense_log_bwd_a_kernel<<<(unsigned)blocks, NT, 0, st>>>(a, b, part, grad_out, grad_a, m, k, n, (int)tr,
+                                                              (int)tcn);
+      if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+    }
+    if (grad_b) {
+      const int64_t tr = ceil_div(K, BR), tcn = ceil_div(N, BC), blocks = B * tr * tcn;
+      if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+      dense_log_bwd_b_kernel<<<(unsigned)blocks, NT, 0, st>>>(a, b, part, grad_out, grad_b, m, k, n, (int)tr,
+                                                              (int)tcn);
+    }
+    return launch_status();
+  }
+  if (!aux) return GBMM_ERR_INVALID_ARG;
+  const int* idx = static_cast<const int*>(aux);
+  const bool mul = (mode == GBMM_MODE_PRODMAX);
+  if (grad_a) {
+    const int KT = (int)(K < 2048 ? K : 2048);
+    const int64_t rows = B * M, blocks = ceil_div(rows, ROUTE_WARPS);
+    if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(float) * ROUTE_WARPS * KT;
+    if (mul) {
+      cudaFuncSetAttribute(route_grad_a_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      route_grad_a_kernel<true><<<(unsigned)blocks, ROUTE_WARPS * 32, smem, st>>>(b, idx, grad_out, grad_a, rows,
+                                                                                 m, k, n, KT);
+    } else {
+      cudaFuncSetAttribute(route_grad_a_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      route_grad_a_kernel<false><<<(unsigned)blocks, ROUTE_WARPS * 32, smem, st>>>(b, idx, grad_out, grad_a,
+                                                                                  rows, m, k, n, KT);
+    }
+    if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+  }
+  if (grad_b) {
+    const int KT = (int)(K < 1024 ? K : 1024);
+    const int64_t tiles_n = ceil_div(N, 32), blocks = B * tiles_n;
+    if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(float) * 32 * KT;
+    if (mul) {
+      cudaFuncSetAttribute(route_grad_b_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      route_grad_b_kernel<true><<<(unsigned)blocks, 32, smem, st>>>(a, idx, grad_out, grad_b, m, k, n,
+                                                                   (int)tiles_n, KT);
+    } else {
+      cudaFuncSetAttribute(route_grad_b_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      route_grad_b_kernel<false><<<(unsigned)blocks, 32, smem, st>>>(a, idx, grad_out, grad_b, m, k, n,
+                                                                    (int)tiles_n, KT);
+    }
+  }
+  return launch_status();
+}

@@ -1,0 +1,402 @@
+// Dense semiring forward kernels: c[b,m,n] = (+)_k a[b,m,k] (x) b[b,k,n].
+//
+// Replaces the reference's one-thread-per-output kernels (matmul_cuda_kernel.cu:13-152) with
+// shared-memory tiled kernels: a CTA of 256 threads owns a 128x64 tile of the result, each
+// thread an 8x4 micro-tile; operand tiles of 16 reduction steps are double-buffered through
+// registers into shared memory.
+//
+//   max-plus / prod-max : per reduction tile only the tile maximum is tracked (FADD|FMUL + one
+//       3-input FMNMX per two terms); a strict `>` against the running maximum, taken in tile
+//       order, remembers the first tile that reached it, and that one tile is rescanned at the
+//       end for the first k attaining the maximum.  This reproduces the reference's
+//       `if (v > m) { m = v; ind = i; }` (lowest k on ties, -1 and -1e9 when nothing exceeds
+//       -1e9) bit for bit, including the sign of a zero maximum.
+//   log : per tile, the exact tile maximum first, one rescale of the running sum when it
+//       grows, then exp(v - m) on the SFU.  The running maximum starts at -1e9 as in the
+//       reference.
+//   sample : the log kernel followed by an inverse-CDF pass that keeps the reference's fp32
+//       running sum in ascending k and its strict double inequality.
+#include "tile.cuh"
+
+namespace gbmm {
+namespace {
+
+constexpr int BM = 128, BN = 64, BK = 16, NT = 256;
+constexpr int LDX = BM + 4, LDY = BN + 4;
+
+struct TileCoord {
+  int bt, m0, n0;
+  __device__ __forceinline__ TileCoord(int tiles_m, int tiles_n) {
+    const int64_t id = blockIdx.x;
+    n0 = (int)(id % tiles_n) * BN;
+    m0 = (int)((id / tiles_n) % tiles_m) * BM;
+    bt = (int)(id / ((int64_t)tiles_n * tiles_m));
+  }
+};
+
+__device__ __forceinline__ float nan_f() { return __int_as_float(0x7fc00000); }
+__device__ __forceinline__ float ninf_f() { return __int_as_float(0xff800000); }
+// ------------------------------------------------------------------ max-plus / prod-max
+template <bool MUL>
+__global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restrict__ a,
+                                                           const float* __restrict__ b,
+                                                           float* __restrict__ out,
+                                                           int* __restrict__ idx, int M, int K, int N,
+                                                           int tiles_m, int tiles_n) {
+  __shared__ __align__(16) float sx[2][BK * LDX];
+  __shared__ __align__(16) float sy[2][BK * LDY];
+  const TileCoord tc(tiles_m, tiles_n);
+  const Micro8x4 mt;
+  const float* ab = a + (int64_t)tc.bt * M * K;
+  const float* bb = b + (int64_t)tc.bt * K * N;
+  const bool vec_a = aligned16(ab) && (K % 4 == 0);
+  const bool vec_b = aligned16(bb) && (N % 4 == 0);
+
+  float best[8][4], cm[8][4];
+  int cid[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      best[i][j] = kFloor;
+      cm[i][j] = ninf_f();
+      cid[i][j] = -1;
+    }
+
+  TileLoader<BM, BK, NT, true> la;
+  TileLoader<BN, BK, NT, false> lb;
+  const int nt = (K + BK - 1) / BK;
+  // a NaN in the padded reduction steps makes the term a NaN, which the maximum ignores
+  la.load(ab, K, 1, tc.m0, 0, M, K, vec_a, nan_f());
+  lb.load(bb, 1, N, tc.n0, 0, N, K, vec_b, 0.f);
+  la.store(sx[0], LDX);
+  lb.store(sy[0], LDY);
+  __syncthreads();
+
+  for (int t = 0; t < nt; ++t) {
+    const int cur = t & 1;
+    if (t + 1 < nt) {
+      la.load(ab, K, 1, tc.m0, (t + 1) * BK, M, K, vec_a, nan_f());
+      lb.load(bb, 1, N, tc.n0, (t + 1) * BK, N, K, vec_b, 0.f);
+    }
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 2) {
+      float x0[8], x1[8], y0[4], y1[4];
+      mt.load_x(sx[cur] + kk * LDX, LDX, x0);
+      mt.load_y(sy[cur] + kk * LDY, y0);
+      mt.load_x(sx[cur] + (kk + 1) * LDX, LDX, x1);
+      mt.load_y(sy[cur] + (kk + 1) * LDY, y1);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float v0 = MUL ? __fmul_rn(x0[i], y0[j]) : __fadd_rn(x0[i], y0[j]);
+          const float v1 = MUL ? __fmul_rn(x1[i], y1[j]) : __fadd_rn(x1[i], y1[j]);
+          cm[i][j] = max3(cm[i][j], v0, v1);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (cm[i][j] > best[i][j]) {
+          best[i][j] = cm[i][j];
+          cid[i][j] = t;
+        }
+        cm[i][j] = ninf_f();
+      }
+    if (t + 1 < nt) {
+      la.store(sx[cur ^ 1], LDX);
+      lb.store(sy[cur ^ 1], LDY);
+    }
+    __syncthreads();
+  }
+
+  // Rescan the winning tile of every result for the first k that attains the maximum; the
+  // stored value is that term itself, so a zero keeps the sign the reference would keep.
+  float* ob = out + (int64_t)tc.bt * M * N;
+  int* ib = idx + (int64_t)tc.bt * M * N;
+  const bool vec_o = aligned16(ob) && aligned16(ib) && (N % 4 == 0);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int m = tc.m0 + mt.row(i);
+    if (m >= M) continue;
+    float val[4];
+    int ind[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = tc.n0 + mt.col(j);
+      val[j] = best[i][j];
+      ind[j] = -1;
+      if (n < N && cid[i][j] >= 0) {
+        const int k0 = cid[i][j] * BK;
+        const int k1 = min(k0 + BK, K);
+        const float* ap = ab + (int64_t)m * K;
+        const float* bp = bb + n;
+#pragma unroll 1
+        for (int k = k0; k < k1; ++k) {
+          const float x = __ldg(ap + k), y = __ldg(bp + (int64_t)k * N);
+          const float v = MUL ? __fmul_rn(x, y) : __fadd_rn(x, y);
+          if (v == best[i][j]) {
+            val[j] = v;
+            ind[j] = k;
+            break;
+          }
+        }
+      }
+    }
+    const int nb = tc.n0 + mt.col(0);
+    if (vec_o && nb + 3 < N) {
+      *reinterpret_cast<float4*>(ob + (int64_t)m * N + nb) = make_float4(val[0], val[1], val[2], val[3]);
+      *reinterpret_cast<int4*>(ib + (int64_t)m * N + nb) = make_int4(ind[0], ind[1], ind[2], ind[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (nb + j < N) {
+          ob[(int64_t)m * N + nb + j] = val[j];
+          ib[(int64_t)m * N + nb + j] = ind[j];
+        }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ log-sum-exp
+__global__ void __launch_bounds__(NT) dense_log_fwd_kernel(const float* __restrict__ a,
+                                                           const float* __restrict__ b,
+                                                           float* __restrict__ out,
+                                                           float* __restrict__ maxes, int M, int K, int N,
+                                                           int tiles_m, int tiles_n) {
+  __shared__ __align__(16) float sx[2][BK * LDX];
+  __shared__ __align__(16) float sy[2][BK * LDY];
+  const TileCoord tc(tiles_m, tiles_n);
+  const Micro8x4 mt;
+  const float* ab = a + (int64_t)tc.bt * M * K;
+  const float* bb = b + (int64_t)tc.bt * K * N;
+  const bool vec_a = aligned16(ab) && (K % 4 == 0);
+  const bool vec_b = aligned16(bb) && (N % 4 == 0);
+
+  float mx[8][4], sum[8][4], tmx[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      mx[i][j] = kFloor;
+      sum[i][j] = 0.f;
+    }
+
+  TileLoader<BM, BK, NT, true> la;
+  TileLoader<BN, BK, NT, false> lb;
+  const int nt = (K + BK - 1) / BK;
+  // padded reduction steps carry -inf: ignored by the maximum, exp(-inf - m) = 0 in the sum
+  la.load(ab, K, 1, tc.m0, 0, M, K, vec_a, ninf_f());
+  lb.load(bb, 1, N, tc.n0, 0, N, K, vec_b, 0.f);
+  la.store(sx[0], LDX);
+  lb.store(sy[0], LDY);
+  __syncthreads();
+
+  for (int t = 0; t < nt; ++t) {
+    const int cur = t & 1;
+    if (t + 1 < nt) {
+      la.load(ab, K, 1, tc.m0, (t + 1) * BK, M, K, vec_a, ninf_f());
+      lb.load(bb, 1, N, tc.n0, (t + 1) * BK, N, K, vec_b, 0.f);
+    }
+    // pass 1: exact maximum of this tile's terms
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) tmx[i][j] = ninf_f();
+#pragma unroll 2
+    for (int kk = 0; kk < BK; kk += 2) {
+      float x0[8], x1[8], y0[4], y1[4];
+      mt.load_x(sx[cur] + kk * LDX, LDX, x0);
+      mt.load_y(sy[cur] + kk * LDY, y0);
+      mt.load_x(sx[cur] + (kk + 1) * LDX, LDX, x1);
+      mt.load_y(sy[cur] + (kk + 1) * LDY, y1);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tmx[i][j] = max3(tmx[i][j], x0[i] + y0[j], x1[i] + y1[j]);
+    }
+    // rescale the running sum where the maximum grew
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (tmx[i][j] > mx[i][j]) {
+          sum[i][j] *= exp_sfu(mx[i][j] - tmx[i][j]);
+          mx[i][j] = tmx[i][j];
+        }
+    // The sums of pass 1 are recomputed, not kept: the barrier stops the compiler from
+    // carrying BK*32 of them in registers across the two passes.
+    asm volatile("" ::: "memory");
+    // pass 2: accumulate exp(v - m)
+#pragma unroll 4
+    for (int kk = 0; kk < BK; ++kk) {
+      float x[8], y[4];
+      mt.load_x(sx[cur] + kk * LDX, LDX, x);
+      mt.load_y(sy[cur] + kk * LDY, y);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sum[i][j] += exp_sfu((x[i] + y[j]) - mx[i][j]);
+    }
+    if (t + 1 < nt) {
+      la.store(sx[cur ^ 1], LDX);
+      lb.store(sy[cur ^ 1], LDY);
+    }
+    __syncthreads();
+  }
+
+  float* ob = out + (int64_t)tc.bt * M * N;
+  float* mb = maxes ? maxes + (int64_t)tc.bt * M * N : nullptr;
+  const bool vec_o = aligned16(ob) && (!mb || aligned16(mb)) && (N % 4 == 0);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int m = tc.m0 + mt.row(i);
+    if (m >= M) continue;
+    float val[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) val[j] = logf(sum[i][j]) + mx[i][j];
+    const int nb = tc.n0 + mt.col(0);
+    if (vec_o && nb + 3 < N) {
+      *reinterpret_cast<float4*>(ob + (int64_t)m * N + nb) = make_float4(val[0], val[1], val[2], val[3]);
+      if (mb)
+        *reinterpret_cast<float4*>(mb + (int64_t)m * N + nb) =
+            make_float4(mx[i][0], mx[i][1], mx[i][2], mx[i][3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (nb + j < N) {
+          ob[(int64_t)m * N + nb + j] = val[j];
+          if (mb) mb[(int64_t)m * N + nb + j] = mx[i][j];
+        }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ inverse-CDF sampling pass
+// Follows matmul_cuda_kernel.cu:109-118: with p_k = exp(a+b-out) and `total` the fp32 running
+// sum in ascending k, the sample is the first k with total < u and total + p_k > u; 0 if none.
+// total never decreases, so the condition can hold for one k only and no early exit is needed.
+__global__ void __launch_bounds__(NT) dense_sample_pick_kernel(const float* __restrict__ a,
+                                                               const float* __restrict__ b,
+                                                               const float* __restrict__ u,
+                                                               const float* __restrict__ out,
+                                                               int* __restrict__ idx, int M, int K, int N,
+                                                               int tiles_m, int tiles_n) {
+  __shared__ __align__(16) float sx[2][BK * LDX];
+  __shared__ __align__(16) float sy[2][BK * LDY];
+  const TileCoord tc(tiles_m, tiles_n);
+  const Micro8x4 mt;
+  const float* ab = a + (int64_t)tc.bt * M * K;
+  const float* bb = b + (int64_t)tc.bt * K * N;
+  const float* ub = u + (int64_t)tc.bt * M * N;
+  const float* ob = out + (int64_t)tc.bt * M * N;
+  const bool vec_a = aligned16(ab) && (K % 4 == 0);
+  const bool vec_b = aligned16(bb) && (N % 4 == 0);
+
+  float total[8][4], lse[8][4], r[8][4];
+  int pick[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = tc.m0 + mt.row(i), n = tc.n0 + mt.col(j);
+      const bool ok = m < M && n < N;
+      total[i][j] = 0.f;
+      pick[i][j] = 0;
+      lse[i][j] = ok ? __ldg(ob + (int64_t)m * N + n) : 0.f;
+      r[i][j] = ok ? __ldg(ub + (int64_t)m * N + n) : 0.f;
+    }
+
+  TileLoader<BM, BK, NT, true> la;
+  TileLoader<BN, BK, NT, false> lb;
+  const int nt = (K + BK - 1) / BK;
+  la.load(ab, K, 1, tc.m0, 0, M, K, vec_a, ninf_f());
+  lb.load(bb, 1, N, tc.n0, 0, N, K, vec_b, 0.f);
+  la.store(sx[0], LDX);
+  lb.store(sy[0], LDY);
+  __syncthreads();
+
+  for (int t = 0; t < nt; ++t) {
+    const int cur = t & 1;
+    if (t + 1 < nt) {
+      la.load(ab, K, 1, tc.m0, (t + 1) * BK, M, K, vec_a, ninf_f());
+      lb.load(bb, 1, N, tc.n0, (t + 1) * BK, N, K, vec_b, 0.f);
+    }
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float x[8], y[4];
+      mt.load_x(sx[cur] + kk * LDX, LDX, x);
+      mt.load_y(sy[cur] + kk * LDY, y);
+      const int k = t * BK + kk;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float e = exp_sfu((x[i] + y[j]) - lse[i][j]);
+          const float nxt = total[i][j] + e;
+          if (total[i][j] < r[i][j] && nxt > r[i][j]) pick[i][j] = k;
+          total[i][j] = nxt;
+        }
+    }
+    if (t + 1 < nt) {
+      la.store(sx[cur ^ 1], LDX);
+      lb.store(sy[cur ^ 1], LDY);
+    }
+    __syncthreads();
+  }
+
+  int* ib = idx + (int64_t)tc.bt * M * N;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int m = tc.m0 + mt.row(i);
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = tc.n0 + mt.col(j);
+      if (n < N) ib[(int64_t)m * N + n] = pick[i][j];
+    }
+  }
+}
+
+}  // namespace
+}  // namespace gbmm
+
+using namespace gbmm;
+
+extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, const float* u, float* out,
+                                      void* aux, int64_t B, int64_t M, int64_t K, int64_t N, void* stream) {
+  if (mode < 0 || mode > 3) return GBMM_ERR_INVALID_ARG;
+  if (B < 0 || M < 0 || K < 0 || N < 0) return GBMM_ERR_INVALID_ARG;
+  if (B == 0 || M == 0 || N == 0) return GBMM_OK;
+  if (!a && K > 0) return GBMM_ERR_INVALID_ARG;
+  if (!b && K > 0) return GBMM_ERR_INVALID_ARG;
+  if (!out) return GBMM_ERR_INVALID_ARG;
+  if (mode != GBMM_MODE_LOG && !aux) return GBMM_ERR_INVALID_ARG;
+  if (mode == GBMM_MODE_SAMPLE && !u) return GBMM_ERR_INVALID_ARG;
+  if (M >= (1LL << 31) - BM || K >= (1LL << 31) - BK || N >= (1LL << 31) - BN) return GBMM_ERR_UNSUPPORTED;
+  const int64_t tiles_m = ceil_div(M, BM), tiles_n = ceil_div(N, BN);
+  const int64_t blocks = B * tiles_m * tiles_n;
+  if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid((unsigned)blocks), block(NT);
+  const int m = (int)M, k = (int)K, n = (int)N, tm = (int)tiles_m, tn = (int)tiles_n;
+  switch (mode) {
+    case GBMM_MODE_LOG:
+      dense_log_fwd_kernel<<<grid, block, 0, st>>>(a, b, out, static_cast<float*>(aux), m, k, n, tm, tn);
+      break;
+    case GBMM_MODE_MAX:
+      dense_max_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, static_cast<int*>(aux), m, k, n, tm, tn);
+      break;
+    case GBMM_MODE_PRODMAX:
+      dense_max_fwd_kernel<true><<<grid, block, 0, st>>>(a, b, out, static_cast<int*>(aux), m, k, n, tm, tn);
+      break;
+    case GBMM_MODE_SAMPLE:
+      dense_log_fwd_kernel<<<grid, block, 0, st>>>(a, b, out, nullptr, m, k, n, tm, tn);
+      if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+      dense_sample_pick_kernel<<<grid, block, 0, st>>>(a, b, u, out, static_cast<int*>(aux), m, k, n, tm, tn);
+      break;
+  }
+  return launch_status();
+}

@@ -1,0 +1,131 @@
+"""Dense semiring batched matrix products as torch.autograd.Functions.
+
+Same public names and call shapes as the reference's genbmm/genmul.py:100-103:
+`logbmm(a, b)`, `maxbmm(a, b)`, `samplebmm(a, b)`, `prodmaxbmm(a, b)` on 3-D CUDA tensors
+a:(B,M,K), b:(B,K,N), each returning c:(B,M,N) of a's dtype.  Additive: `samplebmm` takes
+an optional third argument, the uniforms that drive the sample.
+
+Differences from the reference that a caller can observe:
+  * the logbmm backward makes no transposed copies (genmul.py:38-41 makes six);
+  * half / bfloat16 inputs are computed in float32 and cast back; float64 is rejected
+    (the kernels are fp32);
+  * inputs must be contiguous CUDA tensors, as in the reference (matmul_cuda.cpp:65-67).
+"""
+import torch
+
+from . import _native
+
+
+def trans(s):
+    return s.transpose(-2, -1).contiguous()
+
+
+def _as_f32(x, name):
+    if x.dtype == torch.float32:
+        return x
+    if x.dtype in (torch.float16, torch.bfloat16):
+        return x.float()
+    raise RuntimeError("%s: dtype %s is not supported by the fp32 kernels" % (name, x.dtype))
+
+
+class LogMatMulBack(torch.autograd.Function):
+    """First-order gradients of logbmm as a differentiable node (genmul.py:11-24).
+
+    forward returns (grad_a, grad_b) in one call.
+    """
+
+    @staticmethod
+    def forward(ctx, a, b, grad_out, part):
+        ctx.save_for_backward(a, b, grad_out, part)
+        grad_a, grad_b = _native.backward(a, b, grad_out, part, None, _native.MODE_LOG)
+        return grad_a, grad_b
+
+    @staticmethod
+    def backward(ctx, h_a, h_b):
+        raise NotImplementedError(
+            "genbmm_b200.logbmm: second-order gradients (create_graph=True) are not built yet")
+
+
+class LogMatMul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b):
+        a32, b32 = _as_f32(a, "a"), _as_f32(b, "b")
+        out, _ = _native.forward(a32, b32, _native.MODE_LOG, want_maxes=False)
+        ctx.save_for_backward(a32, b32, out)
+        ctx.dtypes = (a.dtype, b.dtype)
+        return out.to(a.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        a, b, out = ctx.saved_tensors
+        grad_a, grad_b = LogMatMulBack.apply(a, b, grad_output.contiguous().float(), out)
+        return grad_a.to(ctx.dtypes[0]), grad_b.to(ctx.dtypes[1])
+
+
+class _IndexRouted(torch.autograd.Function):
+    """Shared shape of the three index-routed products (genmul.py:50-97)."""
+
+    MODE = None
+
+    @classmethod
+    def _forward(cls, ctx, a, b, u=None):
+        a32, b32 = _as_f32(a, "a"), _as_f32(b, "b")
+        out, switches = _native.forward(a32, b32, cls.MODE, u)
+        ctx.save_for_backward(a32, b32, switches)
+        ctx.dtypes = (a.dtype, b.dtype)
+        return out.to(a.dtype)
+
+    @classmethod
+    def _backward(cls, ctx, grad_output):
+        a, b, switches = ctx.saved_tensors
+        grad_a, grad_b = _native.backward(a, b, grad_output.contiguous().float(), switches, switches, cls.MODE)
+        return grad_a.to(ctx.dtypes[0]), grad_b.to(ctx.dtypes[1])
+
+
+class MaxMatMul(_IndexRouted):
+    MODE = _native.MODE_MAX
+
+    @staticmethod
+    def forward(ctx, a, b):
+        return MaxMatMul._forward(ctx, a, b)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return MaxMatMul._backward(ctx, grad_output)
+
+
+class SampleMatMul(_IndexRouted):
+    MODE = _native.MODE_SAMPLE
+
+    @staticmethod
+    def forward(ctx, a, b, u=None):
+        return SampleMatMul._forward(ctx, a, b, u)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return SampleMatMul._backward(ctx, grad_output) + (None,)
+
+
+class ProdMaxMatMul(_IndexRouted):
+    MODE = _native.MODE_PRODMAX
+
+    @staticmethod
+    def forward(ctx, a, b):
+        return ProdMaxMatMul._forward(ctx, a, b)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return ProdMaxMatMul._backward(ctx, grad_output)
+
+
+logbmm = LogMatMul.apply
+maxbmm = MaxMatMul.apply
+prodmaxbmm = ProdMaxMatMul.apply
+
+
+def samplebmm(a, b, u=None):
+    """log-sum-exp value whose gradient is a one-hot sample from softmax_k(a+b).
+
+    `u`:(B,M,N) uniforms in [0,1) select the sample; omitted, they are drawn on the device.
+    """
+    return SampleMatMul.apply(a, b, u)

@@ -1,0 +1,115 @@
+/*
+ * genbmm_b200 — C ABI of the B200 (sm_100a) semiring batched-matmul library.
+ *
+ * Every entry point takes raw device pointers, plain sizes and a CUDA stream
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream), launches
+ * asynchronously on that stream and returns a status code (0 = ok).  Nothing
+ * here allocates, frees or synchronises unless a comment says otherwise.
+ * All tensors are fp32 (indices int32), row-major and contiguous.
+ *
+ * The entry points replace, one for one, the functions of the reference's
+ * pybind11 module `_genbmm` (harvardnlp/genbmm, matmul_cuda.cpp:165-172); the
+ * comment on each declaration names the reference function it stands in for.
+ * The difference in shape is deliberate: the reference functions allocate and
+ * return torch tensors, these fill caller-provided buffers.
+ */
+#ifndef GENBMM_B200_H
+#define GENBMM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define GBMM_OK 0
+#define GBMM_ERR_INVALID_ARG 1  /* null pointer, negative size, unknown mode */
+#define GBMM_ERR_UNSUPPORTED 2  /* size beyond what the kernels index (e.g. a dimension >= 2^31) */
+#define GBMM_ERR_LAUNCH 3       /* the CUDA runtime refused a launch (see cudaGetLastError) */
+#define GBMM_ERR_DEVICE 4       /* not an sm_100 device, or no device */
+
+/* semiring selectors — the integer `mode` of the reference
+ * (dense: matmul_cuda_kernel.cu:487-542; banded: banded_cuda_kernel.cu:42-98) */
+#define GBMM_MODE_LOG 0
+#define GBMM_MODE_MAX 1
+#define GBMM_MODE_SAMPLE 2   /* dense only */
+#define GBMM_MODE_PRODMAX 3  /* dense only */
+#define GBMM_BAND_LOG 0
+#define GBMM_BAND_MAX 1
+#define GBMM_BAND_MUL 3
+
+/* Human-readable text for a status code (static storage). */
+const char* gbmm_status_string(int status);
+
+/* ABI version of this header. */
+int gbmm_abi_version(void);
+
+/*
+ * Dense forward.  Replaces `_genbmm.forward(a, b, mode)` — matmul_forward,
+ * matmul_cuda.cpp:69-77 -> matmul_cuda_forward, matmul_cuda_kernel.cu:465-543.
+ *   a:(B,M,K) b:(B,K,N) -> out:(B,M,N)
+ *   mode LOG:     out = log sum_k exp(a+b); aux (float*, may be NULL) receives the
+ *                 running maximum `maxes` the reference returns as its second output.
+ *   mode MAX:     out = max_k a+b; aux (int32*) = argmax, lowest k on ties, -1 if no
+ *                 term exceeds -1e9.
+ *   mode PRODMAX: out = max_k a*b; aux as for MAX.
+ *   mode SAMPLE:  out = log sum_k exp(a+b); aux (int32*) = first k with
+ *                 cdf(k-1) < u < cdf(k) of softmax_k(a+b), 0 if none; `u`:(B,M,N) are the
+ *                 uniforms, which the reference draws itself (matmul_cuda_kernel.cu:517)
+ *                 and this ABI takes from the caller.  `u` is ignored by other modes.
+ */
+int gbmm_dense_forward_f32(int mode, const float* a, const float* b, const float* u,
+                           float* out, void* aux,
+                           int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+
+/*
+ * Dense backward.  Replaces `_genbmm.backward(a, b, grad_output, part, maxes, mode)`
+ * — matmul_backward, matmul_cuda.cpp:79-92 -> matmul_cuda_backward,
+ * matmul_cuda_kernel.cu:625-720.  Fills grad_a:(B,M,K) and grad_b:(B,K,N); either
+ * may be NULL to skip it.  Unlike the reference, mode LOG fills grad_b too (the
+ * reference leaves it zero and obtains it from a second call on transposed copies,
+ * genmul.py:38-41).
+ *   mode LOG:  part = the forward's out (float*); aux unused (may be NULL).
+ *   other modes: aux = the forward's int32 indices; part unused (may be NULL).
+ */
+int gbmm_dense_backward_f32(int mode, const float* a, const float* b, const float* grad_out,
+                            const float* part, const void* aux,
+                            float* grad_a, float* grad_b,
+                            int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+
+/*
+ * Banded forward.  Replaces `_genbmm.forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode)`
+ * — banded_forward, matmul_cuda.cpp:112-123 -> banded_cuda_forward,
+ * banded_cuda_kernel.cu:354-402.
+ *   a:(B,n,a_lu+a_ld+1) b:(B,n,b_lu+b_ld+1) -> out:(B,n,Wo), Wo = Wa+Wb-1, with result
+ *   bands lu = a_lu+b_ld, ld = a_ld+b_lu.  Cells outside the matrix are written as 0.
+ *   idx (int32*, mode MAX; argmax in a's band coordinate, -1 if none) and maxes
+ *   (float*, mode LOG) may be NULL when not wanted; they are written in full
+ *   (0 outside the matrix) when given.
+ */
+int gbmm_band_forward_f32(int mode, const float* a, int a_lu, int a_ld,
+                          const float* b, int b_lu, int b_ld,
+                          float* out, int32_t* idx, float* maxes,
+                          int64_t B, int64_t n, void* stream);
+
+/*
+ * Banded backward.  Replaces `_genbmm.backward_band(a, a_lu, a_lb, b, b_lu, b_lb,
+ * grad_output, part, mode)` — banded_backward, matmul_cuda.cpp:125-143 ->
+ * banded_cuda_backward, banded_cuda_kernel.cu:404-450 — which yields grad_a only; the
+ * reference gets grad_b from a second call with operands swapped and band-transposed
+ * cotangents (sparse.py:436-446, 540-544, 625-635).  Here grad_b:(B,n,Wb) is computed
+ * directly; grad_a or grad_b may be NULL to skip it.
+ *   mode MUL: part unused.  mode LOG: part = forward out (float*).
+ *   mode MAX: part = forward idx (int32*, a's band coordinate).
+ */
+int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_ld,
+                           const float* b, int b_lu, int b_ld,
+                           const float* grad_out, const void* part,
+                           float* grad_a, float* grad_b,
+                           int64_t B, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GENBMM_B200_H */

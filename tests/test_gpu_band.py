@@ -1,0 +1,143 @@
+"""Parity of the banded CUDA kernels (through the C ABI) with the CPU oracle and the golden fixtures."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from util import assert_close, assert_equal_bits, band_inside, cfg5
+
+pytestmark = pytest.mark.gpu
+
+# (B, n, a_lu, a_ld, b_lu, b_ld)
+CASES = [(2, 5, 2, 1, 1, 2), (3, 8, 0, 3, 2, 0), (2, 6, 3, 3, 3, 3), (1, 4, 5, 4, 0, 0), (2, 9, 1, 1, 2, 2),
+         (1, 1, 0, 0, 0, 0), (2, 70, 4, 7, 9, 2), (2, 300, 20, 13, 5, 31), (1, 40, 64, 64, 64, 64),
+         (3, 33, 0, 0, 3, 1)]
+MODES = [("multiply", 3), ("multiply_log", 0), ("multiply_max", 1)]
+
+
+@pytest.fixture(scope="module")
+def gb():
+    import genbmm_b200
+    return genbmm_b200
+
+
+def run(gb, method, a, alu, ald, b, blu, bld, g):
+    ad, bd = a.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+    r = getattr(gb.BandedMatrix(ad, alu, ald), method)(gb.BandedMatrix(bd, blu, bld))
+    ga, gb_ = torch.autograd.grad(r.data, (ad, bd), g.cuda())
+    return r, ga, gb_
+
+
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("method,mode", MODES)
+def test_band_products_match_oracle(gb, case, method, mode):
+    B, n, alu, ald, blu, bld = case
+    gen = torch.Generator().manual_seed(sum(case) + mode)
+    a = torch.randn(B, n, alu + ald + 1, generator=gen)
+    b = torch.randn(B, n, blu + bld + 1, generator=gen)
+    g = torch.rand(B, n, alu + ald + blu + bld + 1, generator=gen)
+    if mode == 1:  # ties on purpose
+        a, b = (a * 4).round() / 4, (b * 4).round() / 4
+    r, ga, gb_ = run(gb, method, a, alu, ald, b, blu, bld, g)
+    assert (r.lu, r.ld) == (alu + bld, ald + blu)
+    if mode == 1:
+        out, idx, _, dA, dB = oracle.band_fwd_bwd(mode, a, alu, ald, b, blu, bld, g)
+        assert_equal_bits(r.data, out, "max value")
+        from genbmm_b200 import _native
+        _, idx_gpu, _ = _native.forward_band(a.cuda(), alu, ald, b.cuda(), blu, bld, 1)
+        assert_equal_bits(idx_gpu, idx, "max index")
+        assert_equal_bits(ga, dA, "max grad_a")
+        assert_equal_bits(gb_, dB, "max grad_b")
+    else:
+        out, _, _, dA, dB = oracle.band_fwd_bwd(mode, a, alu, ald, b, blu, bld, g, dtype=np.float64)
+        assert_close(r.data, out, what=method)
+        assert_close(ga, dA, what=method + " grad_a")
+        assert_close(gb_, dB, what=method + " grad_b")
+    inside = band_inside(B, n, alu + bld, ald + blu)
+    assert (r.data.cpu().numpy()[~inside] == 0).all()
+
+
+@pytest.mark.parametrize("ci", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("method,name", [("multiply", "mul"), ("multiply_log", "log"), ("multiply_max", "max")])
+def test_band_products_match_reference_fixture(gb, golden, ci, method, name):
+    B, n, alu, ald, blu, bld = (int(v) for v in golden["band%d_dims" % ci])
+    f = lambda k: torch.from_numpy(golden["band%d_%s" % (ci, k)]).float()
+    r, ga, gb_ = run(gb, method, f("a"), alu, ald, f("b"), blu, bld, f("g"))
+    inside = band_inside(B, n, alu + bld, ald + blu)
+    assert_close(r.data.cpu().numpy()[inside], golden["band%d_%s_out" % (ci, name)][inside], what=name)
+    assert_close(ga, golden["band%d_%s_ga" % (ci, name)] * band_inside(B, n, alu, ald), what=name + " grad_a")
+    assert_close(gb_, golden["band%d_%s_gb" % (ci, name)] * band_inside(B, n, blu, bld), what=name + " grad_b")
+
+
+def test_reference_test_property(gb):
+    """genbmm/test_cuda.py:81-109: b.multiply_log(a.transpose()) against the CPU loops."""
+    gen = torch.Generator().manual_seed(0)
+    B, n, lu, ld = 4, 5, 3, 4
+    band = gb.banddiag(torch.rand(B, n, n, generator=gen), lu, ld)[0]
+    band2 = gb.banddiag(torch.rand(B, n, n, generator=gen), lu, ld)[0]
+    x, y = gb.BandedMatrix(band.cuda(), lu, ld), gb.BandedMatrix(band2.cuda(), lu, ld)
+    got = y.multiply_log(x.transpose())
+    xt = oracle.band_transpose(band, lu, ld)
+    want, _, _ = oracle.band_fwd(0, band2, lu, ld, xt, ld, lu, dtype=np.float64)
+    assert_close(got.data, want)
+
+
+def test_config5_full_size(gb):
+    """n=8192, 129 diagonals: the oracle on a batch slice, then properties at full size."""
+    from genbmm_b200 import _native
+    a, b = cfg5()
+    lu = ld = 64
+    ad, bd = a.cuda(), b.cuda()
+    gen = torch.Generator().manual_seed(44)
+    g = torch.rand(32, 8192, 257, generator=gen)
+    gd = g.cuda()
+    for mode in (3, 0, 1):
+        out, idx, _ = _native.forward_band(ad, lu, ld, bd, lu, ld, mode)
+        part = out if mode == 0 else idx
+        ga, gb_ = _native.backward_band(ad, lu, ld, bd, lu, ld, gd, part, mode, both=True)
+        dt = np.float32 if mode == 1 else np.float64
+        wout, widx, _, dA, dB = oracle.band_fwd_bwd(mode, a[:1], lu, ld, b[:1], lu, ld, g[:1], dtype=dt)
+        if mode == 1:
+            assert_equal_bits(out[:1], wout)
+            assert_equal_bits(idx[:1], widx)
+            assert_equal_bits(ga[:1], dA)
+            assert_equal_bits(gb_[:1], dB)
+        else:
+            assert_close(out[:1], wout, 1e-5, 2e-5)
+            assert_close(ga[:1], dA, 1e-5, 2e-5)
+            assert_close(gb_[:1], dB, 1e-5, 2e-5)
+    # linearity of the ordinary product at full size
+    out1 = _native.forward_band(ad, lu, ld, bd, lu, ld, 3)[0]
+    out2 = _native.forward_band(2 * ad, lu, ld, bd, lu, ld, 3)[0]
+    assert torch.allclose(out2, 2 * out1, rtol=1e-6, atol=1e-6)
+    # max-plus: adding t to every entry of a adds t to every in-matrix result, indices unchanged
+    o1, i1, _ = _native.forward_band(ad, lu, ld, bd, lu, ld, 1)
+    o2, i2, _ = _native.forward_band(ad + 0.5, lu, ld, bd, lu, ld, 1)
+    inside = torch.from_numpy(band_inside(32, 8192, 128, 128).copy()).cuda()
+    assert torch.equal(i1, i2)
+    assert torch.allclose(o2[inside], o1[inside] + 0.5, rtol=0, atol=1e-5)
+    # log bounds max
+    ol = _native.forward_band(ad, lu, ld, bd, lu, ld, 0)[0]
+    assert (ol[inside] >= o1[inside] - 1e-4).all() and (ol[inside] <= o1[inside] + np.log(129.0) + 1e-4).all()
+
+
+def test_wide_band_falls_back_to_global_reads(gb):
+    """Bands too wide for shared-memory staging take the unstaged path."""
+    B, n, lu, ld = 1, 600, 150, 149
+    gen = torch.Generator().manual_seed(3)
+    a, b = torch.randn(B, n, 300, generator=gen), torch.randn(B, n, 300, generator=gen)
+    g = torch.rand(B, n, 599, generator=gen)
+    for method, mode in MODES:
+        r, ga, gb_ = run(gb, method, a, lu, ld, b, lu, ld, g)
+        out, idx, _, dA, dB = oracle.band_fwd_bwd(mode, a, lu, ld, b, lu, ld, g, dtype=np.float64)
+        assert_close(r.data, out, 1e-5, 2e-5, what=method)
+        assert_close(ga, dA, 1e-5, 2e-5, what=method + " grad_a")
+        assert_close(gb_, dB, 1e-5, 2e-5, what=method + " grad_b")
+
+
+def test_band_rejects_bad_inputs(gb):
+    a = torch.rand(2, 5, 3)
+    with pytest.raises(RuntimeError, match="a must be a CUDA tensor"):
+        gb.BandedMatrix(a, 1, 1).multiply(gb.BandedMatrix(a.cuda(), 1, 1))
+    with pytest.raises(AssertionError):
+        gb.BandedMatrix(a.cuda(), 2, 2)
