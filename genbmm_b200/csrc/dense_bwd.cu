@@ -83,11 +83,13 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __rest
   TileLoader<BR, BK, NT, true> lc, lg;
   TileLoader<BC, BK, NT, true> lb;
   const int nt = (N + BK - 1) / BK;
-  // padding: c = +inf makes the weight exp(-inf) = 0 and g = 0 removes the term
+  // c is staged as -c*log2(e), so that exp(a+b-c) = 2^((a+b)*log2e + staged): one FADD, one FFMA,
+  // one MUFU and the accumulating FFMA per term.  Padding: c = +inf makes the weight 0 and g = 0
+  // removes the term
   lc.load(cb, N, 1, tc.r0, 0, M, N, vec_c, pinf_f());
   lg.load(gb, N, 1, tc.r0, 0, M, N, vec_g, 0.f);
   lb.load(bb, N, 1, tc.c0, 0, K, N, vec_b, 0.f);
-  lc.store(sc[0], LDR);
+  lc.store_scaled(sc[0], LDR, -kLog2e);
   lg.store(sg[0], LDR);
   lb.store(sb[0], LDC);
   __syncthreads();
@@ -109,10 +111,10 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __rest
       for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          acc[i][j] = fmaf(exp_sfu((av[i][j] + bv[j]) - cv[i]), gv[i], acc[i][j]);
+          acc[i][j] = fmaf(ex2_approx(fmaf(av[i][j] + bv[j], kLog2e, cv[i])), gv[i], acc[i][j]);
     }
     if (t + 1 < nt) {
-      lc.store(sc[cur ^ 1], LDR);
+      lc.store_scaled(sc[cur ^ 1], LDR, -kLog2e);
       lg.store(sg[cur ^ 1], LDR);
       lb.store(sb[cur ^ 1], LDC);
     }
@@ -157,7 +159,7 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __rest
   lc.load(cb, 1, N, tc.c0, 0, N, M, vec_c, pinf_f());
   lg.load(gb, 1, N, tc.c0, 0, N, M, vec_g, 0.f);
   la.store(sa[0], LDR);
-  lc.store(sc[0], LDC);
+  lc.store_scaled(sc[0], LDC, -kLog2e);
   lg.store(sg[0], LDC);
   __syncthreads();
 
@@ -178,11 +180,11 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __rest
       for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          acc[i][j] = fmaf(exp_sfu((xa[i] + bv[i][j]) - cv[j]), gv[j], acc[i][j]);
+          acc[i][j] = fmaf(ex2_approx(fmaf(xa[i] + bv[i][j], kLog2e, cv[j])), gv[j], acc[i][j]);
     }
     if (t + 1 < nt) {
       la.store(sa[cur ^ 1], LDR);
-      lc.store(sc[cur ^ 1], LDC);
+      lc.store_scaled(sc[cur ^ 1], LDC, -kLog2e);
       lg.store(sg[cur ^ 1], LDC);
     }
     __syncthreads();

@@ -230,6 +230,11 @@ __global__ void __launch_bounds__(NT) dense_log_fwd_kernel(const float* __restri
     // carrying BK*32 of them in registers across the two passes.
     asm volatile("" ::: "memory");
     // pass 2: accumulate exp(v - m)
+    // exp(v - m) = 2^(v*log2e - m*log2e): one FADD, one FFMA, one MUFU and one FADD per term
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) tmx[i][j] = -mx[i][j] * kLog2e;
 #pragma unroll 4
     for (int kk = 0; kk < BK; ++kk) {
       float x[8], y[4];
@@ -238,7 +243,7 @@ __global__ void __launch_bounds__(NT) dense_log_fwd_kernel(const float* __restri
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) sum[i][j] += exp_sfu((x[i] + y[j]) - mx[i][j]);
+        for (int j = 0; j < 4; ++j) sum[i][j] += ex2_approx(fmaf(x[i] + y[j], kLog2e, tmx[i][j]));
     }
     if (t + 1 < nt) {
       la.store(sx[cur ^ 1], LDX);
@@ -305,7 +310,7 @@ __global__ void __launch_bounds__(NT) dense_sample_pick_kernel(const float* __re
       const bool ok = m < M && n < N;
       total[i][j] = 0.f;
       pick[i][j] = 0;
-      lse[i][j] = ok ? __ldg(ob + (int64_t)m * N + n) : 0.f;
+      lse[i][j] = ok ? -kLog2e * __ldg(ob + (int64_t)m * N + n) : 0.f;  // -out * log2(e)
       r[i][j] = ok ? __ldg(ub + (int64_t)m * N + n) : 0.f;
     }
 
@@ -334,7 +339,7 @@ __global__ void __launch_bounds__(NT) dense_sample_pick_kernel(const float* __re
       for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float e = exp_sfu((x[i] + y[j]) - lse[i][j]);
+          const float e = ex2_approx(fmaf(x[i] + y[j], kLog2e, lse[i][j]));  // exp(a + b - out)
           const float nxt = total[i][j] + e;
           if (total[i][j] < r[i][j] && nxt > r[i][j]) pick[i][j] = k;
           total[i][j] = nxt;

@@ -57,6 +57,18 @@ struct TileLoader {
     }
   }
 
+  // store() after multiplying every element by `scale`
+  __device__ __forceinline__ void store_scaled(float* __restrict__ s, int LD, float scale) {
+#pragma unroll
+    for (int q = 0; q < NV; ++q) {
+      v[q].x *= scale;
+      v[q].y *= scale;
+      v[q].z *= scale;
+      v[q].w *= scale;
+    }
+    store(s, LD);
+  }
+
   // LD = pitch of the shared tile in floats (a multiple of 4).
   __device__ __forceinline__ void store(float* __restrict__ s, int LD) const {
 #pragma unroll

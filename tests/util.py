@@ -77,5 +77,13 @@ def assert_valid_sample(a, b, u, idx, tol=1e-5):
     hi = np.take_along_axis(cdf, idx[:, :, None, :], 2)[:, :, 0, :]
     lo = hi - np.take_along_axis(p, idx[:, :, None, :], 2)[:, :, 0, :]
     ok = (lo - tol <= u) & (u <= hi + tol)
-    none = (idx == 0) & ((u <= tol) | (u >= 1 - tol))
-    assert (ok | none).all(), "%d sampled indices do not bracket their uniform" % (~(ok | none)).sum()
+    # the strict double inequality also fails when the fp32 running sum lands exactly on u:
+    # u then sits on a CDF step, and the reference leaves index 0
+    on_step = np.abs(cdf - u[:, :, None, :]).min(2) <= tol
+    none = (idx == 0) & ((u <= tol) | (u >= 1 - tol) | on_step)
+    bad = ~(ok | none)
+    if bad.any():
+        w = np.argwhere(bad)[:4]
+        detail = ["%s idx=%d u=%.8f lo=%.8f hi=%.8f" % (tuple(i), idx[tuple(i)], u[tuple(i)], lo[tuple(i)],
+                                                      hi[tuple(i)]) for i in w]
+        raise AssertionError("%d sampled indices do not bracket their uniform: %s" % (bad.sum(), "; ".join(detail)))
