@@ -25,6 +25,13 @@ _SIGNATURES = {
     "gbmm_dense_backward_f32": ([_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
     "gbmm_band_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L, _P], _I),
     "gbmm_band_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P], _I),
+    "gbmm_logbmm_workspace_bytes": ([_I, _L, _L, _L, _L], _L),
+    "gbmm_logbmm_flag_count": ([_L, _L, _L], _L),
+    "gbmm_logbmm_forward_f32": ([_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
+    "gbmm_logbmm_backward_f32": ([_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
+    "gbmm_logbmm_check": ([_P, _P], _I),
+    "gbmm_profile_enable": ([_I], None),
+    "gbmm_profile_last_ms": ([_I], ctypes.c_float),
 }
 
 _lib = None
@@ -218,3 +225,55 @@ def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=Fa
                                            _ptr(part), _ptr(grad_a), _ptr(grad_b), B, n, _stream(a.device))
     _check(st, "gbmm_band_backward_f32")
     return [grad_a, grad_b] if both else [grad_a]
+
+
+# ---- factorised fast path of logbmm -----------------------------------------------------------
+
+def _workspace(nbytes, device):
+    return torch.empty((max(int(nbytes), 256),), dtype=torch.uint8, device=device)
+
+
+def logbmm_fast_forward(a, b, check=False):
+    """c = logbmm(a, b) by the factorised kernels.  Returns (out, rowmax, colmax, flags); the last
+    three are what `logbmm_fast_backward` needs.  Requires K > 0."""
+    _check_input(a, "a")
+    _check_input(b, "b")
+    if a.dim() != 3 or b.dim() != 3 or a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1]:
+        raise RuntimeError("expected a:(B,M,K) and b:(B,K,N), got %s and %s" % (tuple(a.shape), tuple(b.shape)))
+    B, M, K = a.shape
+    N = b.shape[2]
+    lib = load()
+    with torch.cuda.device(a.device):
+        out = torch.empty((B, M, N), dtype=a.dtype, device=a.device)
+        rowmax = torch.empty((B, M), dtype=a.dtype, device=a.device)
+        colmax = torch.empty((B, N), dtype=a.dtype, device=a.device)
+        flags = torch.empty((max(lib.gbmm_logbmm_flag_count(B, M, N), 1),), dtype=torch.int32, device=a.device)
+        nbytes = lib.gbmm_logbmm_workspace_bytes(0, B, M, K, N)
+        ws = _workspace(nbytes, a.device)
+        st = lib.gbmm_logbmm_forward_f32(_ptr(a), _ptr(b), _ptr(out), _ptr(rowmax), _ptr(colmax), _ptr(flags),
+                                         _ptr(ws), ws.numel(), B, M, K, N, _stream(a.device))
+        _check(st, "gbmm_logbmm_forward_f32")
+        if check:
+            _check(lib.gbmm_logbmm_check(_ptr(ws), _stream(a.device)), "gbmm_logbmm_forward_f32 (device)")
+    return out, rowmax, colmax, flags
+
+
+def logbmm_fast_backward(a, b, grad_output, out, rowmax, colmax, flags, check=False):
+    """(grad_a, grad_b) of logbmm by the factorised kernels, from what the fast forward saved."""
+    for x, name in ((a, "a"), (b, "b"), (grad_output, "grad_output"), (out, "out"), (rowmax, "rowmax"),
+                    (colmax, "colmax")):
+        _check_input(x, name)
+    B, M, K = a.shape
+    N = b.shape[2]
+    lib = load()
+    with torch.cuda.device(a.device):
+        grad_a = torch.empty_like(a)
+        grad_b = torch.empty_like(b)
+        ws = _workspace(lib.gbmm_logbmm_workspace_bytes(1, B, M, K, N), a.device)
+        st = lib.gbmm_logbmm_backward_f32(_ptr(a), _ptr(b), _ptr(grad_output), _ptr(out), _ptr(rowmax),
+                                          _ptr(colmax), _ptr(flags), _ptr(grad_a), _ptr(grad_b), _ptr(ws),
+                                          ws.numel(), B, M, K, N, _stream(a.device))
+        _check(st, "gbmm_logbmm_backward_f32")
+        if check:
+            _check(lib.gbmm_logbmm_check(_ptr(ws), _stream(a.device)), "gbmm_logbmm_backward_f32 (device)")
+    return grad_a, grad_b

@@ -1,0 +1,18 @@
+// Launchers shared between the dense translation units.
+#pragma once
+#include "common.cuh"
+
+namespace gbmm {
+
+// Exact (SFU) log-sum-exp forward restricted to the 128x128 result tiles whose entry in
+// flags[batch][ceil(M/128)][ceil(N/128)] is non-zero; flags == nullptr means every tile.
+int launch_log_fwd_flagged(const float* a, const float* b, float* out, const int* flags, int64_t B, int64_t M,
+                           int64_t K, int64_t N, cudaStream_t st);
+
+// Exact log backward restricted to the terms of flagged result tiles, ADDED to grad_a and
+// grad_b (either may be null).
+int launch_log_bwd_flagged(const float* a, const float* b, const float* c, const float* g, float* grad_a,
+                           float* grad_b, const int* flags, int64_t B, int64_t M, int64_t K, int64_t N,
+                           cudaStream_t st);
+
+}  // namespace gbmm

@@ -12,6 +12,7 @@
 //   grad_a[m,idx] += g[m,n] (* b[idx,n]),   grad_b[idx,n] += g[m,n] (* a[m,idx]),
 // accumulated in shared-memory rows/columns in ascending n (grad_a) and ascending m
 // (grad_b), the order of the reference's loops.  An index outside [0,K) routes nowhere.
+#include "dense.cuh"
 #include "tile.cuh"
 
 namespace gbmm {
@@ -32,6 +33,7 @@ struct TileCoord {
   }
 };
 
+template <bool ACCUMULATE>
 __device__ __forceinline__ void store_tile(float* __restrict__ dst, int64_t pitch, int rows, int cols,
                                            const TileCoord& tc, const Micro8x4& mt, const float (&acc)[8][4]) {
   const bool vec = aligned16(dst) && (pitch % 4 == 0);
@@ -41,23 +43,38 @@ __device__ __forceinline__ void store_tile(float* __restrict__ dst, int64_t pitc
     if (r >= rows) continue;
     const int cb = tc.c0 + mt.col(0);
     if (vec && cb + 3 < cols) {
-      *reinterpret_cast<float4*>(dst + (int64_t)r * pitch + cb) =
-          make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+      float4* p = reinterpret_cast<float4*>(dst + (int64_t)r * pitch + cb);
+      float4 v = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+      if (ACCUMULATE) {
+        const float4 old = *p;
+        v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+      }
+      *p = v;
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        if (cb + j < cols) dst[(int64_t)r * pitch + cb + j] = acc[i][j];
+        if (cb + j < cols) {
+          float* p = dst + (int64_t)r * pitch + cb + j;
+          *p = ACCUMULATE ? *p + acc[i][j] : acc[i][j];
+        }
     }
   }
 }
 
+// In FLAGGED mode (used behind the factorised fast path, dense_fast.cu) only the terms whose
+// (m,n) lies in a 128x128 result tile marked in `flags` are summed, and the sum is added to
+// what the fast kernels already wrote; a CTA with no marked tile in its strip returns at once.
+// flags is indexed [batch][m/128][n/128].
+
 // grad_a tile: rows m, columns k, reduction over n.
+template <bool FLAGGED>
 __global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __restrict__ a,
                                                              const float* __restrict__ b,
                                                              const float* __restrict__ c,
                                                              const float* __restrict__ g,
                                                              float* __restrict__ grad_a, int M, int K, int N,
-                                                             int tiles_r, int tiles_c) {
+                                                             int tiles_r, int tiles_c,
+                                                             const int* __restrict__ flags) {
   __shared__ __align__(16) float sc[2][BK * LDR];
   __shared__ __align__(16) float sg[2][BK * LDR];
   __shared__ __align__(16) float sb[2][BK * LDC];
@@ -69,6 +86,15 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __rest
   const float* gb = g + (int64_t)tc.bt * M * N;
   const bool vec_n = (N % 4 == 0);
   const bool vec_b = vec_n && aligned16(bb), vec_c = vec_n && aligned16(cb), vec_g = vec_n && aligned16(gb);
+  const int nt = (N + BK - 1) / BK;
+  constexpr int GRP = 128 / BK;  // reduction tiles per 128-wide flag tile
+  const int ngrp = FLAGGED ? (N + 127) / 128 : 1;
+  const int* frow = FLAGGED ? flags + ((int64_t)tc.bt * tiles_r + tc.r0 / 128) * ngrp : nullptr;
+  if (FLAGGED) {
+    bool any = false;
+    for (int q = 0; q < ngrp; ++q) any |= (__ldg(frow + q) != 0);
+    if (!any) return;
+  }
 
   float acc[8][4], av[8][4];
 #pragma unroll
@@ -82,54 +108,61 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __rest
 
   TileLoader<BR, BK, NT, true> lc, lg;
   TileLoader<BC, BK, NT, true> lb;
-  const int nt = (N + BK - 1) / BK;
   // c is staged as -c*log2(e), so that exp(a+b-c) = 2^((a+b)*log2e + staged): one FADD, one FFMA,
   // one MUFU and the accumulating FFMA per term.  Padding: c = +inf makes the weight 0 and g = 0
-  // removes the term
-  lc.load(cb, N, 1, tc.r0, 0, M, N, vec_c, pinf_f());
-  lg.load(gb, N, 1, tc.r0, 0, M, N, vec_g, 0.f);
-  lb.load(bb, N, 1, tc.c0, 0, K, N, vec_b, 0.f);
-  lc.store_scaled(sc[0], LDR, -kLog2e);
-  lg.store(sg[0], LDR);
-  lb.store(sb[0], LDC);
-  __syncthreads();
-
-  for (int t = 0; t < nt; ++t) {
-    const int cur = t & 1;
-    if (t + 1 < nt) {
-      lc.load(cb, N, 1, tc.r0, (t + 1) * BK, M, N, vec_c, pinf_f());
-      lg.load(gb, N, 1, tc.r0, (t + 1) * BK, M, N, vec_g, 0.f);
-      lb.load(bb, N, 1, tc.c0, (t + 1) * BK, K, N, vec_b, 0.f);
-    }
-#pragma unroll
-    for (int kk = 0; kk < BK; ++kk) {
-      float cv[8], gv[8], bv[4];
-      mt.load_x(sc[cur] + kk * LDR, LDR, cv);
-      mt.load_x(sg[cur] + kk * LDR, LDR, gv);
-      mt.load_y(sb[cur] + kk * LDC, bv);
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          acc[i][j] = fmaf(ex2_approx(fmaf(av[i][j] + bv[j], kLog2e, cv[i])), gv[i], acc[i][j]);
-    }
-    if (t + 1 < nt) {
-      lc.store_scaled(sc[cur ^ 1], LDR, -kLog2e);
-      lg.store(sg[cur ^ 1], LDR);
-      lb.store(sb[cur ^ 1], LDC);
-    }
+  // removes the term.
+  for (int grp = 0; grp < ngrp; ++grp) {
+    if (FLAGGED && __ldg(frow + grp) == 0) continue;
+    const int t_begin = FLAGGED ? grp * GRP : 0;
+    const int t_end = FLAGGED ? min(nt, t_begin + GRP) : nt;
+    if (t_begin >= t_end) continue;
+    lc.load(cb, N, 1, tc.r0, t_begin * BK, M, N, vec_c, pinf_f());
+    lg.load(gb, N, 1, tc.r0, t_begin * BK, M, N, vec_g, 0.f);
+    lb.load(bb, N, 1, tc.c0, t_begin * BK, K, N, vec_b, 0.f);
+    __syncthreads();  // the previous group's last tile is fully consumed
+    lc.store_scaled(sc[0], LDR, -kLog2e);
+    lg.store(sg[0], LDR);
+    lb.store(sb[0], LDC);
     __syncthreads();
+    for (int t = t_begin; t < t_end; ++t) {
+      const int cur = (t - t_begin) & 1;
+      if (t + 1 < t_end) {
+        lc.load(cb, N, 1, tc.r0, (t + 1) * BK, M, N, vec_c, pinf_f());
+        lg.load(gb, N, 1, tc.r0, (t + 1) * BK, M, N, vec_g, 0.f);
+        lb.load(bb, N, 1, tc.c0, (t + 1) * BK, K, N, vec_b, 0.f);
+      }
+#pragma unroll
+      for (int kk = 0; kk < BK; ++kk) {
+        float cv[8], gv[8], bv[4];
+        mt.load_x(sc[cur] + kk * LDR, LDR, cv);
+        mt.load_x(sg[cur] + kk * LDR, LDR, gv);
+        mt.load_y(sb[cur] + kk * LDC, bv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            acc[i][j] = fmaf(ex2_approx(fmaf(av[i][j] + bv[j], kLog2e, cv[i])), gv[i], acc[i][j]);
+      }
+      if (t + 1 < t_end) {
+        lc.store_scaled(sc[cur ^ 1], LDR, -kLog2e);
+        lg.store(sg[cur ^ 1], LDR);
+        lb.store(sb[cur ^ 1], LDC);
+      }
+      __syncthreads();
+    }
   }
-  store_tile(grad_a + (int64_t)tc.bt * M * K, K, M, K, tc, mt, acc);
+  store_tile<FLAGGED>(grad_a + (int64_t)tc.bt * M * K, K, M, K, tc, mt, acc);
 }
 
 // grad_b tile: rows k, columns n, reduction over m.
+template <bool FLAGGED>
 __global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __restrict__ a,
                                                              const float* __restrict__ b,
                                                              const float* __restrict__ c,
                                                              const float* __restrict__ g,
                                                              float* __restrict__ grad_b, int M, int K, int N,
-                                                             int tiles_r, int tiles_c) {
+                                                             int tiles_r, int tiles_c,
+                                                             const int* __restrict__ flags) {
   __shared__ __align__(16) float sa[2][BK * LDR];
   __shared__ __align__(16) float sc[2][BK * LDC];
   __shared__ __align__(16) float sg[2][BK * LDC];
@@ -141,6 +174,16 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __rest
   const float* gb = g + (int64_t)tc.bt * M * N;
   const bool vec_a = (K % 4 == 0) && aligned16(ab);
   const bool vec_c = (N % 4 == 0) && aligned16(cb), vec_g = (N % 4 == 0) && aligned16(gb);
+  const int nt = (M + BK - 1) / BK;
+  constexpr int GRP = 128 / BK;
+  const int ngrp = FLAGGED ? (M + 127) / 128 : 1;
+  const int fpitch = (N + 127) / 128;
+  const int* fcol = FLAGGED ? flags + (int64_t)tc.bt * ngrp * fpitch + tc.c0 / 128 : nullptr;
+  if (FLAGGED) {
+    bool any = false;
+    for (int q = 0; q < ngrp; ++q) any |= (__ldg(fcol + (int64_t)q * fpitch) != 0);
+    if (!any) return;
+  }
 
   float acc[8][4], bv[8][4];
 #pragma unroll
@@ -154,42 +197,47 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __rest
 
   TileLoader<BR, BK, NT, false> la;
   TileLoader<BC, BK, NT, false> lc, lg;
-  const int nt = (M + BK - 1) / BK;
-  la.load(ab, 1, K, tc.r0, 0, K, M, vec_a, 0.f);
-  lc.load(cb, 1, N, tc.c0, 0, N, M, vec_c, pinf_f());
-  lg.load(gb, 1, N, tc.c0, 0, N, M, vec_g, 0.f);
-  la.store(sa[0], LDR);
-  lc.store_scaled(sc[0], LDC, -kLog2e);
-  lg.store(sg[0], LDC);
-  __syncthreads();
-
-  for (int t = 0; t < nt; ++t) {
-    const int cur = t & 1;
-    if (t + 1 < nt) {
-      la.load(ab, 1, K, tc.r0, (t + 1) * BK, K, M, vec_a, 0.f);
-      lc.load(cb, 1, N, tc.c0, (t + 1) * BK, N, M, vec_c, pinf_f());
-      lg.load(gb, 1, N, tc.c0, (t + 1) * BK, N, M, vec_g, 0.f);
-    }
-#pragma unroll
-    for (int kk = 0; kk < BK; ++kk) {
-      float xa[8], cv[4], gv[4];
-      mt.load_x(sa[cur] + kk * LDR, LDR, xa);
-      mt.load_y(sc[cur] + kk * LDC, cv);
-      mt.load_y(sg[cur] + kk * LDC, gv);
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          acc[i][j] = fmaf(ex2_approx(fmaf(xa[i] + bv[i][j], kLog2e, cv[j])), gv[j], acc[i][j]);
-    }
-    if (t + 1 < nt) {
-      la.store(sa[cur ^ 1], LDR);
-      lc.store_scaled(sc[cur ^ 1], LDC, -kLog2e);
-      lg.store(sg[cur ^ 1], LDC);
-    }
+  for (int grp = 0; grp < ngrp; ++grp) {
+    if (FLAGGED && __ldg(fcol + (int64_t)grp * fpitch) == 0) continue;
+    const int t_begin = FLAGGED ? grp * GRP : 0;
+    const int t_end = FLAGGED ? min(nt, t_begin + GRP) : nt;
+    if (t_begin >= t_end) continue;
+    la.load(ab, 1, K, tc.r0, t_begin * BK, K, M, vec_a, 0.f);
+    lc.load(cb, 1, N, tc.c0, t_begin * BK, N, M, vec_c, pinf_f());
+    lg.load(gb, 1, N, tc.c0, t_begin * BK, N, M, vec_g, 0.f);
     __syncthreads();
+    la.store(sa[0], LDR);
+    lc.store_scaled(sc[0], LDC, -kLog2e);
+    lg.store(sg[0], LDC);
+    __syncthreads();
+    for (int t = t_begin; t < t_end; ++t) {
+      const int cur = (t - t_begin) & 1;
+      if (t + 1 < t_end) {
+        la.load(ab, 1, K, tc.r0, (t + 1) * BK, K, M, vec_a, 0.f);
+        lc.load(cb, 1, N, tc.c0, (t + 1) * BK, N, M, vec_c, pinf_f());
+        lg.load(gb, 1, N, tc.c0, (t + 1) * BK, N, M, vec_g, 0.f);
+      }
+#pragma unroll
+      for (int kk = 0; kk < BK; ++kk) {
+        float xa[8], cv[4], gv[4];
+        mt.load_x(sa[cur] + kk * LDR, LDR, xa);
+        mt.load_y(sc[cur] + kk * LDC, cv);
+        mt.load_y(sg[cur] + kk * LDC, gv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            acc[i][j] = fmaf(ex2_approx(fmaf(xa[i] + bv[i][j], kLog2e, cv[j])), gv[j], acc[i][j]);
+      }
+      if (t + 1 < t_end) {
+        la.store(sa[cur ^ 1], LDR);
+        lc.store_scaled(sc[cur ^ 1], LDC, -kLog2e);
+        lg.store(sg[cur ^ 1], LDC);
+      }
+      __syncthreads();
+    }
   }
-  store_tile(grad_b + (int64_t)tc.bt * K * N, N, K, N, tc, mt, acc);
+  store_tile<FLAGGED>(grad_b + (int64_t)tc.bt * K * N, N, K, N, tc, mt, acc);
 }
 
 // ------------------------------------------------------------------ index routing
@@ -280,6 +328,30 @@ __global__ void __launch_bounds__(32) route_grad_b_kernel(const float* __restric
 }  // namespace
 }  // namespace gbmm
 
+namespace gbmm {
+// Exact recomputation of the gradient terms of the result tiles marked in `flags`, added to
+// grad_a / grad_b (see dense.cuh).
+int launch_log_bwd_flagged(const float* a, const float* b, const float* c, const float* g, float* grad_a,
+                           float* grad_b, const int* flags, int64_t B, int64_t M, int64_t K, int64_t N,
+                           cudaStream_t st) {
+  const int m = (int)M, k = (int)K, n = (int)N;
+  if (grad_a) {
+    const int64_t tr = ceil_div(M, BR), tcn = ceil_div(K, BC), blocks = B * tr * tcn;
+    if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+    dense_log_bwd_a_kernel<true><<<(unsigned)blocks, NT, 0, st>>>(a, b, c, g, grad_a, m, k, n, (int)tr, (int)tcn,
+                                                                  flags);
+    if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+  }
+  if (grad_b) {
+    const int64_t tr = ceil_div(K, BR), tcn = ceil_div(N, BC), blocks = B * tr * tcn;
+    if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+    dense_log_bwd_b_kernel<true><<<(unsigned)blocks, NT, 0, st>>>(a, b, c, g, grad_b, m, k, n, (int)tr, (int)tcn,
+                                                                  flags);
+  }
+  return launch_status();
+}
+}  // namespace gbmm
+
 using namespace gbmm;
 
 extern "C" int gbmm_dense_backward_f32(int mode, const float* a, const float* b, const float* grad_out,
@@ -305,15 +377,15 @@ extern "C" int gbmm_dense_backward_f32(int mode, const float* a, const float* b,
     if (grad_a) {
       const int64_t tr = ceil_div(M, BR), tcn = ceil_div(K, BC), blocks = B * tr * tcn;
       if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
-      dense_log_bwd_a_kernel<<<(unsigned)blocks, NT, 0, st>>>(a, b, part, grad_out, grad_a, m, k, n, (int)tr,
-                                                              (int)tcn);
+      dense_log_bwd_a_kernel<false><<<(unsigned)blocks, NT, 0, st>>>(a, b, part, grad_out, grad_a, m, k, n,
+                                                                     (int)tr, (int)tcn, nullptr);
       if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
     }
     if (grad_b) {
       const int64_t tr = ceil_div(K, BR), tcn = ceil_div(N, BC), blocks = B * tr * tcn;
       if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
-      dense_log_bwd_b_kernel<<<(unsigned)blocks, NT, 0, st>>>(a, b, part, grad_out, grad_b, m, k, n, (int)tr,
-                                                              (int)tcn);
+      dense_log_bwd_b_kernel<false><<<(unsigned)blocks, NT, 0, st>>>(a, b, part, grad_out, grad_b, m, k, n,
+                                                                     (int)tr, (int)tcn, nullptr);
     }
     return launch_status();
   }

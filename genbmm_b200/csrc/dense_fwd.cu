@@ -16,6 +16,7 @@
 //       reference.
 //   sample : the log kernel followed by an inverse-CDF pass that keeps the reference's fp32
 //       running sum in ascending k and its strict double inequality.
+#include "dense.cuh"
 #include "tile.cuh"
 
 namespace gbmm {
@@ -165,10 +166,14 @@ __global__ void __launch_bounds__(NT) dense_log_fwd_kernel(const float* __restri
                                                            const float* __restrict__ b,
                                                            float* __restrict__ out,
                                                            float* __restrict__ maxes, int M, int K, int N,
-                                                           int tiles_m, int tiles_n) {
+                                                           int tiles_m, int tiles_n,
+                                                           const int* __restrict__ flags) {
   __shared__ __align__(16) float sx[2][BK * LDX];
   __shared__ __align__(16) float sy[2][BK * LDY];
   const TileCoord tc(tiles_m, tiles_n);
+  // Behind the factorised fast path only the 128x128 result tiles it marked are recomputed.
+  if (flags && __ldg(flags + ((int64_t)tc.bt * tiles_m + tc.m0 / 128) * ((N + 127) / 128) + tc.n0 / 128) == 0)
+    return;
   const Micro8x4 mt;
   const float* ab = a + (int64_t)tc.bt * M * K;
   const float* bb = b + (int64_t)tc.bt * K * N;
@@ -368,6 +373,18 @@ __global__ void __launch_bounds__(NT) dense_sample_pick_kernel(const float* __re
 }  // namespace
 }  // namespace gbmm
 
+namespace gbmm {
+// Exact log-sum-exp of the result tiles marked in `flags` (all tiles when flags is null).
+int launch_log_fwd_flagged(const float* a, const float* b, float* out, const int* flags, int64_t B, int64_t M,
+                           int64_t K, int64_t N, cudaStream_t st) {
+  const int64_t tiles_m = ceil_div(M, BM), tiles_n = ceil_div(N, BN), blocks = B * tiles_m * tiles_n;
+  if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  dense_log_fwd_kernel<<<(unsigned)blocks, NT, 0, st>>>(a, b, out, nullptr, (int)M, (int)K, (int)N, (int)tiles_m,
+                                                        (int)tiles_n, flags);
+  return launch_status();
+}
+}  // namespace gbmm
+
 using namespace gbmm;
 
 extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, const float* u, float* out,
@@ -389,7 +406,7 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
   const int m = (int)M, k = (int)K, n = (int)N, tm = (int)tiles_m, tn = (int)tiles_n;
   switch (mode) {
     case GBMM_MODE_LOG:
-      dense_log_fwd_kernel<<<grid, block, 0, st>>>(a, b, out, static_cast<float*>(aux), m, k, n, tm, tn);
+      dense_log_fwd_kernel<<<grid, block, 0, st>>>(a, b, out, static_cast<float*>(aux), m, k, n, tm, tn, nullptr);
       break;
     case GBMM_MODE_MAX:
       dense_max_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, static_cast<int*>(aux), m, k, n, tm, tn);
@@ -398,7 +415,7 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
       dense_max_fwd_kernel<true><<<grid, block, 0, st>>>(a, b, out, static_cast<int*>(aux), m, k, n, tm, tn);
       break;
     case GBMM_MODE_SAMPLE:
-      dense_log_fwd_kernel<<<grid, block, 0, st>>>(a, b, out, nullptr, m, k, n, tm, tn);
+      dense_log_fwd_kernel<<<grid, block, 0, st>>>(a, b, out, nullptr, m, k, n, tm, tn, nullptr);
       if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
       dense_sample_pick_kernel<<<grid, block, 0, st>>>(a, b, u, out, static_cast<int*>(aux), m, k, n, tm, tn);
       break;

@@ -11,6 +11,8 @@ Differences from the reference that a caller can observe:
     (the kernels are fp32);
   * inputs must be contiguous CUDA tensors, as in the reference (matmul_cuda.cpp:65-67).
 """
+import os
+
 import torch
 
 from . import _native
@@ -28,16 +30,29 @@ def _as_f32(x, name):
     raise RuntimeError("%s: dtype %s is not supported by the fp32 kernels" % (name, x.dtype))
 
 
+def _use_fast_log(M, K, N):
+    """The factorised kernels pay off once the product is big enough to amortise their four
+    small preparation kernels; GENBMM_B200_LOGBMM=exact|fast overrides the size rule."""
+    mode = os.environ.get("GENBMM_B200_LOGBMM", "auto")
+    if K == 0 or M == 0 or N == 0 or mode == "exact":
+        return False
+    return mode == "fast" or M * K * N >= 128 * 128 * 64
+
+
 class LogMatMulBack(torch.autograd.Function):
     """First-order gradients of logbmm as a differentiable node (genmul.py:11-24).
 
-    forward returns (grad_a, grad_b) in one call.
+    forward returns (grad_a, grad_b) in one call.  `aux` is None after the exact forward, or
+    the (rowmax, colmax, flags) triple of the factorised forward.
     """
 
     @staticmethod
-    def forward(ctx, a, b, grad_out, part):
+    def forward(ctx, a, b, grad_out, part, aux):
         ctx.save_for_backward(a, b, grad_out, part)
-        grad_a, grad_b = _native.backward(a, b, grad_out, part, None, _native.MODE_LOG)
+        if aux is None:
+            grad_a, grad_b = _native.backward(a, b, grad_out, part, None, _native.MODE_LOG)
+        else:
+            grad_a, grad_b = _native.logbmm_fast_backward(a, b, grad_out, part, *aux)
         return grad_a, grad_b
 
     @staticmethod
@@ -50,7 +65,12 @@ class LogMatMul(torch.autograd.Function):
     @staticmethod
     def forward(ctx, a, b):
         a32, b32 = _as_f32(a, "a"), _as_f32(b, "b")
-        out, _ = _native.forward(a32, b32, _native.MODE_LOG, want_maxes=False)
+        ctx.aux = None
+        if a32.dim() == 3 and b32.dim() == 3 and _use_fast_log(a32.shape[1], a32.shape[2], b32.shape[-1]):
+            out, rowmax, colmax, flags = _native.logbmm_fast_forward(a32, b32)
+            ctx.aux = (rowmax, colmax, flags)
+        else:
+            out, _ = _native.forward(a32, b32, _native.MODE_LOG, want_maxes=False)
         ctx.save_for_backward(a32, b32, out)
         ctx.dtypes = (a.dtype, b.dtype)
         return out.to(a.dtype)
@@ -58,7 +78,7 @@ class LogMatMul(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         a, b, out = ctx.saved_tensors
-        grad_a, grad_b = LogMatMulBack.apply(a, b, grad_output.contiguous().float(), out)
+        grad_a, grad_b = LogMatMulBack.apply(a, b, grad_output.contiguous().float(), out, ctx.aux)
         return grad_a.to(ctx.dtypes[0]), grad_b.to(ctx.dtypes[1])
 
 

@@ -109,6 +109,42 @@ int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_ld,
                            float* grad_a, float* grad_b,
                            int64_t B, int64_t n, void* stream);
 
+/*
+ * Factorised log-semiring product (fast path of logbmm).  Same result as
+ * gbmm_dense_forward_f32(GBMM_MODE_LOG, ...) / gbmm_dense_backward_f32 within fp32 rounding,
+ * computed as ordinary fp32 matrix products of exponentiated operands
+ * (c = rowmax + colmax + log(exp(a - rowmax) @ exp(b - colmax)), the formulation sketched in
+ * the reference's commented einsum, genmul.py:45-47), with the exact kernels re-run on the
+ * 128x128 result tiles where the factorisation would underflow.  They stand in for the same
+ * reference functions as the dense entry points above (matmul_cuda.cpp:69-92).
+ *
+ * Scratch: the caller provides `workspace` (256-byte aligned, at least
+ * gbmm_logbmm_workspace_bytes(backward, B, M, K, N) bytes; contents need not be preserved
+ * between calls) and three small tensors that forward fills and backward reads:
+ * rowmax:(B,M), colmax:(B,N) and flags: gbmm_logbmm_flag_count(B, M, N) int32.
+ * K must be > 0 (and M, N > 0 for backward); use the dense entry points otherwise.
+ */
+int64_t gbmm_logbmm_workspace_bytes(int backward, int64_t B, int64_t M, int64_t K, int64_t N);
+int64_t gbmm_logbmm_flag_count(int64_t B, int64_t M, int64_t N);
+int gbmm_logbmm_forward_f32(const float* a, const float* b, float* out, float* rowmax, float* colmax,
+                            int32_t* flags, void* workspace, int64_t workspace_bytes,
+                            int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+int gbmm_logbmm_backward_f32(const float* a, const float* b, const float* grad_out, const float* out,
+                             const float* rowmax, const float* colmax, const int32_t* flags,
+                             float* grad_a, float* grad_b, void* workspace, int64_t workspace_bytes,
+                             int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+/* Synchronises the stream and reports whether a kernel of the fast path gave up on a bounded
+ * wait for a TMA copy (GBMM_ERR_LAUNCH; its outputs are then invalid).  `workspace` is the one
+ * passed to the call being checked.  Diagnostic; not needed in normal operation. */
+int gbmm_logbmm_check(const void* workspace, void* stream);
+
+/* Diagnostic timing of the fast path's product kernels (no counterpart in the reference).
+ * While enabled, each gbmm_logbmm_* call brackets its product launch with CUDA events on its
+ * stream; gbmm_profile_last_ms(which) waits for the latest bracket (which = 0 forward product,
+ * 1 grad_a product, 2 grad_b product) and returns milliseconds, or -1.  Not thread-safe. */
+void gbmm_profile_enable(int on);
+float gbmm_profile_last_ms(int which);
+
 #ifdef __cplusplus
 }
 #endif

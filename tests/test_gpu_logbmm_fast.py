@@ -1,0 +1,118 @@
+"""The factorised (TMA-fed FP32 product) path of logbmm against the oracle, the exact path and
+the cases its guard exists for."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from util import assert_close
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(3, 7, 9, 8), (2, 33, 17, 65), (2, 130, 70, 67), (1, 128, 128, 64), (2, 129, 257, 130),
+          (1, 256, 512, 384), (2, 5, 1, 3), (1, 1, 1, 1), (1, 300, 40, 5)]
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from genbmm_b200 import _native
+    return _native
+
+
+def fast_fwd_bwd(nat, a, b, g):
+    ad, bd, gd = a.cuda(), b.cuda(), g.cuda()
+    out, rowmax, colmax, flags = nat.logbmm_fast_forward(ad, bd, check=True)
+    ga, gb = nat.logbmm_fast_backward(ad, bd, gd, out, rowmax, colmax, flags, check=True)
+    return out, ga, gb, flags
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_fast_path_matches_oracle(nat, shape):
+    B, M, K, N = shape
+    gen = torch.Generator().manual_seed(sum(shape))
+    a, b = torch.randn(B, M, K, generator=gen), torch.randn(B, K, N, generator=gen)
+    g = torch.randn(B, M, N, generator=gen)
+    out, ga, gb, flags = fast_fwd_bwd(nat, a, b, g)
+    want, maxes = oracle.dense_fwd(0, a, b, dtype=np.float64)
+    dA, dB = oracle.dense_bwd(0, a, b, g, want, maxes, dtype=np.float64)
+    assert int(flags.sum()) == 0          # well-conditioned inputs never need the guard
+    assert_close(out, want, what="fwd")
+    assert_close(ga, dA, 1e-5, 5e-6, what="grad_a")
+    assert_close(gb, dB, 1e-5, 5e-6, what="grad_b")
+    # and agrees with the exact SFU path
+    exact, _ = nat.forward(a.cuda(), b.cuda(), 0)
+    assert torch.allclose(out, exact, rtol=1e-5, atol=2e-6)
+
+
+def test_guard_recomputes_underflowing_tiles(nat):
+    """Row and column supports that do not meet: row maximum + column maximum overshoots the true
+    maximum by hundreds of nats, the factorised sum underflows, the tile is flagged and redone."""
+    gen = torch.Generator().manual_seed(1)
+    B, M, K, N = 2, 200, 96, 260
+    a, b = torch.randn(B, M, K, generator=gen), torch.randn(B, K, N, generator=gen)
+    g = torch.rand(B, M, N, generator=gen)
+    a[:, :60, :48] -= 400.0      # rows 0..59 live on k >= 48 ...
+    b[:, 48:, :70] -= 400.0      # ... columns 0..69 live on k < 48
+    out, ga, gb, flags = fast_fwd_bwd(nat, a, b, g)
+    nflag = int(flags.sum())
+    assert 0 < nflag < flags.numel()      # some tiles take the exact kernels, some the fast ones
+    want, maxes = oracle.dense_fwd(0, a, b, dtype=np.float64)
+    dA, dB = oracle.dense_bwd(0, a, b, g, want, maxes, dtype=np.float64)
+    # results near -400 carry fp32 spacing 3e-5, and the weights exp(a+b-c) inherit it
+    assert_close(out, want, 1e-5, 1e-5, what="fwd")
+    assert_close(ga, dA, 3e-4, 1e-5, what="grad_a")
+    assert_close(gb, dB, 3e-4, 1e-5, what="grad_b")
+    # the exact path, given the same inputs, agrees to the same tolerance
+    ea, eb = nat.backward(a.cuda(), b.cuda(), g.cuda(), out, None, 0)
+    assert torch.allclose(ga, ea, rtol=3e-4, atol=1e-5) and torch.allclose(gb, eb, rtol=3e-4, atol=1e-5)
+
+
+def test_guard_with_semiring_zero_fills(nat):
+    """-1e9 fills (the usual semiring zero): forward values, flagged or not, match the oracle."""
+    gen = torch.Generator().manual_seed(2)
+    B, M, K, N = 2, 200, 96, 260
+    a, b = torch.randn(B, M, K, generator=gen), torch.randn(B, K, N, generator=gen)
+    a[:, 150:, :] = -1e9         # fully masked rows
+    a[:, :40, ::2] = -1e9        # half of the reduction masked
+    b[:, 1::2, :40] = -1e9       # the other half masked for these columns: nothing survives
+    b[:, :, 200:] -= 1e9
+    out, _, _, flags = nat.logbmm_fast_forward(a.cuda(), b.cuda(), check=True)
+    assert int(flags.sum()) > 0
+    want, _ = oracle.dense_fwd(0, a, b)
+    assert_close(out, want, 1e-5, 1e-4, what="fwd")
+
+
+def test_guard_keeps_the_reference_floor(nat):
+    """Everything below the reference's -1e9 floor gives -inf, as matmul_cuda_kernel.cu:31-43 does."""
+    a = torch.full((1, 130, 64), -3e9)
+    b = torch.zeros(1, 64, 140)
+    a[0, 5, :] = 0.25
+    out, _, _, flags = nat.logbmm_fast_forward(a.cuda(), b.cuda(), check=True)
+    want, _ = oracle.dense_fwd(0, a, b)
+    assert int(flags.sum()) > 0
+    assert torch.isinf(out[0, 0]).all() and np.isinf(want[0, 0]).all()
+    assert_close(out[0, 5], want[0, 5])
+    # rows of -inf
+    a = torch.randn(1, 40, 64)
+    a[0, 3] = float("-inf")
+    b = torch.randn(1, 64, 50)
+    out, _, _, _ = nat.logbmm_fast_forward(a.cuda(), b.cuda(), check=True)
+    want, _ = oracle.dense_fwd(0, a, b, dtype=np.float64)
+    assert_close(out, want)
+
+
+def test_autograd_uses_fast_path_for_large_products(monkeypatch):
+    import genbmm_b200 as gb
+    gen = torch.Generator().manual_seed(3)
+    a, b = torch.randn(2, 192, 160, generator=gen), torch.randn(2, 160, 136, generator=gen)
+    g = torch.rand(2, 192, 136, generator=gen)
+    res = {}
+    for mode in ("fast", "exact"):
+        monkeypatch.setenv("GENBMM_B200_LOGBMM", mode)
+        ad, bd = a.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+        c = gb.logbmm(ad, bd)
+        res[mode] = (c.detach(),) + torch.autograd.grad(c, (ad, bd), g.cuda())
+    for x, y in zip(res["fast"], res["exact"]):
+        assert torch.allclose(x, y, rtol=1e-5, atol=5e-6)
+    want, maxes = oracle.dense_fwd(0, a, b, dtype=np.float64)
+    assert_close(res["fast"][0], want)
