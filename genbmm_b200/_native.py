@@ -30,6 +30,9 @@ _SIGNATURES = {
     "gbmm_logbmm_forward_f32": ([_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
     "gbmm_logbmm_backward_f32": ([_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
     "gbmm_logbmm_check": ([_P, _P], _I),
+    "gbmm_logbmm_forward_noalloc_max_bytes": ([], _L),
+    "gbmm_logbmm_forward_noalloc_need_bytes": ([_L, _L, _L, _L], _L),
+    "gbmm_logbmm_forward_noalloc_f32": ([_P, _P, _P, _L, _L, _L, _L, _P], _I),
     "gbmm_profile_enable": ([_I], None),
     "gbmm_profile_last_ms": ([_I], ctypes.c_float),
 }

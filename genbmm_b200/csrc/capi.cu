@@ -8,6 +8,7 @@ extern "C" const char* gbmm_status_string(int status) {
     case GBMM_ERR_UNSUPPORTED: return "size not supported";
     case GBMM_ERR_LAUNCH: return "CUDA launch failed";
     case GBMM_ERR_DEVICE: return "no usable CUDA device";
+    case GBMM_ERR_SCRATCH_LIMIT: return "problem exceeds the built-in scratch of the no-allocation entry point";
     default: return "unknown status";
   }
 }

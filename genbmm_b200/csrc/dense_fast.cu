@@ -431,3 +431,92 @@ extern "C" float gbmm_profile_last_ms(int which) {
   if (cudaEventElapsedTime(&ms, g_events[which][0], g_events[which][1]) != cudaSuccess) return -1.f;
   return ms;
 }
+
+// ------------------------------------------------------------------ forward without allocation
+// Some callers may not allocate device memory at the point where they need a product: code
+// running inside a memory-pool region whose owner forbids new reservations, a real-time loop
+// that must not touch the driver's allocator because its latency is unbounded, or a host
+// framework that hands the operator fixed input/output buffers and nothing else.  For them the
+// scratch of the factorised forward lives in this fixed device array instead of a
+// caller-provided workspace.  It costs kNoAllocBytes of device memory on every GPU that loads
+// the library, until the process exits, so it is kept small; problems that need more are
+// rejected.
+constexpr int64_t kNoAllocBytes = 32LL << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_noalloc_scratch on the current device.  In host code the array's name
+// is only a handle for the runtime, not an address a kernel can use, so the address is asked
+// for once per device (with that device current) and remembered.
+int noalloc_scratch(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return GBMM_ERR_DEVICE;
+  void* p = g_noalloc_ptr[dev];
+  if (!p) {
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return GBMM_ERR_DEVICE;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = p;
+  return GBMM_OK;
+}
+}  // namespace
+
+extern "C" int64_t gbmm_logbmm_forward_noalloc_max_bytes(void) { return kNoAllocBytes; }
+
+extern "C" int64_t gbmm_logbmm_forward_noalloc_need_bytes(int64_t B, int64_t M, int64_t K, int64_t N) {
+  if (bad_dims(B, M, K, N)) return -1;
+  const int64_t floats = 64 + pad64(B * K * pad4(M)) + pad64(B * K * pad4(N)) + pad64(B * M) + pad64(B * N) +
+                         pad64(B * ceil_div(M, GI) * ceil_div(N, GJ));
+  return floats * (int64_t)sizeof(float);
+}
+
+extern "C" int gbmm_logbmm_forward_noalloc_f32(const float* a, const float* b, float* out, int64_t B, int64_t M,
+                                               int64_t K, int64_t N, void* stream) {
+  if (bad_dims(B, M, K, N)) return GBMM_ERR_INVALID_ARG;
+  if (B == 0 || M == 0 || N == 0) return GBMM_OK;
+  if (K == 0) return GBMM_ERR_UNSUPPORTED;
+  if (!a || !b || !out) return GBMM_ERR_INVALID_ARG;
+  if (big_dims(M, K, N)) return GBMM_ERR_UNSUPPORTED;
+  if (gbmm_logbmm_forward_noalloc_need_bytes(B, M, K, N) > kNoAllocBytes) return GBMM_ERR_SCRATCH_LIMIT;
+  void* base = nullptr;
+  int rc = noalloc_scratch(&base);
+  if (rc != GBMM_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* cur = static_cast<float*>(base);
+  int* error = reinterpret_cast<int*>(carve(cur, 64));
+  float* eat = carve(cur, B * K * pad4(M));
+  float* eb = carve(cur, B * K * pad4(N));
+  float* rowmax = carve(cur, B * M);
+  float* colmax = carve(cur, B * N);
+  int* flags = reinterpret_cast<int*>(carve(cur, B * ceil_div(M, GI) * ceil_div(N, GJ)));
+  // the array keeps whatever the previous call left: the error word is the one thing that
+  // must start at zero; everything else is fully rewritten before it is read
+  if (cudaMemsetAsync(error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
+
+  rowmax_kernel<<<(unsigned)ceil_div(B * M, 8), 256, 0, st>>>(a, rowmax, B * M, (int)K);
+  const int64_t tn = ceil_div(N, 32);
+  colmax_kernel<<<(unsigned)(B * tn), 256, 0, st>>>(b, colmax, (int)K, (int)N, (int)tn);
+  if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+  rc = launch_transform<0>(a, rowmax, nullptr, nullptr, nullptr, nullptr, eat, B, M, K, st);
+  if (rc != GBMM_OK) return rc;
+  rc = launch_transform<1>(b, colmax, nullptr, nullptr, nullptr, eb, nullptr, B, K, N, st);
+  if (rc != GBMM_OK) return rc;
+
+  CUtensorMap mx, my;
+  if (!make_map_3d(&mx, eat, B, K, M, pad4(M), GK, GI) || !make_map_3d(&my, eb, B, K, N, pad4(N), GK, GJ))
+    return GBMM_ERR_LAUNCH;
+  const int64_t ti = ceil_div(M, GI), tj = ceil_div(N, GJ), blocks = B * ti * tj;
+  if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  const size_t smem = sizeof(GemmSmem) + 128;
+  if (cudaFuncSetAttribute(sgemm_tn_kernel<EPI_LOG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return GBMM_ERR_LAUNCH;
+  EpiParams ep{out, rowmax, colmax, nullptr, flags, error};
+  sgemm_tn_kernel<EPI_LOG><<<(unsigned)blocks, GNT, smem, st>>>(mx, my, ep, (int)K, (int)M, (int)N, (int)ti,
+                                                                (int)tj);
+  if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+  return launch_log_fwd_flagged(a, b, out, flags, B, M, K, N, st);
+}

@@ -28,6 +28,7 @@ extern "C" {
 #define GBMM_ERR_UNSUPPORTED 2  /* size beyond what the kernels index (e.g. a dimension >= 2^31) */
 #define GBMM_ERR_LAUNCH 3       /* the CUDA runtime refused a launch (see cudaGetLastError) */
 #define GBMM_ERR_DEVICE 4       /* not an sm_100 device, or no device */
+#define GBMM_ERR_SCRATCH_LIMIT 5 /* problem needs more than the built-in scratch of a no-allocation entry point */
 
 /* semiring selectors — the integer `mode` of the reference
  * (dense: matmul_cuda_kernel.cu:487-542; banded: banded_cuda_kernel.cu:42-98) */
@@ -137,6 +138,38 @@ int gbmm_logbmm_backward_f32(const float* a, const float* b, const float* grad_o
  * wait for a TMA copy (GBMM_ERR_LAUNCH; its outputs are then invalid).  `workspace` is the one
  * passed to the call being checked.  Diagnostic; not needed in normal operation. */
 int gbmm_logbmm_check(const void* workspace, void* stream);
+
+/*
+ * logbmm forward for callers that cannot allocate device memory.  (No counterpart in the
+ * reference, whose every entry point allocates its outputs with torch.)
+ *
+ * Who needs it: a caller that must not call cudaMalloc where it needs the product — e.g. it
+ * runs inside a region whose memory owner forbids new reservations, it sits in a latency-bound
+ * loop where the allocator's unbounded cost is unacceptable, or its host framework gives an
+ * operator fixed input and output buffers and no workspace.  Such a caller cannot provide the
+ * workspace, rowmax, colmax and flags that gbmm_logbmm_forward_f32 asks for.
+ *
+ * What it does: the same computation and result as gbmm_logbmm_forward_f32 (out = log sum_k
+ * exp(a + b)); the caller passes only a, b and out.  All scratch lives in one fixed device
+ * array inside the library, gbmm_logbmm_forward_noalloc_max_bytes() = 32 MiB, which every GPU
+ * that loads the library holds until the process exits.  The call allocates and frees
+ * nothing, on the device or through any library.
+ *
+ * Limits and rules:
+ *  - gbmm_logbmm_forward_noalloc_need_bytes(B, M, K, N) must not exceed the maximum, else the
+ *    call returns GBMM_ERR_SCRATCH_LIMIT and launches nothing (roughly 4*B*K*(M+N) bytes:
+ *    e.g. up to three 1024x1024x1024 products per call).  K must be > 0.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current); make that first call outside any stream capture.
+ *  - All calls on a device share the array.  It keeps the previous call's contents; the call
+ *    clears the one word that must start at zero and rewrites the rest before reading it.
+ *    Two calls whose kernels can overlap on the GPU (different streams, no ordering between
+ *    them) race on the array and give wrong results: order them.
+ */
+int64_t gbmm_logbmm_forward_noalloc_max_bytes(void);
+int64_t gbmm_logbmm_forward_noalloc_need_bytes(int64_t B, int64_t M, int64_t K, int64_t N);
+int gbmm_logbmm_forward_noalloc_f32(const float* a, const float* b, float* out,
+                                    int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
 
 /* Diagnostic timing of the fast path's product kernels (no counterpart in the reference).
  * While enabled, each gbmm_logbmm_* call brackets its product launch with CUDA events on its
