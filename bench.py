@@ -166,7 +166,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=16, help="1024^3 problems per GPU per step")
+    ap.add_argument("--batch", type=int, default=32, help="1024^3 problems per GPU per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -225,7 +225,6 @@ def main():
         step_log()
     stop.record()
     sync()
-    clocks = sampler.stop()
     t_log = torch.tensor([start.elapsed_time(stop) / 1e3], device=dev)
     if dist is not None:
         dist.all_reduce(t_log, op=dist.ReduceOp.MAX)
@@ -259,6 +258,14 @@ def main():
     t_e2e = float(t_e2e.item())
     h2d = 2 * B * SIZE * SIZE * 4
     d2h = 2 * B * SIZE * SIZE * 4 + 4
+    # extend the load until nvidia-smi (100 ms period) has seen it for about a second, so that the
+    # clock record covers a sustained run of the same step
+    t_end = time.perf_counter() + 1.0
+    while time.perf_counter() < t_end:
+        for _ in range(20):
+            step_log()
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
 
     # ---- per-kernel durations for the roofline (this rank's GPU) ---------------------------
     # The step is dominated by the three TMA-fed FP32 products of the factorised path (forward,

@@ -130,20 +130,25 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
       val[j] = best[i][j];
       ind[j] = -1;
       if (n < N && cid[i][j] >= 0) {
+        // all loads of the tile are issued before any is used; the scan runs from the last k
+        // down, so the lowest matching k is the assignment that sticks
         const int k0 = cid[i][j] * BK;
-        const int k1 = min(k0 + BK, K);
-        const float* ap = ab + (int64_t)m * K;
-        const float* bp = bb + n;
-#pragma unroll 1
-        for (int k = k0; k < k1; ++k) {
-          const float x = __ldg(ap + k), y = __ldg(bp + (int64_t)k * N);
-          const float v = MUL ? __fmul_rn(x, y) : __fadd_rn(x, y);
-          if (v == best[i][j]) {
-            val[j] = v;
-            ind[j] = k;
-            break;
-          }
+        const float* ap = ab + (int64_t)m * K + k0;
+        const float* bp = bb + (int64_t)k0 * N + n;
+        float v[BK];
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+          const bool ok = k0 + kk < K;
+          const float x = ok ? __ldg(ap + kk) : nan_f();
+          const float y = ok ? __ldg(bp + (int64_t)kk * N) : 0.f;
+          v[kk] = MUL ? __fmul_rn(x, y) : __fadd_rn(x, y);
         }
+#pragma unroll
+        for (int kk = BK - 1; kk >= 0; --kk)
+          if (v[kk] == best[i][j]) {
+            val[j] = v[kk];
+            ind[j] = k0 + kk;
+          }
       }
     }
     const int nb = tc.n0 + mt.col(0);
