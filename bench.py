@@ -113,9 +113,21 @@ def cpu_logbmm_sample(rows, chunk, repeats=1):
     return macs / best, best, torch.get_num_threads()
 
 
+def host_threads():
+    """All host threads this process may use (torchrun pins OMP_NUM_THREADS=1 per rank; undo that
+    for the single rank that runs the CPU arm)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
+    host_threads()
     rows, chunk = 512, 64
     for _ in range(args.warmup):
         cpu_logbmm_sample(chunk, chunk)
@@ -333,6 +345,7 @@ def main():
                  / (t_max / args.steps)},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        host_threads()
         value, secs, threads = cpu_logbmm_sample(512, 64)
         line["cpu_baseline"] = {
             "value": value, "unit": "MAC/s", "cores": threads, "kind": "port",

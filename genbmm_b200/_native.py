@@ -23,6 +23,7 @@ _SIGNATURES = {
     "gbmm_abi_version": ([], _I),
     "gbmm_dense_forward_f32": ([_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
     "gbmm_dense_backward_f32": ([_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
+    "gbmm_dense_backbackward_f32": ([_P] * 9 + [_L] * 4 + [_P], _I),
     "gbmm_band_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L, _P], _I),
     "gbmm_band_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P], _I),
     "gbmm_logbmm_workspace_bytes": ([_I, _L, _L, _L, _L], _L),
@@ -164,6 +165,32 @@ def backward(a, b, grad_output, part, maxes, mode):
                                             _ptr(grad_a), _ptr(grad_b), B, M, K, N, _stream(a.device))
     _check(st, "gbmm_dense_backward_f32")
     return [grad_a, grad_b]
+
+
+def backbackward(a, b, grad_output, part, maxes, grad_out_a, mode=0, grad_out_b=None):
+    """`_genbmm.backbackward(a, b, grad_output, part, maxes, grad_out_a, mode)` -> [grad_a, grad_b,
+    grad_grad] for the log product (mode 0 only, as in the reference, matmul_cuda_kernel.cu:583).
+    `grad_out_a` / `grad_out_b` are the cotangents of the first-order grad_a / grad_b (the reference
+    has the first only); `maxes` is accepted for signature compatibility and not read."""
+    if mode != MODE_LOG:
+        raise RuntimeError("backbackward is defined for mode 0 (log) only")
+    for x, name in ((a, "a"), (b, "b"), (grad_output, "grad_output"), (part, "part")):
+        _check_input(x, name)
+    B, M, K = a.shape
+    N = b.shape[2]
+    with torch.cuda.device(a.device):
+        h_a = torch.zeros_like(a) if grad_out_a is None else grad_out_a.contiguous()
+        h_b = torch.zeros_like(b) if grad_out_b is None else grad_out_b.contiguous()
+        _check_input(h_a, "grad_out_a")
+        _check_input(h_b, "grad_out_b")
+        d_a, d_b, d_g = torch.empty_like(a), torch.empty_like(b), torch.empty_like(grad_output)
+        if min(B, M, K, N) == 0:
+            return [d_a.zero_(), d_b.zero_(), d_g.zero_()]
+        st = load().gbmm_dense_backbackward_f32(_ptr(a), _ptr(b), _ptr(grad_output), _ptr(part), _ptr(h_a),
+                                                _ptr(h_b), _ptr(d_a), _ptr(d_b), _ptr(d_g), B, M, K, N,
+                                                _stream(a.device))
+    _check(st, "gbmm_dense_backbackward_f32")
+    return [d_a, d_b, d_g]
 
 
 def _check_band(a, a_lu, a_lb, b, b_lu, b_lb):

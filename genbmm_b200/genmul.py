@@ -57,8 +57,11 @@ class LogMatMulBack(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, h_a, h_b):
-        raise NotImplementedError(
-            "genbmm_b200.logbmm: second-order gradients (create_graph=True) are not built yet")
+        a, b, grad_out, part = ctx.saved_tensors
+        d_a, d_b, d_g = _native.backbackward(a, b, grad_out, part, None,
+                                             None if h_a is None else h_a.float(), 0,
+                                             None if h_b is None else h_b.float())
+        return d_a, d_b, d_g, None, None
 
 
 class LogMatMul(torch.autograd.Function):

@@ -80,6 +80,20 @@ int gbmm_dense_backward_f32(int mode, const float* a, const float* b, const floa
                             int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
 
 /*
+ * Dense log-semiring second-order terms.  Replaces `_genbmm.backbackward(a, b, grad_output, part,
+ * maxes, grad_out_a, 0)` — matmul_backbackward, matmul_cuda.cpp:94-110 -> matmul_cuda_backbackward,
+ * matmul_cuda_kernel.cu:547-622 — extended to the cotangents of both first-order gradients:
+ * for L = <grad_a, h_a> + <grad_b, h_b> it fills d_a = dL/da:(B,M,K), d_b = dL/db:(B,K,N) and
+ * d_grad_out = dL/dgrad_output:(B,M,N).  part = the forward's out.  (The reference's entry takes
+ * h_a only and reaches h_b through a second call on transposed copies; pass zeros for an absent
+ * cotangent.)  All sizes must be > 0.
+ */
+int gbmm_dense_backbackward_f32(const float* a, const float* b, const float* grad_out, const float* part,
+                                const float* h_a, const float* h_b,
+                                float* d_a, float* d_b, float* d_grad_out,
+                                int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+
+/*
  * Banded forward.  Replaces `_genbmm.forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode)`
  * — banded_forward, matmul_cuda.cpp:112-123 -> banded_cuda_forward,
  * banded_cuda_kernel.cu:354-402.

@@ -214,3 +214,22 @@ def expr_fwd_bwd(mode, a, b, g=None, chunk_bytes=1 << 30):
         gas.append(ga)
         gbs.append(gb)
     return torch.cat(cs), torch.cat(gas), torch.cat(gbs)
+
+
+# --------------------------------------------------------------------------------------------
+# Linear-chain CRF (benchmark configuration 4): left-to-right semiring products in float64 with
+# autograd for the edge marginals.  The reference has no such routine; this restates the
+# configuration's definition (chain product of the potentials, logZ = logsumexp of its entries).
+# --------------------------------------------------------------------------------------------
+
+def crf_log_partition(pot):
+    """(logZ, marginals) for torch CPU potentials pot:(B, L, C, C), in float64, sequentially."""
+    import torch
+
+    pot = pot.detach().double().requires_grad_(True)
+    p = pot[:, 0]
+    for t in range(1, pot.shape[1]):
+        p = (p.unsqueeze(-1) + pot[:, t].unsqueeze(-3)).logsumexp(-2)
+    logz = p.flatten(1).logsumexp(1)
+    grad, = torch.autograd.grad(logz.sum(), pot)
+    return logz.detach(), grad

@@ -262,3 +262,38 @@ def test_half_inputs_round_trip(gb):
     assert c.dtype == torch.float16
     want, _ = oracle.dense_fwd(0, a.float().cpu(), b.float().cpu(), dtype=np.float64)
     assert_close(c.float(), want, 2e-3, 2e-3)
+
+
+@pytest.mark.parametrize("ci", [0, 1, 2, 3])
+def test_logbmm_second_order_matches_reference_fixture(gb, golden, ci):
+    """genbmm/test_cuda.py:30-42: grad of (grad_a, grad_b) w.r.t. (a, b, back); the reference's own
+    test accepts rtol 1e-2, the fixture (float64 autograd of the dense expression) is met at 1e-4."""
+    f = lambda k: torch.from_numpy(golden["dense%d_log_%s" % (ci, k)]).float().cuda()
+    a, b, back = f("a").requires_grad_(True), f("b").requires_grad_(True), f("back").requires_grad_(True)
+    c = gb.logbmm(a, b)
+    g = torch.autograd.grad(c, (a, b), back, create_graph=True)
+    h = torch.autograd.grad((g[0], g[1]), (a, b, back), (f("h_a"), f("h_b")))
+    for got, name in zip(h, ("hh_a", "hh_b", "hh_back")):
+        assert_close(got, golden["dense%d_log_%s" % (ci, name)], 1e-4, 1e-5, name)
+    # the cotangent of grad_a alone: the case the reference's kernels implement
+    c = gb.logbmm(a, b)
+    g = torch.autograd.grad(c, (a, b), back, create_graph=True)
+    h = torch.autograd.grad(g[0], (a, b, back), f("h_a"))
+    for got, name in zip(h, ("ha_only_a", "ha_only_b", "ha_only_back")):
+        assert_close(got, golden["dense%d_log_%s" % (ci, name)], 1e-4, 1e-5, name)
+
+
+@pytest.mark.parametrize("shape", [(2, 33, 17, 65), (2, 130, 70, 67), (1, 129, 200, 130)])
+def test_logbmm_second_order_matches_oracle(gb, shape):
+    from genbmm_b200 import _native
+    B, M, K, N = shape
+    gen = torch.Generator().manual_seed(sum(shape))
+    a, b = torch.randn(B, M, K, generator=gen), torch.randn(B, K, N, generator=gen)
+    g, h = torch.rand(B, M, N, generator=gen), torch.randn(B, M, K, generator=gen)
+    out, maxes = oracle.dense_fwd(0, a, b, dtype=np.float64)
+    wa, wb, wg = oracle.dense_bwdbwd(a, b, g, out, maxes, h, dtype=np.float64)
+    part = torch.from_numpy(out).float().cuda()
+    da, db, dg = _native.backbackward(a.cuda(), b.cuda(), g.cuda(), part, None, h.cuda(), 0)
+    assert_close(da, wa, 1e-4, 2e-5, "d/da")
+    assert_close(db, wb, 1e-4, 2e-5, "d/db")
+    assert_close(dg, wg, 1e-4, 2e-5, "d/dgrad_out")
