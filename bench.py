@@ -172,6 +172,58 @@ def time_steps(fn, steps, warmup, sync):
     return start.elapsed_time(stop) / 1e3
 
 
+def measure_configs(gb, dev):
+    """Forward+backward time of the other benchmark configurations (seeded synthetic inputs made on
+    the device; parity of the same shapes is covered by the test-suite).  Reported under "configs"."""
+    from genbmm_b200 import crf
+    res = {}
+    gen = torch.Generator(device=dev)
+
+    def fwd_bwd(fn, args, n_iter=5):
+        leaves = [x.detach().requires_grad_(True) for x in args[:2]]
+        rest = list(args[2:])
+
+        def step():
+            c = fn(*leaves, *rest)
+            c = c.data if isinstance(c, gb.BandedMatrix) else c
+            torch.autograd.grad(c, leaves, torch.ones_like(c))
+
+        return time_steps(step, n_iter, 2, torch.cuda.synchronize) / n_iter
+
+    gen.manual_seed(0)
+    a, b = (torch.rand(32, 64, 64, device=dev, generator=gen) for _ in range(2))
+    t = fwd_bwd(gb.logbmm, (a, b), 20)
+    res["cfg1_logbmm_32x64x64x64"] = {"ms": t * 1e3, "mac_per_s": 3 * 32 * 64 ** 3 / t}
+    gen.manual_seed(1)
+    a, b = ((torch.randn(256, 128, 128, device=dev, generator=gen) * 8).round() / 8 for _ in range(2))
+    for name in ("maxbmm", "prodmaxbmm"):
+        t = fwd_bwd(getattr(gb, name), (a, b), 10)
+        res["cfg2_%s_256x128x128x128" % name] = {"ms": t * 1e3, "mac_per_s": 256 * 128 ** 3 / t}
+    gen.manual_seed(2)
+    a, b = (2 * torch.randn(64, 256, 256, device=dev, generator=gen) for _ in range(2))
+    u = torch.rand(64, 256, 256, device=dev, generator=gen)
+    t = fwd_bwd(gb.samplebmm, (a, b, u), 10)
+    res["cfg3_samplebmm_64x256x256x256"] = {"ms": t * 1e3, "mac_per_s": 64 * 256 ** 3 / t}
+    gen.manual_seed(3)
+    pot = torch.randn(16, 511, 256, 256, device=dev, generator=gen)
+
+    def crf_step():
+        crf.marginals(pot)
+
+    t = time_steps(crf_step, 3, 1, torch.cuda.synchronize) / 3
+    res["cfg4_crf_B16_T512_C256"] = {"ms": t * 1e3, "mac_per_s": 3 * 16 * 510 * 256 ** 3 / t}
+    del pot
+    gen.manual_seed(4)
+    x, y = (torch.randn(32, 8192, 129, device=dev, generator=gen) for _ in range(2))
+    triples = 32 * 135428672  # valid (i, ja, jo) triples per forward at n=8192, 129 diagonals each
+    for name in ("multiply", "multiply_log", "multiply_max"):
+        def band(p, q, name=name):
+            return getattr(gb.BandedMatrix(p, 64, 64), name)(gb.BandedMatrix(q, 64, 64))
+        t = fwd_bwd(band, (x, y), 3)
+        res["cfg5_banded_%s_32x8192x129" % name] = {"ms": t * 1e3, "mac_per_s": 3 * triples / t}
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -180,6 +232,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=32, help="1024^3 problems per GPU per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the side measurements of configs 1-5")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -344,6 +397,11 @@ def main():
                  "maxbmm_frac_of_fp32_bound": (macs_max * 2 / (N_SMS * FP32_PER_SM_CLK * peaks["sm_max_mhz"] * 1e6))
                  / (t_max / args.steps)},
     }
+    if rank == 0 and world == 1 and not args.no_configs:
+        try:
+            line["configs"] = measure_configs(gb, dev)
+        except Exception as exc:  # the headline must not depend on the side measurements
+            line["configs"] = {"error": repr(exc)}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         host_threads()
         value, secs, threads = cpu_logbmm_sample(512, 64)

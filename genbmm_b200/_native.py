@@ -24,8 +24,9 @@ _SIGNATURES = {
     "gbmm_dense_forward_f32": ([_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
     "gbmm_dense_backward_f32": ([_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
     "gbmm_dense_backbackward_f32": ([_P] * 9 + [_L] * 4 + [_P], _I),
-    "gbmm_band_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L, _P], _I),
-    "gbmm_band_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P], _I),
+    "gbmm_band_workspace_bytes": ([_L, _L], _L),
+    "gbmm_band_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L, _P, _L, _P], _I),
+    "gbmm_band_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P, _L, _P], _I),
     "gbmm_logbmm_workspace_bytes": ([_I, _L, _L, _L, _L], _L),
     "gbmm_logbmm_flag_count": ([_L, _L, _L], _L),
     "gbmm_logbmm_forward_f32": ([_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
@@ -204,11 +205,18 @@ def _check_band(a, a_lu, a_lb, b, b_lu, b_lb):
         raise RuntimeError("a and b must be on the same device")
 
 
-def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode):
+def _band_workspace(B, n, device):
+    if os.environ.get("GENBMM_B200_BANDLOG", "auto") == "exact":
+        return None
+    return torch.empty((max(int(load().gbmm_band_workspace_bytes(B, n)), 256),), dtype=torch.uint8, device=device)
+
+
+def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode, want_maxes=False):
     """`_genbmm.forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode)` -> [out, indices, maxes].
 
     Only the outputs the mode defines are produced (the reference allocates and zero-fills all
-    three every call, banded_cuda_kernel.cu:373-387); the others are returned as None.
+    three every call, banded_cuda_kernel.cu:373-387); the others are returned as None, and the
+    log mode's `maxes` only on request (the backward does not need it).
     """
     _check_band(a, a_lu, a_lb, b, b_lu, b_lb)
     if mode not in (BAND_LOG, BAND_MAX, BAND_MUL):
@@ -218,9 +226,11 @@ def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode):
     with torch.cuda.device(a.device):
         out = torch.empty((B, n, Wo), dtype=a.dtype, device=a.device)
         idx = torch.empty((B, n, Wo), dtype=torch.int32, device=a.device) if mode == BAND_MAX else None
-        maxes = torch.empty_like(out) if mode == BAND_LOG else None
+        maxes = torch.empty_like(out) if (mode == BAND_LOG and want_maxes) else None
+        ws = _band_workspace(B, n, a.device) if mode == BAND_LOG else None
         st = load().gbmm_band_forward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), _ptr(idx),
-                                          _ptr(maxes), B, n, _stream(a.device))
+                                          _ptr(maxes), B, n, _ptr(ws), 0 if ws is None else ws.numel(),
+                                          _stream(a.device))
     _check(st, "gbmm_band_forward_f32")
     return [out, idx, maxes]
 
@@ -251,8 +261,10 @@ def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=Fa
             raise RuntimeError("part must have shape %s" % ((B, n, Wo),))
         grad_a = torch.empty_like(a)
         grad_b = torch.empty_like(b) if both else None
+        ws = _band_workspace(B, n, a.device) if mode == BAND_LOG else None
         st = load().gbmm_band_backward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(grad_output),
-                                           _ptr(part), _ptr(grad_a), _ptr(grad_b), B, n, _stream(a.device))
+                                           _ptr(part), _ptr(grad_a), _ptr(grad_b), B, n, _ptr(ws),
+                                           0 if ws is None else ws.numel(), _stream(a.device))
     _check(st, "gbmm_band_backward_f32")
     return [grad_a, grad_b] if both else [grad_a]
 

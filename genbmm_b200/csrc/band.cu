@@ -14,7 +14,7 @@
 // so that the skewed access b[o(j)][k2(j)] of consecutive lanes hits distinct banks), only
 // the outputs a mode needs are written, and grad_b is computed directly.
 // When the rows of a CTA do not fit in shared memory the same code reads global memory.
-#include "common.cuh"
+#include "band.cuh"
 
 namespace gbmm {
 namespace {
@@ -44,15 +44,6 @@ __device__ __forceinline__ void stage_rows(T* dst, int pitch, const T* src, int 
   }
 }
 
-struct BandDims {
-  int64_t n;
-  int a_lu, a_ld, b_lu, b_ld;
-  __host__ __device__ int Wa() const { return a_lu + a_ld + 1; }
-  __host__ __device__ int Wb() const { return b_lu + b_ld + 1; }
-  __host__ __device__ int r_lu() const { return a_lu + b_ld; }
-  __host__ __device__ int Wo() const { return Wa() + Wb() - 1; }
-};
-
 // even pitch for b rows: consecutive lanes step by pitch-1 floats, which must be odd
 __host__ __device__ inline int b_pitch(int Wb) { return (Wb & 1) ? Wb + 1 : Wb; }
 
@@ -61,12 +52,14 @@ template <int MODE>
 __global__ void __launch_bounds__(NT) band_fwd_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                                       float* __restrict__ out, int* __restrict__ idx,
                                                       float* __restrict__ maxes, BandDims d, int TI,
-                                                      int tiles_i, int staged) {
+                                                      int tiles_i, int staged, const int* __restrict__ flags) {
   extern __shared__ float smem[];
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
   const int64_t n = d.n;
   const int64_t bt = blockIdx.x / tiles_i;
   const int64_t i0 = (int64_t)(blockIdx.x % tiles_i) * TI;
+  // behind the block-banded fast path only the flagged 64-row blocks are recomputed
+  if (flags && __ldg(flags + bt * ((n + 63) / 64) + i0 / 64) == 0) return;
   const float* ab = a + bt * n * Wa;
   const float* bb = b + bt * n * Wb;
   Rows<float> va{ab, Wa, 0}, vb{bb, Wb, 0};
@@ -101,11 +94,13 @@ __global__ void __launch_bounds__(NT) band_fwd_kernel(const float* __restrict__ 
     const int kofs = Wb - 1 - jo;
     if (MODE == GBMM_BAND_MUL) {
       float val = 0.f;
+#pragma unroll 8
       for (int ja = lo; ja <= hi; ++ja) val = fmaf(va.at(i, ja), vb.at(o, ja + kofs), val);
       out[oi] = val;
     } else if (MODE == GBMM_BAND_MAX) {
       float m = kFloor;
       int ind = -1;
+#pragma unroll 8
       for (int ja = lo; ja <= hi; ++ja) {
         const float v = __fadd_rn(va.at(i, ja), vb.at(o, ja + kofs));
         if (v > m) {
@@ -117,8 +112,10 @@ __global__ void __launch_bounds__(NT) band_fwd_kernel(const float* __restrict__ 
       if (idx) idx[oi] = ind;
     } else {
       float m = kFloor;
+#pragma unroll 8
       for (int ja = lo; ja <= hi; ++ja) m = fmaxf(m, va.at(i, ja) + vb.at(o, ja + kofs));
       float s = 0.f;
+#pragma unroll 8
       for (int ja = lo; ja <= hi; ++ja) s += exp_sfu((va.at(i, ja) + vb.at(o, ja + kofs)) - m);
       out[oi] = logf(s) + m;
       if (maxes) maxes[oi] = m;
@@ -131,12 +128,13 @@ template <int MODE>
 __global__ void __launch_bounds__(NT) band_bwd_a_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                                         const float* __restrict__ g, const void* __restrict__ part,
                                                         float* __restrict__ grad_a, BandDims d, int TI,
-                                                        int tiles_i, int staged) {
+                                                        int tiles_i, int staged, const int* __restrict__ flags) {
   extern __shared__ float smem[];
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
   const int64_t n = d.n;
   const int64_t bt = blockIdx.x / tiles_i;
   const int64_t i0 = (int64_t)(blockIdx.x % tiles_i) * TI;
+  if (flags && __ldg(flags + bt * ((n + 63) / 64) + i0 / 64) == 0) return;  // rows of flagged blocks only
   const float* ab = a + bt * n * Wa;
   const float* bb = b + bt * n * Wb;
   const float* gb = g + bt * n * Wo;
@@ -173,6 +171,7 @@ __global__ void __launch_bounds__(NT) band_bwd_a_kernel(const float* __restrict_
       lo = (int)max((int64_t)lo, (int64_t)r_lu - i);
       hi = (int)min((int64_t)hi, n - 1 - i + r_lu);
       const float av = (MODE == GBMM_BAND_LOG) ? __ldg(ab + (i * Wa + ja)) : 0.f;
+#pragma unroll 8
       for (int jo = lo; jo <= hi; ++jo) {
         const int64_t o = i + jo - r_lu;
         const int k2 = ja - jo + Wb - 1;
@@ -196,7 +195,7 @@ template <int MODE>
 __global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                                         const float* __restrict__ g, const void* __restrict__ part,
                                                         float* __restrict__ grad_b, BandDims d, int TO, int TI,
-                                                        int tiles_o, int staged) {
+                                                        int tiles_o, int staged, const int* __restrict__ flags) {
   extern __shared__ float smem[];
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
   const int r_ld = Wo - 1 - r_lu;
@@ -213,6 +212,14 @@ __global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict_
   const int64_t i_begin = max((int64_t)0, o0 - r_ld);
   const int64_t i_end = min(n, o0 + TO + r_lu);  // exclusive
   const int total = TO * Wb;
+  // With flags (behind the block-banded fast path) only rows i of flagged 64-row blocks
+  // contribute and the sums are added to what the fast kernel wrote.
+  const int* frow = flags ? flags + bt * ((n + 63) / 64) : nullptr;
+  if (frow) {
+    bool any = false;
+    for (int64_t q = i_begin / 64; q <= (i_end - 1) / 64; ++q) any |= (__ldg(frow + q) != 0);
+    if (!any) return;
+  }
 
   float* acc = smem;             // [TO*Wb], staged mode only
   float* sa = acc + TO * Wb;     // [TI*Wa]
@@ -252,7 +259,9 @@ __global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict_
         lo = max(lo, c0);
         hi = min(hi, c1 - 1);
         const float bv = (MODE == GBMM_BAND_LOG) ? __ldg(bb + (o * Wb + k2)) : 0.f;
+#pragma unroll 4
         for (int64_t i = lo; i <= hi; ++i) {
+          if (frow && __ldg(frow + i / 64) == 0) continue;
           const int jo = (int)(o - i + r_lu);
           const int ja = k2 + jo - (Wb - 1);
           if (MODE == GBMM_BAND_MUL) {
@@ -267,7 +276,7 @@ __global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict_
       if (staged)
         acc[e] = val;
       else
-        ob[o * Wb + k2] = val;
+        ob[o * Wb + k2] = frow ? ob[o * Wb + k2] + val : val;
     }
   }
   if (staged) {
@@ -275,9 +284,10 @@ __global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict_
     for (int e = threadIdx.x; e < total; e += NT) {
       const int ol = e / Wb;
       if (o0 + ol >= n) break;
-      ob[(o0 + ol) * Wb + (e - ol * Wb)] = acc[e];
+      float* dst = ob + (o0 + ol) * Wb + (e - ol * Wb);
+      *dst = frow ? *dst + acc[e] : acc[e];
     }
-  } else if (i_begin >= i_end) {
+  } else if (i_begin >= i_end && !frow) {
     for (int e = threadIdx.x; e < total; e += NT) {
       const int ol = e / Wb;
       if (o0 + ol >= n) break;
@@ -310,15 +320,10 @@ int check_band(int mode, int64_t B, int64_t n, int a_lu, int a_ld, int b_lu, int
 
 using namespace gbmm;
 
-extern "C" int gbmm_band_forward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu,
-                                     int b_ld, float* out, int32_t* idx, float* maxes, int64_t B, int64_t n,
-                                     void* stream) {
-  const int st0 = check_band(mode, B, n, a_lu, a_ld, b_lu, b_ld);
-  if (st0 != GBMM_OK) return st0;
-  if (B == 0 || n == 0) return GBMM_OK;
-  if (!a || !b || !out) return GBMM_ERR_INVALID_ARG;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const BandDims d{n, a_lu, a_ld, b_lu, b_ld};
+// The direct kernels above on every row (flags == nullptr) or on the flagged 64-row blocks only.
+static int exact_forward(int mode, const float* a, const float* b, float* out, int32_t* idx, float* maxes,
+                         const BandDims& d, int64_t B, const int* flags, cudaStream_t st) {
+  const int64_t n = d.n;
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo();
   const size_t ldb = b_pitch(Wb);
   int TI = pick_rows((size_t)(Wo - 1) * ldb, (size_t)Wa + ldb);
@@ -331,7 +336,7 @@ extern "C" int gbmm_band_forward_f32(int mode, const float* a, int a_lu, int a_l
   do {                                                                                                  \
     if (smem > 48 * 1024 && !allow_smem(band_fwd_kernel<MODE>, smem)) return GBMM_ERR_LAUNCH;           \
     band_fwd_kernel<MODE><<<(unsigned)blocks, NT, smem, st>>>(a, b, out, idx, maxes, d, TI, (int)tiles, \
-                                                             staged);                                  \
+                                                             staged, flags);                           \
   } while (0)
   if (mode == GBMM_BAND_MUL) GBMM_LAUNCH_BAND_FWD(GBMM_BAND_MUL);
   else if (mode == GBMM_BAND_MAX) GBMM_LAUNCH_BAND_FWD(GBMM_BAND_MAX);
@@ -340,16 +345,10 @@ extern "C" int gbmm_band_forward_f32(int mode, const float* a, int a_lu, int a_l
   return launch_status();
 }
 
-extern "C" int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu,
-                                      int b_ld, const float* grad_out, const void* part, float* grad_a,
-                                      float* grad_b, int64_t B, int64_t n, void* stream) {
-  const int st0 = check_band(mode, B, n, a_lu, a_ld, b_lu, b_ld);
-  if (st0 != GBMM_OK) return st0;
-  if (B == 0 || n == 0) return GBMM_OK;
-  if (!a || !b || !grad_out) return GBMM_ERR_INVALID_ARG;
-  if (mode != GBMM_BAND_MUL && !part) return GBMM_ERR_INVALID_ARG;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const BandDims d{n, a_lu, a_ld, b_lu, b_ld};
+static int exact_backward(int mode, const float* a, const float* b, const float* grad_out, const void* part,
+                          float* grad_a, float* grad_b, const BandDims& d, int64_t B, const int* flags,
+                          cudaStream_t st) {
+  const int64_t n = d.n;
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo();
   const size_t ldb = b_pitch(Wb);
   if (grad_a) {
@@ -363,7 +362,7 @@ extern "C" int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_
   do {                                                                                                    \
     if (smem > 48 * 1024 && !allow_smem(band_bwd_a_kernel<MODE>, smem)) return GBMM_ERR_LAUNCH;           \
     band_bwd_a_kernel<MODE><<<(unsigned)blocks, NT, smem, st>>>(a, b, grad_out, part, grad_a, d, TI,      \
-                                                               (int)tiles, staged);                      \
+                                                               (int)tiles, staged, flags);               \
   } while (0)
     if (mode == GBMM_BAND_MUL) GBMM_LAUNCH_BAND_BWD_A(GBMM_BAND_MUL);
     else if (mode == GBMM_BAND_MAX) GBMM_LAUNCH_BAND_BWD_A(GBMM_BAND_MAX);
@@ -389,7 +388,7 @@ extern "C" int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_
   do {                                                                                                    \
     if (smem > 48 * 1024 && !allow_smem(band_bwd_b_kernel<MODE>, smem)) return GBMM_ERR_LAUNCH;           \
     band_bwd_b_kernel<MODE><<<(unsigned)blocks, NT, smem, st>>>(a, b, grad_out, part, grad_b, d, TO, TI,  \
-                                                               (int)tiles, staged);                      \
+                                                               (int)tiles, staged, flags);               \
   } while (0)
     if (mode == GBMM_BAND_MUL) GBMM_LAUNCH_BAND_BWD_B(GBMM_BAND_MUL);
     else if (mode == GBMM_BAND_MAX) GBMM_LAUNCH_BAND_BWD_B(GBMM_BAND_MAX);
@@ -397,4 +396,55 @@ extern "C" int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_
 #undef GBMM_LAUNCH_BAND_BWD_B
   }
   return launch_status();
+}
+
+// Bands this narrow leave too few in-band cells per 64x64 block for the block-banded kernels
+// to pay off; the direct kernels take them.
+static bool use_block_path(const BandDims& d) { return (int64_t)d.Wa() * d.Wb() >= 64; }
+
+extern "C" int64_t gbmm_band_workspace_bytes(int64_t B, int64_t n) {
+  if (B < 0 || n < 0) return -1;
+  return band_fast_workspace_bytes(B, n);
+}
+
+extern "C" int gbmm_band_forward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu,
+                                     int b_ld, float* out, int32_t* idx, float* maxes, int64_t B, int64_t n,
+                                     void* workspace, int64_t workspace_bytes, void* stream) {
+  const int st0 = check_band(mode, B, n, a_lu, a_ld, b_lu, b_ld);
+  if (st0 != GBMM_OK) return st0;
+  if (B == 0 || n == 0) return GBMM_OK;
+  if (!a || !b || !out) return GBMM_ERR_INVALID_ARG;
+  if (mode == GBMM_BAND_MAX && !idx) return GBMM_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const BandDims d{n, a_lu, a_ld, b_lu, b_ld};
+  const bool have_ws = workspace && workspace_bytes >= band_fast_workspace_bytes(B, n) &&
+                       (reinterpret_cast<uintptr_t>(workspace) & 255) == 0;
+  const bool fast = use_block_path(d) && (mode != GBMM_BAND_LOG || (have_ws && !maxes));
+  if (!fast) return exact_forward(mode, a, b, out, idx, maxes, d, B, nullptr, st);
+  int* flags = nullptr;
+  const int rc = band_fast_forward(mode, a, b, out, idx, d, B, workspace, &flags, st);
+  if (rc != GBMM_OK || mode != GBMM_BAND_LOG) return rc;
+  return exact_forward(mode, a, b, out, nullptr, nullptr, d, B, flags, st);
+}
+
+extern "C" int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu,
+                                      int b_ld, const float* grad_out, const void* part, float* grad_a,
+                                      float* grad_b, int64_t B, int64_t n, void* workspace,
+                                      int64_t workspace_bytes, void* stream) {
+  const int st0 = check_band(mode, B, n, a_lu, a_ld, b_lu, b_ld);
+  if (st0 != GBMM_OK) return st0;
+  if (B == 0 || n == 0) return GBMM_OK;
+  if (!a || !b || !grad_out) return GBMM_ERR_INVALID_ARG;
+  if (mode != GBMM_BAND_MUL && !part) return GBMM_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const BandDims d{n, a_lu, a_ld, b_lu, b_ld};
+  const bool have_ws = workspace && workspace_bytes >= band_fast_workspace_bytes(B, n) &&
+                       (reinterpret_cast<uintptr_t>(workspace) & 255) == 0;
+  const bool fast = use_block_path(d) && mode != GBMM_BAND_MAX && (mode != GBMM_BAND_LOG || have_ws);
+  if (!fast) return exact_backward(mode, a, b, grad_out, part, grad_a, grad_b, d, B, nullptr, st);
+  int* flags = nullptr;
+  const int rc = band_fast_backward(mode, a, b, grad_out, static_cast<const float*>(part), grad_a, grad_b, d, B,
+                                    workspace, &flags, st);
+  if (rc != GBMM_OK || mode != GBMM_BAND_LOG) return rc;
+  return exact_backward(mode, a, b, grad_out, part, grad_a, grad_b, d, B, flags, st);
 }

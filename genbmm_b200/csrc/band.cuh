@@ -1,0 +1,26 @@
+// Shared declarations of the banded kernels.
+#pragma once
+#include "common.cuh"
+
+namespace gbmm {
+
+struct BandDims {
+  int64_t n;
+  int a_lu, a_ld, b_lu, b_ld;
+  __host__ __device__ int Wa() const { return a_lu + a_ld + 1; }
+  __host__ __device__ int Wb() const { return b_lu + b_ld + 1; }
+  __host__ __device__ int r_lu() const { return a_lu + b_ld; }
+  __host__ __device__ int Wo() const { return Wa() + Wb() - 1; }
+};
+
+// Block-banded fast path (band_block.cu).  `ws` is the caller's workspace of at least
+// band_fast_workspace_bytes(B, n) bytes (log semiring only; may be null otherwise); for the log
+// semiring *flags_out receives the device array (B, ceil(n/64)) of row blocks that the exact
+// kernels must redo.
+int64_t band_fast_workspace_bytes(int64_t B, int64_t n);
+int band_fast_forward(int mode, const float* a, const float* b, float* out, int* idx, const BandDims& d, int64_t B,
+                      void* ws, int** flags_out, cudaStream_t st);
+int band_fast_backward(int mode, const float* a, const float* b, const float* g, const float* part, float* grad_a,
+                       float* grad_b, const BandDims& d, int64_t B, void* ws, int** flags_out, cudaStream_t st);
+
+}  // namespace gbmm

@@ -99,14 +99,17 @@ int gbmm_dense_backbackward_f32(const float* a, const float* b, const float* gra
  * banded_cuda_kernel.cu:354-402.
  *   a:(B,n,a_lu+a_ld+1) b:(B,n,b_lu+b_ld+1) -> out:(B,n,Wo), Wo = Wa+Wb-1, with result
  *   bands lu = a_lu+b_ld, ld = a_ld+b_lu.  Cells outside the matrix are written as 0.
- *   idx (int32*, mode MAX; argmax in a's band coordinate, -1 if none) and maxes
- *   (float*, mode LOG) may be NULL when not wanted; they are written in full
- *   (0 outside the matrix) when given.
+ *   idx (int32*, required for mode MAX; argmax in a's band coordinate, -1 if none) and maxes
+ *   (float*, mode LOG, optional) are written in full (0 outside the matrix) when given.
+ * workspace: optional scratch of gbmm_band_workspace_bytes(B, n) bytes, 256-byte aligned.  With
+ * it (and maxes == NULL) mode LOG runs the block-banded fast kernels with the exact kernels as
+ * guard; without it mode LOG runs the exact kernels only.  Other modes ignore it.
  */
+int64_t gbmm_band_workspace_bytes(int64_t B, int64_t n);
 int gbmm_band_forward_f32(int mode, const float* a, int a_lu, int a_ld,
                           const float* b, int b_lu, int b_ld,
                           float* out, int32_t* idx, float* maxes,
-                          int64_t B, int64_t n, void* stream);
+                          int64_t B, int64_t n, void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
  * Banded backward.  Replaces `_genbmm.backward_band(a, a_lu, a_lb, b, b_lu, b_lb,
@@ -117,12 +120,13 @@ int gbmm_band_forward_f32(int mode, const float* a, int a_lu, int a_ld,
  * directly; grad_a or grad_b may be NULL to skip it.
  *   mode MUL: part unused.  mode LOG: part = forward out (float*).
  *   mode MAX: part = forward idx (int32*, a's band coordinate).
+ * workspace: as for the forward (mode LOG).
  */
 int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_ld,
                            const float* b, int b_lu, int b_ld,
                            const float* grad_out, const void* part,
                            float* grad_a, float* grad_b,
-                           int64_t B, int64_t n, void* stream);
+                           int64_t B, int64_t n, void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
  * Factorised log-semiring product (fast path of logbmm).  Same result as

@@ -143,3 +143,25 @@ def test_band_rejects_bad_inputs(gb):
         gb.BandedMatrix(a, 1, 1).multiply(gb.BandedMatrix(a.cuda(), 1, 1))
     with pytest.raises(AssertionError):
         gb.BandedMatrix(a.cuda(), 2, 2)
+
+
+def test_band_log_guard_recomputes_flagged_row_blocks(gb, monkeypatch):
+    """Operand rows whose supports miss each other make the factorised sum underflow: the row
+    block is flagged and goes through the exact kernels, forward and backward."""
+    from genbmm_b200 import _native
+    B, n, lu, ld = 2, 200, 9, 8
+    gen = torch.Generator().manual_seed(5)
+    a, b = torch.randn(B, n, lu + ld + 1, generator=gen), torch.randn(B, n, lu + ld + 1, generator=gen)
+    g = torch.rand(B, n, 2 * (lu + ld) + 1, generator=gen)
+    a[:, 70:90, :9] -= 300.0     # rows 70..89 of a live on the upper half of the band ...
+    b[:, 60:100, 9:] -= 300.0    # ... the b rows they meet live on the lower half
+    out, ga, gb_ = run(gb, "multiply_log", a, lu, ld, b, lu, ld, g)
+    want, _, _, dA, dB = oracle.band_fwd_bwd(0, a, lu, ld, b, lu, ld, g, dtype=np.float64)
+    assert_close(out.data, want, 1e-5, 2e-5, "fwd")
+    assert_close(ga, dA, 3e-4, 1e-5, "grad_a")
+    assert_close(gb_, dB, 3e-4, 1e-5, "grad_b")
+    # and the exact kernels alone agree
+    monkeypatch.setenv("GENBMM_B200_BANDLOG", "exact")
+    out2, ga2, gb2 = run(gb, "multiply_log", a, lu, ld, b, lu, ld, g)
+    assert torch.allclose(out.data, out2.data, rtol=1e-5, atol=2e-5)
+    assert torch.allclose(ga, ga2, rtol=3e-4, atol=1e-5) and torch.allclose(gb_, gb2, rtol=3e-4, atol=1e-5)

@@ -39,9 +39,9 @@ def test_status_strings_and_argument_validation_without_a_gpu():
     assert lib.gbmm_dense_forward_f32(0, None, None, None, None, None, 1, 1, 1, 1, None) == 1
     assert lib.gbmm_dense_forward_f32(0, None, None, None, None, None, 0, 1, 1, 1, None) == 0
     assert lib.gbmm_dense_forward_f32(0, None, None, None, None, None, -1, 1, 1, 1, None) == 1
-    assert lib.gbmm_band_forward_f32(2, None, 1, 1, None, 1, 1, None, None, None, 1, 4, None) == 1
-    assert lib.gbmm_band_forward_f32(3, None, -1, 1, None, 1, 1, None, None, None, 1, 4, None) == 1
-    assert lib.gbmm_band_backward_f32(0, None, 1, 1, None, 1, 1, None, None, None, None, 0, 4, None) == 0
+    assert lib.gbmm_band_forward_f32(2, None, 1, 1, None, 1, 1, None, None, None, 1, 4, None, 0, None) == 1
+    assert lib.gbmm_band_forward_f32(3, None, -1, 1, None, 1, 1, None, None, None, 1, 4, None, 0, None) == 1
+    assert lib.gbmm_band_backward_f32(0, None, 1, 1, None, 1, 1, None, None, None, None, 0, 4, None, 0, None) == 0
 
 
 def test_host_mirror_rejects_cpu_and_strided_tensors():
