@@ -296,6 +296,82 @@ __global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict_
   }
 }
 
+// ------------------------------------------------------------------ max semiring: index routing
+// Each result cell (i, jo) hands its cotangent to exactly one cell of each operand, the one its
+// saved argmax names: grad_a[i][ja] with ja = idx[i][jo], and grad_b[o][k2] with o = i+jo-r_lu,
+// k2 = ja-jo+Wb-1.  O(n*Wo) work instead of the O(n*Wa*Wb) comparisons of
+// banded_cuda_kernel.cu:139-141; sums run in ascending jo (grad_a) and ascending i (grad_b), the
+// order of the reference's loops (its grad_b comes from the operand-swapped call, which walks
+// the same cells in ascending i).
+
+// grad_a: one warp per row i; lanes take 32 consecutive jo, same-target lanes add in lane order.
+__global__ void __launch_bounds__(256) band_route_a_kernel(const int* __restrict__ idx, const float* __restrict__ g,
+                                                           float* __restrict__ grad_a, int64_t rows, BandDims d) {
+  extern __shared__ float hist_all[];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
+  const int64_t n = d.n, i = row % n;
+  float* hist = hist_all + warp * Wa;
+  for (int k = lane; k < Wa; k += 32) hist[k] = 0.f;
+  __syncwarp();
+  for (int j0 = 0; j0 < Wo; j0 += 32) {
+    const int jo = j0 + lane;
+    int k = -1;
+    float gv = 0.f;
+    bool hit = false;
+    if (jo < Wo) {
+      const int64_t o = i + jo - r_lu;
+      k = __ldg(idx + row * Wo + jo);
+      gv = __ldg(g + row * Wo + jo);
+      const int k2 = k - jo + Wb - 1;
+      const int64_t p = i + k - d.a_lu;
+      hit = o >= 0 && o < n && k >= 0 && k < Wa && k2 >= 0 && k2 < Wb && p >= 0 && p < n;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, hit ? k : -1 - lane);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
+    for (int r = 0; r <= last; ++r) {
+      if (hit && rank == r) hist[k] = __fadd_rn(hist[k], gv);
+      __syncwarp();
+    }
+  }
+  for (int k = lane; k < Wa; k += 32) grad_a[row * Wa + k] = hist[k];
+}
+
+// grad_b: one warp per 32 consecutive rows o of b; lane = one o, walking the contributing rows
+// i = o-jo+r_lu in ascending order into its private column of the [Wb][33] histogram.
+__global__ void __launch_bounds__(32) band_route_b_kernel(const int* __restrict__ idx, const float* __restrict__ g,
+                                                          float* __restrict__ grad_b, BandDims d, int tiles_o) {
+  extern __shared__ float hist[];
+  const int lane = threadIdx.x;
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu(), r_ld = Wo - 1 - r_lu;
+  const int64_t n = d.n;
+  const int64_t bt = blockIdx.x / tiles_o;
+  const int64_t o0 = (int64_t)(blockIdx.x % tiles_o) * 32, o = o0 + lane;
+  const int* ib = idx + bt * n * Wo;
+  const float* gb = g + bt * n * Wo;
+  for (int k = 0; k < Wb; ++k) hist[k * 33 + lane] = 0.f;
+  const int64_t i_lo = max((int64_t)0, o0 - r_ld), i_hi = min(n - 1, o0 + 31 + r_lu);
+  if (o < n) {
+#pragma unroll 4
+    for (int64_t i = i_lo; i <= i_hi; ++i) {
+      const int64_t jo = o - i + r_lu;
+      if (jo < 0 || jo >= Wo) continue;
+      const int ja = __ldg(ib + i * Wo + jo);
+      const int k2 = ja - (int)jo + Wb - 1;
+      const int64_t p = i + ja - d.a_lu;
+      if (ja >= 0 && ja < Wa && k2 >= 0 && k2 < Wb && p >= 0 && p < n)
+        hist[k2 * 33 + lane] = __fadd_rn(hist[k2 * 33 + lane], __ldg(gb + i * Wo + jo));
+    }
+  }
+  __syncwarp();
+  float* ob = grad_b + bt * n * Wb;
+  for (int ol = 0; ol < 32 && o0 + ol < n; ++ol)
+    for (int k = lane; k < Wb; k += 32) ob[(o0 + ol) * Wb + k] = hist[k * 33 + ol];
+}
+
 int pick_rows(size_t fixed_floats, size_t per_row_floats) {
   for (int t = 32; t >= 1; t >>= 1)
     if ((fixed_floats + per_row_floats * t) * sizeof(float) <= (size_t)kSmemBudget) return t;
@@ -345,10 +421,36 @@ static int exact_forward(int mode, const float* a, const float* b, float* out, i
   return launch_status();
 }
 
+static int route_max_backward(const float* grad_out, const int* idx, float* grad_a, float* grad_b,
+                              const BandDims& d, int64_t B, cudaStream_t st, bool* handled) {
+  const size_t smem_a = sizeof(float) * 8 * d.Wa(), smem_b = sizeof(float) * 33 * d.Wb();
+  *handled = smem_a <= (size_t)kSmemBudget && smem_b <= (size_t)kSmemBudget;
+  if (!*handled) return GBMM_OK;  // bands too wide for the histograms: the scanning kernels take over
+  if (grad_a) {
+    const int64_t rows = B * d.n, blocks = ceil_div(rows, 8);
+    if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+    if (smem_a > 48 * 1024 && !allow_smem(band_route_a_kernel, smem_a)) return GBMM_ERR_LAUNCH;
+    band_route_a_kernel<<<(unsigned)blocks, 256, smem_a, st>>>(idx, grad_out, grad_a, rows, d);
+    if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+  }
+  if (grad_b) {
+    const int64_t tiles = ceil_div(d.n, 32), blocks = B * tiles;
+    if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+    if (smem_b > 48 * 1024 && !allow_smem(band_route_b_kernel, smem_b)) return GBMM_ERR_LAUNCH;
+    band_route_b_kernel<<<(unsigned)blocks, 32, smem_b, st>>>(idx, grad_out, grad_b, d, (int)tiles);
+  }
+  return launch_status();
+}
+
 static int exact_backward(int mode, const float* a, const float* b, const float* grad_out, const void* part,
                           float* grad_a, float* grad_b, const BandDims& d, int64_t B, const int* flags,
                           cudaStream_t st) {
   const int64_t n = d.n;
+  if (mode == GBMM_BAND_MAX) {
+    bool handled = false;
+    const int rc = route_max_backward(grad_out, static_cast<const int*>(part), grad_a, grad_b, d, B, st, &handled);
+    if (rc != GBMM_OK || handled) return rc;
+  }
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo();
   const size_t ldb = b_pitch(Wb);
   if (grad_a) {

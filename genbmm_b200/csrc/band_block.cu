@@ -25,7 +25,7 @@
 namespace gbmm {
 namespace {
 
-constexpr int TB = 64, SK = 16, NTB = 256, LDT = TB + 4;
+constexpr int TB = 64, SK = 32, NTB = 256, LDT = TB + 4;
 constexpr float kTinyLog = -62.383246f;  // log(2^-90)
 
 enum { F_FWD = 0, F_DA = 1, F_DB = 2 };
@@ -36,10 +36,12 @@ struct BandView {
   int lu, W;
 };
 
-__device__ __forceinline__ bool band_cell(const BandView& m, int64_t n, int64_t row, int64_t col, int64_t* idx) {
-  const int64_t j = col - row + m.lu;
-  if (row < 0 || row >= n || col < 0 || col >= n || j < 0 || j >= m.W) return false;
-  *idx = row * m.W + j;
+// Is (row, col) a stored cell of the band matrix, and where?  Rows, columns and band offsets
+// fit in 32 bits (n < 2^31); only the element index is 64-bit.
+__device__ __forceinline__ bool band_cell(const BandView& m, int n, int row, int col, int64_t* idx) {
+  const int j = col - row + m.lu;
+  if ((unsigned)row >= (unsigned)n || (unsigned)col >= (unsigned)n || (unsigned)j >= (unsigned)m.W) return false;
+  *idx = (int64_t)row * m.W + j;
   return true;
 }
 
@@ -62,19 +64,19 @@ __global__ void __launch_bounds__(NTB) band_block_kernel(BlockArgs g) {
   __shared__ __align__(16) float xt[SK * LDT];
   __shared__ __align__(16) float yt[SK * LDT];
   const BandDims& d = g.d;
-  const int64_t n = d.n;
+  const int n = (int)d.n;
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu(), r_ld = Wo - 1 - r_lu;
-  const int nrb = (int)((n + TB - 1) / TB);
+  const int nrb = (n + TB - 1) / TB;
   const int64_t id = blockIdx.x;
   const int cbi = (int)(id % g.ncb);
   const int rbk = (int)((id / g.ncb) % nrb);
   const int64_t bt = id / ((int64_t)g.ncb * nrb);
   const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
 
-  const BandView A{g.a + bt * n * Wa, d.a_lu, Wa};
-  const BandView Bm{g.b + bt * n * Wb, d.b_lu, Wb};
-  const BandView G{g.g ? g.g + bt * n * Wo : nullptr, r_lu, Wo};
-  const BandView P{g.part ? g.part + bt * n * Wo : nullptr, r_lu, Wo};
+  const BandView A{g.a + bt * n * (int64_t)Wa, d.a_lu, Wa};
+  const BandView Bm{g.b + bt * n * (int64_t)Wb, d.b_lu, Wb};
+  const BandView G{g.g ? g.g + bt * n * (int64_t)Wo : nullptr, r_lu, Wo};
+  const BandView P{g.part ? g.part + bt * n * (int64_t)Wo : nullptr, r_lu, Wo};
   const float* ra = g.ra ? g.ra + bt * n : nullptr;
   const float* rb = g.rb ? g.rb + bt * n : nullptr;
   const int* flags = g.flags ? g.flags + bt * nrb : nullptr;
@@ -84,14 +86,14 @@ __global__ void __launch_bounds__(NTB) band_block_kernel(BlockArgs g) {
   if (FORM == F_FWD) { lu_out = r_lu; w_out = Wo; xl = d.a_lu; xu = d.a_ld; yl = d.b_lu; yu = d.b_ld; }
   if (FORM == F_DA)  { lu_out = d.a_lu; w_out = Wa; xl = r_lu; xu = r_ld; yl = d.b_ld; yu = d.b_lu; }
   if (FORM == F_DB)  { lu_out = d.b_lu; w_out = Wb; xl = r_ld; xu = r_lu; yl = d.a_ld; yu = d.a_lu; }
-  const int64_t r0 = (int64_t)rbk * TB;
+  const int r0 = rbk * TB;
   // first c-block that can meet the band of rows r0..: floor((r0 - lu_out) / TB)
-  const int64_t cfirst = (r0 - lu_out >= 0) ? (r0 - lu_out) / TB : -((lu_out - r0 + TB - 1) / TB);
-  const int64_t c0 = (cfirst + cbi) * TB;
+  const int cfirst = (r0 - lu_out >= 0) ? (r0 - lu_out) / TB : -((lu_out - r0 + TB - 1) / TB);
+  const int c0 = (cfirst + cbi) * TB;
   if (c0 - (r0 + TB - 1) > (w_out - 1 - lu_out)) return;  // wholly beyond the band
 
   // value of X at (r, s) and of Y at (c, s), transformed for the semiring
-  auto xval = [&](int64_t r, int64_t s) -> float {
+  auto xval = [&](int r, int s) -> float {
     int64_t q;
     if (FORM == F_FWD) {
       if (!band_cell(A, n, r, s, &q)) return SEMI == S_MAX ? __int_as_float(0xff800000) : 0.f;
@@ -99,7 +101,7 @@ __global__ void __launch_bounds__(NTB) band_block_kernel(BlockArgs g) {
       return SEMI == S_LOG ? exp_sfu(v - __ldg(ra + r)) : v;
     }
     // backward: G at (i, o); F_DA: (r, s) = (i, o); F_DB: (r, s) = (o, i)
-    const int64_t i = FORM == F_DA ? r : s, o = FORM == F_DA ? s : r;
+    const int i = FORM == F_DA ? r : s, o = FORM == F_DA ? s : r;
     if (!band_cell(G, n, i, o, &q)) return 0.f;
     const float gv = __ldg(G.p + q);
     if (SEMI != S_LOG) return gv;
@@ -108,7 +110,7 @@ __global__ void __launch_bounds__(NTB) band_block_kernel(BlockArgs g) {
   };
   // (max semiring: a missing cell of either operand is -inf, so the sum never wins)
   constexpr float kPadY = 0.f;
-  auto yval = [&](int64_t c, int64_t s) -> float {
+  auto yval = [&](int c, int s) -> float {
     int64_t q;
     if (FORM == F_DB) {  // A at (i, p) = (s, c)
       if (!band_cell(A, n, s, c, &q)) return 0.f;
@@ -116,7 +118,7 @@ __global__ void __launch_bounds__(NTB) band_block_kernel(BlockArgs g) {
       return SEMI == S_LOG ? exp_sfu(v - __ldg(ra + s)) : v;
     }
     // Bm at (o, p): F_FWD: (c, s) = (o, p); F_DA: (c, s) = (p, o)
-    const int64_t o = FORM == F_FWD ? c : s, p = FORM == F_FWD ? s : c;
+    const int o = FORM == F_FWD ? c : s, p = FORM == F_FWD ? s : c;
     if (!band_cell(Bm, n, o, p, &q)) return SEMI == S_MAX ? __int_as_float(0xff800000) : kPadY;
     const float v = __ldg(Bm.p + q);
     return SEMI == S_LOG ? exp_sfu(v - __ldg(rb + o)) : v;
@@ -135,9 +137,9 @@ __global__ void __launch_bounds__(NTB) band_block_kernel(BlockArgs g) {
       best[i][j] = -1;
     }
 
-  int64_t s_lo = max(max(r0 - xl, c0 - yl), (int64_t)0);
-  const int64_t s_hi = min(min(r0 + TB - 1 + xu, c0 + TB - 1 + yu), n - 1);
-  for (int64_t s0 = s_lo; s0 <= s_hi; s0 += SK) {
+  const int s_lo = max(max(r0 - xl, c0 - yl), 0);
+  const int s_hi = min(min(r0 + TB - 1 + xu, c0 + TB - 1 + yu), n - 1);
+  for (int s0 = s_lo; s0 <= s_hi; s0 += SK) {
     __syncthreads();
 #pragma unroll
     for (int q = 0; q < TB * SK / NTB; ++q) {
@@ -167,7 +169,7 @@ __global__ void __launch_bounds__(NTB) band_block_kernel(BlockArgs g) {
             const float v = __fadd_rn(x[i], y[j]);
             if (v > acc[i][j]) {
               acc[i][j] = v;
-              best[i][j] = (int)(s0 - s_lo) + sl;
+              best[i][j] = s0 + sl;
             }
           } else {
             acc[i][j] = fmaf(x[i], y[j], acc[i][j]);
@@ -178,17 +180,17 @@ __global__ void __launch_bounds__(NTB) band_block_kernel(BlockArgs g) {
 
   // epilogue: scatter the block's band cells into band storage
   bool bad = false;
-  float* ob = g.out + bt * n * w_out;
+  float* ob = g.out + bt * n * (int64_t)w_out;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int64_t r = r0 + ty * 4 + i;
+    const int r = r0 + ty * 4 + i;
     if (r >= n) continue;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int64_t c = c0 + tx * 4 + j;
-      const int64_t cell = c - r + lu_out;
+      const int c = c0 + tx * 4 + j;
+      const int cell = c - r + lu_out;
       if (cell < 0 || cell >= w_out) continue;
-      const int64_t q = r * w_out + cell;
+      const int64_t q = (int64_t)r * w_out + cell;
       const bool inside = c >= 0 && c < n;
       float v = acc[i][j];
       if (FORM == F_FWD) {
@@ -197,9 +199,9 @@ __global__ void __launch_bounds__(NTB) band_block_kernel(BlockArgs g) {
           bad |= inside && (!(v >= 8.0779356694631609e-28f) || !(v <= 3.0e38f) || sh < kFloor);
           v = logf(v) + sh;
         }
-        if (SEMI == S_MAX) g.idx[bt * n * w_out + q] = (inside && best[i][j] >= 0)
-                                                          ? (int)(s_lo + best[i][j] - r + d.a_lu)
-                                                          : (inside ? -1 : 0);
+        if (SEMI == S_MAX)
+          g.idx[bt * n * (int64_t)w_out + q] = (inside && best[i][j] >= 0) ? best[i][j] - r + d.a_lu
+                                                                            : (inside ? -1 : 0);
         ob[q] = inside ? v : 0.f;  // cells outside the matrix stay zero (banded_cuda_kernel.cu:38)
       } else {
         if (SEMI == S_LOG && inside) {
