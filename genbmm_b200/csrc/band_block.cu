@@ -139,23 +139,40 @@ __global__ void __launch_bounds__(NTB) band_block_kernel(BlockArgs g) {
 
   const int s_lo = max(max(r0 - xl, c0 - yl), 0);
   const int s_hi = min(min(r0 + TB - 1 + xu, c0 + TB - 1 + yu), n - 1);
-  for (int s0 = s_lo; s0 <= s_hi; s0 += SK) {
-    __syncthreads();
+  constexpr int NE = TB * SK / NTB;  // tile elements per thread and operand
+  constexpr float kPadX = SEMI == S_MAX ? -__builtin_huge_valf() : 0.f;
+  float xr[NE], yr[NE];
+  // fetch one chunk of both operand tiles into registers (issued before the previous chunk is
+  // multiplied, so the global-memory latency overlaps the FFMAs)
+  auto fetch = [&](int s0) {
 #pragma unroll
-    for (int q = 0; q < TB * SK / NTB; ++q) {
+    for (int q = 0; q < NE; ++q) {
       const int e = tid + q * NTB;
       {
         const int sl = X_S_FAST ? e % SK : e / TB, rl = X_S_FAST ? e / SK : e % TB;
-        xt[sl * LDT + rl] = (s0 + sl <= s_hi) ? xval(r0 + rl, s0 + sl)
-                                              : (SEMI == S_MAX ? __int_as_float(0xff800000) : 0.f);
+        xr[q] = (s0 + sl <= s_hi) ? xval(r0 + rl, s0 + sl) : kPadX;
       }
       {
         const int sl = Y_S_FAST ? e % SK : e / TB, cl = Y_S_FAST ? e / SK : e % TB;
-        yt[sl * LDT + cl] = (s0 + sl <= s_hi) ? yval(c0 + cl, s0 + sl)
-                                              : (SEMI == S_MAX ? __int_as_float(0xff800000) : 0.f);
+        yr[q] = (s0 + sl <= s_hi) ? yval(c0 + cl, s0 + sl) : kPadX;
       }
     }
+  };
+  // The log semiring's tile values cost extra loads and an exponential each; prefetching them a
+  // chunk ahead costs more in registers than it hides (measured), so those fetch in place.
+  constexpr bool PREFETCH = SEMI != S_LOG;
+  if (PREFETCH && s_lo <= s_hi) fetch(s_lo);
+  for (int s0 = s_lo; s0 <= s_hi; s0 += SK) {
+    __syncthreads();  // the previous chunk's tiles are fully consumed
+    if (!PREFETCH) fetch(s0);
+#pragma unroll
+    for (int q = 0; q < NE; ++q) {
+      const int e = tid + q * NTB;
+      xt[(X_S_FAST ? e % SK : e / TB) * LDT + (X_S_FAST ? e / SK : e % TB)] = xr[q];
+      yt[(Y_S_FAST ? e % SK : e / TB) * LDT + (Y_S_FAST ? e / SK : e % TB)] = yr[q];
+    }
     __syncthreads();
+    if (PREFETCH && s0 + SK <= s_hi) fetch(s0 + SK);
 #pragma unroll
     for (int sl = 0; sl < SK; ++sl) {
       const float4 xv = *reinterpret_cast<const float4*>(xt + sl * LDT + ty * 4);
