@@ -41,8 +41,9 @@ def read_peaks():
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return {"hbm_gbs": p.get("hbm_gbs", 6650.0), "sm_max_mhz": p.get("sm_max_mhz", 1965.0), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "source": "fallback"}
+        return {"hbm_gbs": p.get("hbm_gbs", 6650.0), "sm_max_mhz": p.get("sm_max_mhz", 1965.0),
+                "bf16_tflops": p.get("bf16_tflops", 1590.0), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -333,30 +334,38 @@ def main():
     clocks = sampler.stop()
 
     # ---- per-kernel durations for the roofline (this rank's GPU) ---------------------------
-    # The step is dominated by the three TMA-fed FP32 products of the factorised path (forward,
-    # grad_a, grad_b); the library brackets each product launch with CUDA events on request.
+    # The step is dominated by the three TMA-fed products of the factorised path (forward, grad_a,
+    # grad_b), run as 3xTF32 on tcgen05; the library brackets each product launch with CUDA events
+    # on request.  The same products on the FP32 pipe are timed beside them.
     lib = _native.load()
     ad, bd = a.detach(), b.detach()
-    prod_ms = {"fwd_product": [], "grad_a_product": [], "grad_b_product": []}
-    lib.gbmm_profile_enable(1)
-    for _ in range(max(3, min(args.steps, 10))):
-        out_f, rmax, cmax, flg = _native.logbmm_fast_forward(ad, bd)
-        _native.logbmm_fast_backward(ad, bd, ones, out_f, rmax, cmax, flg)
-        for i, k in enumerate(prod_ms):
-            prod_ms[k].append(float(lib.gbmm_profile_last_ms(i)))
-    lib.gbmm_profile_enable(0)
-    flagged_tiles = int(flg.sum().item())
-    kernels = {k: (sorted(v)[len(v) // 2]) / 1e3 for k, v in prod_ms.items()}
+    names = ("fwd_product", "grad_a_product", "grad_b_product")
+
+    def product_ms(tensor_cores):
+        ms = {k: [] for k in names}
+        lib.gbmm_profile_enable(1)
+        for _ in range(max(3, min(args.steps, 10))):
+            out_f, rmax, cmax, flg = _native.logbmm_fast_forward(ad, bd, tensor_cores=tensor_cores)
+            _native.logbmm_fast_backward(ad, bd, ones, out_f, rmax, cmax, flg, tensor_cores=tensor_cores)
+            for i, k in enumerate(names):
+                ms[k].append(float(lib.gbmm_profile_last_ms(i)))
+        lib.gbmm_profile_enable(0)
+        return {k: sorted(v)[len(v) // 2] / 1e3 for k, v in ms.items()}, int(flg.sum().item())
+
+    kernels, flagged_tiles = product_ms(True)
+    kernels_fp32, _ = product_ms(False)
     dominant = max(kernels, key=kernels.get)
     peaks = read_peaks()
-    flops = 2.0 * B * SIZE ** 3  # one FFMA per (m,k,n) triple in each product
+    flops = 2.0 * B * SIZE ** 3                 # one multiply-add per (m,k,n) triple in each product
+    tensor_flops = 3.0 * flops                  # executed on the tensor cores: three TF32 MMAs per triple
+    tf32_peak = peaks["bf16_tflops"] * 1e12 / 2  # dense TF32 runs at half the measured bf16 rate
     fp32_peak = N_SMS * FP32_PER_SM_CLK * 2 * peaks["sm_max_mhz"] * 1e6
-    achieved = flops / kernels[dominant]
+    achieved = tensor_flops / kernels[dominant]
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
         with open(tpath) as f:
-            t = json.load(f).get("sgemm_tn_kernel")
+            t = json.load(f).get("tc_gemm_kernel")
         if t:
             traffic = t["dram_bytes_per_launch"] * (B / t["batch"])
 
@@ -381,15 +390,17 @@ def main():
                 "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e * 1e3},
         "gpu_launches": 13 * args.steps,
         "roofline": {
-            "bound": "fp32", "kernel": "sgemm_tn_kernel (%s)" % dominant, "achieved": achieved / 1e12,
-            "peak": fp32_peak / 1e12, "unit": "TFLOP/s", "frac": achieved / fp32_peak, "traffic": traffic,
-            "peak_source": "148 SMs x 128 FFMA/clk x 2 x sm_max_mhz of MEASURED_PEAKS.json (%s); these are "
-                           "FP32-pipe kernels, neither HBM- nor tensor-bound" % peaks["source"],
+            "bound": "tensor", "kernel": "tc_gemm_kernel (%s)" % dominant, "achieved": achieved / 1e12,
+            "peak": tf32_peak / 1e12, "unit": "TFLOP/s", "frac": achieved / tf32_peak, "traffic": traffic,
+            "peak_source": "dense TF32 = bf16_tflops of MEASURED_PEAKS.json / 2 (%s); achieved counts the "
+                           "executed tensor FLOPs, 3 TF32 MMAs per multiply-add (3xTF32 split)" % peaks["source"],
+            "useful_tflops": flops / kernels[dominant] / 1e12,
             "kernel_ms": {k: v * 1e3 for k, v in kernels.items()},
-            "step_frac_of_fp32_bound": (3.0 * flops / fp32_peak) / (t_log / args.steps),
             "flagged_tiles": flagged_tiles,
         },
-        "also": {"exact_sfu_path_ms_per_step": t_exact * 1e3,
+        "also": {"fp32_pipe_product_ms": {k: v * 1e3 for k, v in kernels_fp32.items()},
+                 "fp32_pipe_product_frac_of_fp32_peak": flops / max(kernels_fp32.values()) / fp32_peak,
+                 "exact_sfu_path_ms_per_step": t_exact * 1e3,
                  "exact_sfu_path_mac_per_s": macs_log / t_exact,
                  "exact_sfu_path_frac_of_sfu_bound": (2.0 * B * SIZE ** 3 / sfu_peak) / t_exact,
                  "maxbmm_fwd_bwd_mac_per_s": world * macs_max * args.steps / t_max,

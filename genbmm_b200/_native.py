@@ -32,6 +32,9 @@ _SIGNATURES = {
     "gbmm_logbmm_forward_f32": ([_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
     "gbmm_logbmm_backward_f32": ([_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
     "gbmm_logbmm_check": ([_P, _P], _I),
+    "gbmm_logbmm_tc_workspace_bytes": ([_I, _L, _L, _L, _L], _L),
+    "gbmm_logbmm_tc_forward_f32": ([_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
+    "gbmm_logbmm_tc_backward_f32": ([_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
     "gbmm_logbmm_forward_noalloc_max_bytes": ([], _L),
     "gbmm_logbmm_forward_noalloc_need_bytes": ([_L, _L, _L, _L], _L),
     "gbmm_logbmm_forward_noalloc_f32": ([_P, _P, _P, _L, _L, _L, _L, _P], _I),
@@ -275,9 +278,10 @@ def _workspace(nbytes, device):
     return torch.empty((max(int(nbytes), 256),), dtype=torch.uint8, device=device)
 
 
-def logbmm_fast_forward(a, b, check=False):
+def logbmm_fast_forward(a, b, check=False, tensor_cores=False):
     """c = logbmm(a, b) by the factorised kernels.  Returns (out, rowmax, colmax, flags); the last
-    three are what `logbmm_fast_backward` needs.  Requires K > 0."""
+    three are what `logbmm_fast_backward` needs.  Requires K > 0.  tensor_cores=True runs the
+    product as 3xTF32 on tcgen05 instead of the FP32 pipe."""
     _check_input(a, "a")
     _check_input(b, "b")
     if a.dim() != 3 or b.dim() != 3 or a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1]:
@@ -290,17 +294,18 @@ def logbmm_fast_forward(a, b, check=False):
         rowmax = torch.empty((B, M), dtype=a.dtype, device=a.device)
         colmax = torch.empty((B, N), dtype=a.dtype, device=a.device)
         flags = torch.empty((max(lib.gbmm_logbmm_flag_count(B, M, N), 1),), dtype=torch.int32, device=a.device)
-        nbytes = lib.gbmm_logbmm_workspace_bytes(0, B, M, K, N)
-        ws = _workspace(nbytes, a.device)
-        st = lib.gbmm_logbmm_forward_f32(_ptr(a), _ptr(b), _ptr(out), _ptr(rowmax), _ptr(colmax), _ptr(flags),
-                                         _ptr(ws), ws.numel(), B, M, K, N, _stream(a.device))
+        sizer = lib.gbmm_logbmm_tc_workspace_bytes if tensor_cores else lib.gbmm_logbmm_workspace_bytes
+        fn = lib.gbmm_logbmm_tc_forward_f32 if tensor_cores else lib.gbmm_logbmm_forward_f32
+        ws = _workspace(sizer(0, B, M, K, N), a.device)
+        st = fn(_ptr(a), _ptr(b), _ptr(out), _ptr(rowmax), _ptr(colmax), _ptr(flags), _ptr(ws), ws.numel(), B, M,
+                K, N, _stream(a.device))
         _check(st, "gbmm_logbmm_forward_f32")
         if check:
             _check(lib.gbmm_logbmm_check(_ptr(ws), _stream(a.device)), "gbmm_logbmm_forward_f32 (device)")
     return out, rowmax, colmax, flags
 
 
-def logbmm_fast_backward(a, b, grad_output, out, rowmax, colmax, flags, check=False):
+def logbmm_fast_backward(a, b, grad_output, out, rowmax, colmax, flags, check=False, tensor_cores=False):
     """(grad_a, grad_b) of logbmm by the factorised kernels, from what the fast forward saved."""
     for x, name in ((a, "a"), (b, "b"), (grad_output, "grad_output"), (out, "out"), (rowmax, "rowmax"),
                     (colmax, "colmax")):
@@ -311,10 +316,11 @@ def logbmm_fast_backward(a, b, grad_output, out, rowmax, colmax, flags, check=Fa
     with torch.cuda.device(a.device):
         grad_a = torch.empty_like(a)
         grad_b = torch.empty_like(b)
-        ws = _workspace(lib.gbmm_logbmm_workspace_bytes(1, B, M, K, N), a.device)
-        st = lib.gbmm_logbmm_backward_f32(_ptr(a), _ptr(b), _ptr(grad_output), _ptr(out), _ptr(rowmax),
-                                          _ptr(colmax), _ptr(flags), _ptr(grad_a), _ptr(grad_b), _ptr(ws),
-                                          ws.numel(), B, M, K, N, _stream(a.device))
+        sizer = lib.gbmm_logbmm_tc_workspace_bytes if tensor_cores else lib.gbmm_logbmm_workspace_bytes
+        fn = lib.gbmm_logbmm_tc_backward_f32 if tensor_cores else lib.gbmm_logbmm_backward_f32
+        ws = _workspace(sizer(1, B, M, K, N), a.device)
+        st = fn(_ptr(a), _ptr(b), _ptr(grad_output), _ptr(out), _ptr(rowmax), _ptr(colmax), _ptr(flags),
+                _ptr(grad_a), _ptr(grad_b), _ptr(ws), ws.numel(), B, M, K, N, _stream(a.device))
         _check(st, "gbmm_logbmm_backward_f32")
         if check:
             _check(lib.gbmm_logbmm_check(_ptr(ws), _stream(a.device)), "gbmm_logbmm_backward_f32 (device)")

@@ -33,6 +33,10 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 
 __host__ __device__ __forceinline__ int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Optional CUDA-event bracket around a product launch (capi.cu; see gbmm_profile_enable).
+bool profile_begin(int slot, cudaStream_t st);
+void profile_end(int slot, cudaStream_t st);
+
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? GBMM_OK : GBMM_ERR_LAUNCH; }
 
 }  // namespace gbmm

@@ -15,4 +15,8 @@ int launch_log_bwd_flagged(const float* a, const float* b, const float* c, const
                            float* grad_b, const int* flags, int64_t B, int64_t M, int64_t K, int64_t N,
                            cudaStream_t st);
 
+// Row maxima of a and column maxima of b for the factorised logbmm (dense_fast.cu).
+int launch_rowcol_max(const float* a, const float* b, float* rowmax, float* colmax, int64_t B, int64_t M, int64_t K,
+                      int64_t N, cudaStream_t st);
+
 }  // namespace gbmm

@@ -355,12 +355,6 @@ __global__ void __launch_bounds__(GNT, 2) sgemm_tn_kernel(const __grid_constant_
   }
 }
 
-// Optional timing of the three product launches (diagnostic; see gbmm_profile_enable).
-bool g_profile = false;
-cudaEvent_t g_events[3][2];
-bool g_event_made[3] = {false, false, false};
-bool g_event_used[3] = {false, false, false};
-
 template <int EPI>
 int launch_gemm(const float* x, int64_t x_pitch, const float* y, int64_t y_pitch, const EpiParams& ep, int64_t B,
                 int64_t R, int64_t I, int64_t J, cudaStream_t st, int slot) {
@@ -373,20 +367,9 @@ int launch_gemm(const float* x, int64_t x_pitch, const float* y, int64_t y_pitch
   auto kernel = sgemm_tn_kernel<EPI, true>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return GBMM_ERR_LAUNCH;
-  const bool timed = g_profile;
-  if (timed) {
-    if (!g_event_made[slot]) {
-      cudaEventCreate(&g_events[slot][0]);
-      cudaEventCreate(&g_events[slot][1]);
-      g_event_made[slot] = true;
-    }
-    cudaEventRecord(g_events[slot][0], st);
-  }
+  const bool timed = profile_begin(slot, st);
   kernel<<<(unsigned)blocks, GNT, smem, st>>>(mx, my, ep, (int)R, (int)I, (int)J, (int)ti, (int)tj);
-  if (timed) {
-    cudaEventRecord(g_events[slot][1], st);
-    g_event_used[slot] = true;
-  }
+  if (timed) profile_end(slot, st);
   return launch_status();
 }
 
@@ -429,6 +412,17 @@ bool big_dims(int64_t M, int64_t K, int64_t N) {
 }  // namespace gbmm
 
 using namespace gbmm;
+
+namespace gbmm {
+// rowmax:(B,M) = max_k a, colmax:(B,N) = max_k b (0 for rows/columns without a finite entry)
+int launch_rowcol_max(const float* a, const float* b, float* rowmax, float* colmax, int64_t B, int64_t M, int64_t K,
+                      int64_t N, cudaStream_t st) {
+  rowmax_kernel<<<(unsigned)ceil_div(B * M, 8), 256, 0, st>>>(a, rowmax, B * M, (int)K);
+  const int64_t tn = ceil_div(N, 32);
+  colmax_kernel<<<(unsigned)(B * tn), 256, 0, st>>>(b, colmax, (int)K, (int)N, (int)tn);
+  return launch_status();
+}
+}  // namespace gbmm
 
 extern "C" int64_t gbmm_logbmm_workspace_bytes(int backward, int64_t B, int64_t M, int64_t K, int64_t N) {
   if (bad_dims(B, M, K, N)) return -1;
@@ -526,21 +520,6 @@ extern "C" int gbmm_logbmm_check(const void* workspace, void* stream) {
     return GBMM_ERR_LAUNCH;
   if (cudaStreamSynchronize(st) != cudaSuccess) return GBMM_ERR_LAUNCH;
   return err ? GBMM_ERR_LAUNCH : GBMM_OK;
-}
-
-// Diagnostic timing of the product kernels of the fast path.  While enabled, every call of
-// gbmm_logbmm_forward_f32 / gbmm_logbmm_backward_f32 brackets its product launch with CUDA
-// events on the call's stream; gbmm_profile_last_ms(which) waits for the latest bracket of
-// which = 0 (forward product), 1 (grad_a product), 2 (grad_b product) and returns its
-// duration in milliseconds, or -1 if there is none.  Not thread-safe; off by default.
-extern "C" void gbmm_profile_enable(int on) { g_profile = on != 0; }
-
-extern "C" float gbmm_profile_last_ms(int which) {
-  if (which < 0 || which > 2 || !g_event_used[which]) return -1.f;
-  float ms = -1.f;
-  if (cudaEventSynchronize(g_events[which][1]) != cudaSuccess) return -1.f;
-  if (cudaEventElapsedTime(&ms, g_events[which][0], g_events[which][1]) != cudaSuccess) return -1.f;
-  return ms;
 }
 
 // ------------------------------------------------------------------ forward without allocation

@@ -1,0 +1,521 @@
+// Tensor-core variant of the factorised logbmm products: 3xTF32 on tcgen05 with TMEM accumulators.
+//
+// The factorised path (dense_fast.cu) turns logbmm and its gradients into ordinary fp32 matrix
+// products of exponentiated operands.  Here those products run on the 5th-generation tensor
+// cores.  TF32 keeps 11 significand bits, too few for the 1e-5 tolerance, so each operand is
+// split once, while it is exponentiated, into hi = tf32(x) and lo = x - hi, and the product is
+// accumulated as  A_lo*B_hi + A_hi*B_lo + A_hi*B_hi  in one fp32 TMEM accumulator (the dropped
+// lo*lo term is below 2^-22 relative).  Per 128x128 result tile and 32-wide reduction stage:
+// four TMA loads (A_hi, A_lo, B_hi, B_lo: 128 rows x 128 bytes each, 128-byte swizzle) and
+// 12 tcgen05.mma.kind::tf32 instructions (M=128, N=128, K=8).
+//
+// CTA = 6 warps: warp 0 issues the TMA loads, warp 1 owns the TMEM allocation and issues the
+// MMAs (one elected lane each), warps 2-5 read the accumulator back with tcgen05.ld (each warp
+// its own 32-lane quarter) and write log(S) + ra + rb (or the gradient) to global memory.
+// The tensor core adds into its fp32 accumulator with truncation, an error that grows with the
+// length of the sum; so the reduction is cut into chunks of 256 steps, each accumulated in one of
+// two TMEM buffers and then added, in round-to-nearest fp32, to per-thread register sums by the
+// epilogue warps while the MMAs fill the other buffer.
+// Stages are handed over with mbarriers (full: TMA -> MMA; empty: tcgen05.commit -> TMA;
+// chunk_full: commit -> epilogue; chunk_empty: epilogue -> MMA).  Every wait is bounded; a wait that gives up sets the error
+// word, and all paths meet at the final barrier so that the TMEM columns are always released.
+// No cluster launch, no multicast, cta_group::1 only.
+#include "dense.cuh"
+#include "tma.cuh"
+
+namespace gbmm {
+namespace {
+
+constexpr int TM = 128, TN = 128, TK = 32, TST = 3, TNT = 192;
+constexpr float kTiny = 8.0779356694631609e-28f;  // 2^-90
+constexpr uint32_t kTileBytes = TM * TK * sizeof(float);  // 16 KB per operand tile
+constexpr uint32_t kTmemCols = 256;  // two 128-column accumulators
+constexpr int TCH = 8;                // stages per accumulation chunk (256 reduction steps)
+
+__host__ __device__ inline int64_t pad4(int64_t x) { return (x + 3) & ~int64_t(3); }
+__host__ __device__ inline int64_t pad64(int64_t x) { return (x + 63) & ~int64_t(63); }
+
+struct alignas(1024) TcSmem {
+  float a_hi[TST][TM * TK];
+  float a_lo[TST][TM * TK];
+  float b_hi[TST][TN * TK];
+  float b_lo[TST][TN * TK];
+  uint64_t full[TST];
+  uint64_t empty[TST];
+  uint64_t chunk_full[2];
+  uint64_t chunk_empty[2];
+  uint32_t tmem_base;
+};
+
+// ---- descriptors -------------------------------------------------------------------------
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): start address / 16 in
+// bits 0-13, leading byte offset (unused for this layout, 1) in bits 16-29, stride between
+// 8-row groups (1024 B) / 16 in bits 32-45, descriptor version 1 in bits 46-47, layout type
+// 2 (128-byte swizzle) in bits 61-63.
+__device__ __forceinline__ uint64_t umma_desc(const void* smem_tile, int k_byte_offset) {
+  const uint32_t addr = smem_u32(smem_tile) + k_byte_offset;
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::tf32, fp32 accumulate, both operands K-major, M=128, N=128:
+// c_format F32 (1) at bit 4, a/b format TF32 (2) at bits 7 and 10, N/8 at bit 17, M/16 at bit 24.
+constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | ((TN >> 3) << 17) | ((TM >> 4) << 24);
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+
+// the mbarrier receives one arrival when every MMA issued so far by this thread has finished
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+      "%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+// TMA load of one (128 rows x 32 fp32) box of a 3-D tensor map into a swizzled tile.
+__device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* map, uint64_t* bar, int k, int row, int bt) {
+  tma_load_3d(dst, map, bar, k, row, bt);
+}
+
+enum { TC_LOG = 0, TC_GRAD = 1 };
+
+struct TcEpi {
+  float* out;          // (batch, I, J)
+  const float* row_v;  // TC_LOG: ra (batch, I);  TC_GRAD: shift by row or null
+  const float* col_v;  // TC_LOG: rb (batch, J);  TC_GRAD: shift by column or null
+  const float* src;    // TC_GRAD: operand whose exponential multiplies the sum
+  int* flags;          // TC_LOG
+  int* error;
+};
+
+// D[i,j] = sum_r A[i,r] B[j,r] with A:(batch,I,R) and B:(batch,J,R), reduction index contiguous.
+template <int EPI>
+__global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap ma_hi,
+                                                         const __grid_constant__ CUtensorMap ma_lo,
+                                                         const __grid_constant__ CUtensorMap mb_hi,
+                                                         const __grid_constant__ CUtensorMap mb_lo, TcEpi ep, int R,
+                                                         int I, int J, int tiles_i, int tiles_j) {
+  extern __shared__ unsigned char smem_raw[];
+  TcSmem& sm = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int64_t id = blockIdx.x;
+  const int j0 = (int)(id % tiles_j) * TN, i0 = (int)((id / tiles_j) % tiles_i) * TM;
+  const int bt = (int)(id / ((int64_t)tiles_j * tiles_i));
+  const int nt = (R + TK - 1) / TK;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < TST; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    for (int q = 0; q < 2; ++q) {
+      mbar_init(&sm.chunk_full[q], 1);
+      mbar_init(&sm.chunk_empty[q], 4);  // one arrival per epilogue warp
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {  // the whole warp allocates; the same warp frees at the end
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  bool fail = false;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int t = 0; t < nt && !fail; ++t) {
+        const int s = t % TST;
+        if (t >= TST && !mbar_wait_bounded(&sm.empty[s], ((t / TST) - 1) & 1)) {
+          fail = true;
+          break;
+        }
+        mbar_arrive_expect_tx(&sm.full[s], 4 * kTileBytes);
+        tma_tile(sm.a_hi[s], &ma_hi, &sm.full[s], t * TK, i0, bt);
+        tma_tile(sm.a_lo[s], &ma_lo, &sm.full[s], t * TK, i0, bt);
+        tma_tile(sm.b_hi[s], &mb_hi, &sm.full[s], t * TK, j0, bt);
+        tma_tile(sm.b_lo[s], &mb_lo, &sm.full[s], t * TK, j0, bt);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int t = 0; t < nt; ++t) {
+        const int s = t % TST, chunk = t / TCH, buf = chunk & 1;
+        const bool chunk_start = (t % TCH) == 0;
+        if (chunk_start && chunk >= 2 && !mbar_wait_bounded(&sm.chunk_empty[buf], ((chunk >> 1) - 1) & 1)) {
+          fail = true;
+          break;
+        }
+        if (!mbar_wait_bounded(&sm.full[s], (t / TST) & 1)) {
+          fail = true;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t acc = tmem + (uint32_t)(buf * TN);
+#pragma unroll
+        for (int kk = 0; kk < TK / 8; ++kk) {
+          const int ko = kk * 8 * (int)sizeof(float);  // 32 bytes per K=8 step inside the 128-byte row
+          const uint64_t ah = umma_desc(sm.a_hi[s], ko), al = umma_desc(sm.a_lo[s], ko);
+          const uint64_t bh = umma_desc(sm.b_hi[s], ko), bl = umma_desc(sm.b_lo[s], ko);
+          umma_tf32(acc, al, bh, (!chunk_start || kk > 0) ? 1u : 0u);
+          umma_tf32(acc, ah, bl, 1u);
+          umma_tf32(acc, ah, bh, 1u);
+        }
+        umma_commit(&sm.empty[s]);  // stage s may be refilled once these MMAs have read it
+        if ((t % TCH) == TCH - 1 || t == nt - 1) umma_commit(&sm.chunk_full[buf]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp % 4;  // TMEM lanes this warp may read: 32*quad .. 32*quad+31
+    float sum[TN];
+#pragma unroll
+    for (int q = 0; q < TN; ++q) sum[q] = 0.f;
+    const int nchunks = (nt + TCH - 1) / TCH;
+    for (int chunk = 0; chunk < nchunks && !fail; ++chunk) {
+      const int buf = chunk & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.chunk_full[buf], (chunk >> 1) & 1))) {
+        fail = true;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < TN / 32; ++c) {
+        float v[32];
+        tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * TN + c * 32), v);
+#pragma unroll
+        for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q];
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.chunk_empty[buf])) : "memory");
+    }
+    const int ii = i0 + quad * 32 + lane;
+    const float rv = (ii < I && ep.row_v) ? __ldg(ep.row_v + (int64_t)bt * I + ii) : 0.f;
+    bool bad = false;
+    if (ii < I && !fail) {
+      float* op = ep.out + ((int64_t)bt * I + ii) * J + j0;
+#pragma unroll
+      for (int q = 0; q < TN; ++q) {
+        const int jj = j0 + q;
+        if (jj < J) {
+          const float cv = ep.col_v ? __ldg(ep.col_v + (int64_t)bt * J + jj) : 0.f;
+          if (EPI == TC_LOG) {
+            const float shift = rv + cv;
+            bad |= !(sum[q] >= kTiny) || !(sum[q] <= 3.0e38f) || (shift < kFloor);
+            op[q] = logf(sum[q]) + shift;
+          } else {
+            const float x = __ldg(ep.src + ((int64_t)bt * I + ii) * J + jj);
+            op[q] = exp_sfu(x - (rv + cv)) * sum[q];
+          }
+        }
+      }
+    }
+    if (EPI == TC_LOG) {
+      // flags were zeroed before the launch; any epilogue warp that saw a bad sum raises the tile's
+      if (__any_sync(0xffffffffu, bad) && lane == 0) atomicExch(ep.flags + blockIdx.x, 1);
+    }
+  }
+  if (__any_sync(0xffffffffu, fail) && lane == 0) atomicExch(ep.error, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- exponentiate + split ------------------------------------------------------------------
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// 64x64 tiles of a (batch, R, C) tensor: v = transform(src), then hi = tf32(v), lo = v - hi written
+// in the same orientation (n_hi/n_lo, pitch pad4(C)) and/or transposed (t_hi/t_lo: (batch, C, R),
+// pitch pad4(R)); null destinations are skipped.  KIND as in dense_fast.cu:
+//   0: exp(src - shift[r])   1: exp(src - shift[c])   2: g * exp(shift[r] + shift2[c] - src), 0 if flagged
+// VEC: C % 4 == 0 and every pointer 16-byte aligned -> 128-bit loads and stores.
+struct SplitDst {
+  float* n_hi;
+  float* n_lo;
+  float* t_hi;
+  float* t_lo;
+};
+
+template <int KIND, bool VEC>
+__global__ void __launch_bounds__(256) split_transform_kernel(const float* __restrict__ src,
+                                                              const float* __restrict__ shift,
+                                                              const float* __restrict__ shift2,
+                                                              const float* __restrict__ g,
+                                                              const int* __restrict__ flags, SplitDst d, int R, int C,
+                                                              int tiles_r, int tiles_c) {
+  __shared__ float tile[64][65];
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  const int64_t id = blockIdx.x;
+  const int c0 = (int)(id % tiles_c) * 64, r0 = (int)((id / tiles_c) % tiles_r) * 64;
+  const int64_t bt = id / ((int64_t)tiles_c * tiles_r);
+  const float* sb = src + bt * R * C;
+  const float* gb = KIND == 2 ? g + bt * R * C : nullptr;
+  const int64_t pc = pad4(C), pr = pad4(R);
+  bool dead = false;
+  if (KIND == 2) dead = __ldg(flags + (bt * ((R + 127) / 128) + r0 / 128) * ((C + 127) / 128) + c0 / 128) != 0;
+  const int c = c0 + tx * 4;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int rl = ty + q * 16, r = r0 + rl;
+    float x[4] = {0.f, 0.f, 0.f, 0.f}, gv[4] = {0.f, 0.f, 0.f, 0.f}, v[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool row_ok = r < R;
+    if (row_ok) {
+      if (VEC) {
+        if (c < C) {
+          const float4 t = __ldg(reinterpret_cast<const float4*>(sb + (int64_t)r * C + c));
+          x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+          if (KIND == 2) {
+            const float4 u = __ldg(reinterpret_cast<const float4*>(gb + (int64_t)r * C + c));
+            gv[0] = u.x; gv[1] = u.y; gv[2] = u.z; gv[3] = u.w;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (c + k < C) {
+            x[k] = __ldg(sb + (int64_t)r * C + c + k);
+            if (KIND == 2) gv[k] = __ldg(gb + (int64_t)r * C + c + k);
+          }
+      }
+      const float sr = KIND != 1 ? __ldg(shift + bt * R + r) : 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (c + k < C) {
+          if (KIND == 0) v[k] = exp_sfu(x[k] - sr);
+          if (KIND == 1) v[k] = exp_sfu(x[k] - __ldg(shift + bt * C + c + k));
+          if (KIND == 2) v[k] = dead ? 0.f : gv[k] * exp_sfu((sr + __ldg(shift2 + bt * C + c + k)) - x[k]);
+        }
+      if (d.n_hi) {
+        float hi[4], lo[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          hi[k] = tf32_round(v[k]);
+          lo[k] = v[k] - hi[k];
+        }
+        float* ph = d.n_hi + (bt * R + r) * pc + c;
+        float* pl = d.n_lo + (bt * R + r) * pc + c;
+        if (c < C) {  // pitch pad4(C): a group that straddles C lands in the row's padding
+          *reinterpret_cast<float4*>(ph) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<float4*>(pl) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) tile[rl][tx * 4 + k] = v[k];
+  }
+  if (d.t_hi) {
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int cl = ty + q * 16, cc = c0 + cl, r = r0 + tx * 4;
+      if (cc < C && r < R) {
+        float hi[4], lo[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float v = tile[tx * 4 + k][cl];
+          hi[k] = tf32_round(v);
+          lo[k] = v - hi[k];
+        }
+        *reinterpret_cast<float4*>(d.t_hi + (bt * C + cc) * pr + r) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<float4*>(d.t_lo + (bt * C + cc) * pr + r) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+      }
+    }
+  }
+}
+
+template <int KIND>
+int launch_split(const float* src, const float* shift, const float* shift2, const float* g, const int* flags,
+                 const SplitDst& d, int64_t B, int64_t R, int64_t C, cudaStream_t st) {
+  const int64_t tr = ceil_div(R, 64), tcn = ceil_div(C, 64), blocks = B * tr * tcn;
+  if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = (C % 4 == 0) && al16(src) && (!g || al16(g));
+  if (vec)
+    split_transform_kernel<KIND, true><<<(unsigned)blocks, 256, 0, st>>>(src, shift, shift2, g, flags, d, (int)R,
+                                                                        (int)C, (int)tr, (int)tcn);
+  else
+    split_transform_kernel<KIND, false><<<(unsigned)blocks, 256, 0, st>>>(src, shift, shift2, g, flags, d, (int)R,
+                                                                         (int)C, (int)tr, (int)tcn);
+  return launch_status();
+}
+
+// (batch, rows, cols) fp32, pitch % 4 == 0; boxes of 128 rows x 32 columns, 128-byte swizzle
+bool make_map_sw128(CUtensorMap* map, const float* base, uint64_t batch, uint64_t rows, uint64_t cols,
+                    uint64_t pitch) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch & 3)) return false;
+  const cuuint64_t dims[3] = {cols, rows, batch};
+  const cuuint64_t strides[2] = {pitch * sizeof(float), rows * pitch * sizeof(float)};
+  const cuuint32_t box[3] = {TK, TM, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int EPI>
+int launch_tc(const float* a_hi, const float* a_lo, int64_t a_pitch, const float* b_hi, const float* b_lo,
+              int64_t b_pitch, const TcEpi& ep, int64_t B, int64_t R, int64_t I, int64_t J, cudaStream_t st,
+              int slot) {
+  CUtensorMap m0, m1, m2, m3;
+  if (!make_map_sw128(&m0, a_hi, B, I, R, a_pitch) || !make_map_sw128(&m1, a_lo, B, I, R, a_pitch) ||
+      !make_map_sw128(&m2, b_hi, B, J, R, b_pitch) || !make_map_sw128(&m3, b_lo, B, J, R, b_pitch))
+    return GBMM_ERR_LAUNCH;
+  const int64_t ti = ceil_div(I, TM), tj = ceil_div(J, TN), blocks = B * ti * tj;
+  if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  const size_t smem = sizeof(TcSmem) + 1024;
+  if (cudaFuncSetAttribute(tc_gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return GBMM_ERR_LAUNCH;
+  const bool timed = profile_begin(slot, st);
+  tc_gemm_kernel<EPI><<<(unsigned)blocks, TNT, smem, st>>>(m0, m1, m2, m3, ep, (int)R, (int)I, (int)J, (int)ti,
+                                                          (int)tj);
+  if (timed) profile_end(slot, st);
+  return launch_status();
+}
+
+float* carve(float*& cursor, int64_t floats) {
+  float* p = cursor;
+  cursor += pad64(floats);
+  return p;
+}
+
+}  // namespace
+}  // namespace gbmm
+
+using namespace gbmm;
+
+extern "C" int64_t gbmm_logbmm_tc_workspace_bytes(int backward, int64_t B, int64_t M, int64_t K, int64_t N) {
+  if (B < 0 || M < 0 || K < 0 || N < 0) return -1;
+  int64_t floats = 64;
+  if (!backward)
+    floats += 2 * pad64(B * M * pad4(K)) + 2 * pad64(B * N * pad4(K));
+  else
+    floats += 2 * (pad64(B * M * pad4(N)) + pad64(B * K * pad4(N)) + pad64(B * K * pad4(M)) + pad64(B * N * pad4(M)));
+  return floats * (int64_t)sizeof(float);
+}
+
+extern "C" int gbmm_logbmm_tc_forward_f32(const float* a, const float* b, float* out, float* rowmax, float* colmax,
+                                          int32_t* flags, void* workspace, int64_t workspace_bytes, int64_t B,
+                                          int64_t M, int64_t K, int64_t N, void* stream) {
+  if (B < 0 || M < 0 || K < 0 || N < 0) return GBMM_ERR_INVALID_ARG;
+  if (B == 0 || M == 0 || N == 0) return GBMM_OK;
+  if (K == 0) return GBMM_ERR_UNSUPPORTED;
+  if (!a || !b || !out || !rowmax || !colmax || !flags || !workspace) return GBMM_ERR_INVALID_ARG;
+  const int64_t lim = (1LL << 31) - 256;
+  if (M >= lim || K >= lim || N >= lim) return GBMM_ERR_UNSUPPORTED;
+  if (workspace_bytes < gbmm_logbmm_tc_workspace_bytes(0, B, M, K, N)) return GBMM_ERR_INVALID_ARG;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return GBMM_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* cur = static_cast<float*>(workspace);
+  int* error = reinterpret_cast<int*>(carve(cur, 64));
+  float* ea_hi = carve(cur, B * M * pad4(K));
+  float* ea_lo = carve(cur, B * M * pad4(K));
+  float* ebt_hi = carve(cur, B * N * pad4(K));
+  float* ebt_lo = carve(cur, B * N * pad4(K));
+  if (cudaMemsetAsync(error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
+  int rc = launch_rowcol_max(a, b, rowmax, colmax, B, M, K, N, st);
+  if (rc != GBMM_OK) return rc;
+  rc = launch_split<0>(a, rowmax, nullptr, nullptr, nullptr, SplitDst{ea_hi, ea_lo, nullptr, nullptr}, B, M, K, st);
+  if (rc != GBMM_OK) return rc;
+  rc = launch_split<1>(b, colmax, nullptr, nullptr, nullptr, SplitDst{nullptr, nullptr, ebt_hi, ebt_lo}, B, K, N, st);
+  if (rc != GBMM_OK) return rc;
+  if (cudaMemsetAsync(flags, 0, sizeof(int) * B * ceil_div(M, TM) * ceil_div(N, TN), st) != cudaSuccess)
+    return GBMM_ERR_LAUNCH;
+  TcEpi ep{out, rowmax, colmax, nullptr, flags, error};
+  rc = launch_tc<TC_LOG>(ea_hi, ea_lo, pad4(K), ebt_hi, ebt_lo, pad4(K), ep, B, K, M, N, st, 0);
+  if (rc != GBMM_OK) return rc;
+  return launch_log_fwd_flagged(a, b, out, flags, B, M, K, N, st);
+}
+
+extern "C" int gbmm_logbmm_tc_backward_f32(const float* a, const float* b, const float* grad_out, const float* out,
+                                           const float* rowmax, const float* colmax, const int32_t* flags,
+                                           float* grad_a, float* grad_b, void* workspace, int64_t workspace_bytes,
+                                           int64_t B, int64_t M, int64_t K, int64_t N, void* stream) {
+  if (B < 0 || M < 0 || K < 0 || N < 0) return GBMM_ERR_INVALID_ARG;
+  if (B == 0 || K == 0) return GBMM_OK;
+  if (M == 0 || N == 0) return GBMM_ERR_UNSUPPORTED;
+  if (!a || !b || !grad_out || !out || !rowmax || !colmax || !flags || !workspace) return GBMM_ERR_INVALID_ARG;
+  const int64_t lim = (1LL << 31) - 256;
+  if (M >= lim || K >= lim || N >= lim) return GBMM_ERR_UNSUPPORTED;
+  if (workspace_bytes < gbmm_logbmm_tc_workspace_bytes(1, B, M, K, N)) return GBMM_ERR_INVALID_ARG;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return GBMM_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* cur = static_cast<float*>(workspace);
+  int* error = reinterpret_cast<int*>(carve(cur, 64));
+  float* gp_hi = carve(cur, B * M * pad4(N));   // G'   : (B, M, pad4(N))
+  float* gp_lo = carve(cur, B * M * pad4(N));
+  float* eb_hi = carve(cur, B * K * pad4(N));   // EB   : (B, K, pad4(N))
+  float* eb_lo = carve(cur, B * K * pad4(N));
+  float* eat_hi = carve(cur, B * K * pad4(M));  // EA^T : (B, K, pad4(M))
+  float* eat_lo = carve(cur, B * K * pad4(M));
+  float* gt_hi = carve(cur, B * N * pad4(M));   // G'^T : (B, N, pad4(M))
+  float* gt_lo = carve(cur, B * N * pad4(M));
+  if (cudaMemsetAsync(error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
+  int rc = launch_split<2>(out, rowmax, colmax, grad_out, flags,
+                           SplitDst{grad_a ? gp_hi : nullptr, gp_lo, grad_b ? gt_hi : nullptr, gt_lo}, B, M, N, st);
+  if (rc != GBMM_OK) return rc;
+  if (grad_a) {
+    // grad_a[m,k] = EA[m,k] * sum_n G'[m,n] EB[k,n]
+    rc = launch_split<1>(b, colmax, nullptr, nullptr, nullptr, SplitDst{eb_hi, eb_lo, nullptr, nullptr}, B, K, N, st);
+    if (rc != GBMM_OK) return rc;
+    TcEpi ep{grad_a, rowmax, nullptr, a, nullptr, error};
+    rc = launch_tc<TC_GRAD>(gp_hi, gp_lo, pad4(N), eb_hi, eb_lo, pad4(N), ep, B, N, M, K, st, 1);
+    if (rc != GBMM_OK) return rc;
+  }
+  if (grad_b) {
+    // grad_b[k,n] = EB[k,n] * sum_m EA[m,k] G'[m,n]
+    rc = launch_split<0>(a, rowmax, nullptr, nullptr, nullptr, SplitDst{nullptr, nullptr, eat_hi, eat_lo}, B, M, K,
+                         st);
+    if (rc != GBMM_OK) return rc;
+    TcEpi ep{grad_b, nullptr, colmax, b, nullptr, error};
+    rc = launch_tc<TC_GRAD>(eat_hi, eat_lo, pad4(M), gt_hi, gt_lo, pad4(M), ep, B, M, K, N, st, 2);
+    if (rc != GBMM_OK) return rc;
+  }
+  return launch_log_bwd_flagged(a, b, out, grad_out, grad_a, grad_b, flags, B, M, K, N, st);
+}

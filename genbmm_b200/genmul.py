@@ -30,20 +30,26 @@ def _as_f32(x, name):
     raise RuntimeError("%s: dtype %s is not supported by the fp32 kernels" % (name, x.dtype))
 
 
-def _use_fast_log(M, K, N):
-    """The factorised kernels pay off once the product is big enough to amortise their four
-    small preparation kernels; GENBMM_B200_LOGBMM=exact|fast overrides the size rule."""
+def _log_path(M, K, N):
+    """Which kernels logbmm uses: "exact" (SFU, one exponential per term), "fp32" (factorised
+    products on the FP32 pipe) or "tensor" (factorised products as 3xTF32 on tcgen05).  The
+    factorised paths pay off once the product amortises their preparation kernels; the tensor
+    cores are the default for those.  GENBMM_B200_LOGBMM=exact|fp32|tensor overrides the rule."""
     mode = os.environ.get("GENBMM_B200_LOGBMM", "auto")
     if K == 0 or M == 0 or N == 0 or mode == "exact":
-        return False
-    return mode == "fast" or M * K * N >= 128 * 128 * 64
+        return "exact"
+    if mode in ("fp32", "fast"):
+        return "fp32"
+    if mode == "tensor":
+        return "tensor"
+    return "tensor" if M * K * N >= 128 * 128 * 64 else "exact"
 
 
 class LogMatMulBack(torch.autograd.Function):
     """First-order gradients of logbmm as a differentiable node (genmul.py:11-24).
 
     forward returns (grad_a, grad_b) in one call.  `aux` is None after the exact forward, or
-    the (rowmax, colmax, flags) triple of the factorised forward.
+    (rowmax, colmax, flags, tensor_cores) of the factorised forward.
     """
 
     @staticmethod
@@ -52,7 +58,7 @@ class LogMatMulBack(torch.autograd.Function):
         if aux is None:
             grad_a, grad_b = _native.backward(a, b, grad_out, part, None, _native.MODE_LOG)
         else:
-            grad_a, grad_b = _native.logbmm_fast_backward(a, b, grad_out, part, *aux)
+            grad_a, grad_b = _native.logbmm_fast_backward(a, b, grad_out, part, *aux[:3], tensor_cores=aux[3])
         return grad_a, grad_b
 
     @staticmethod
@@ -69,9 +75,11 @@ class LogMatMul(torch.autograd.Function):
     def forward(ctx, a, b):
         a32, b32 = _as_f32(a, "a"), _as_f32(b, "b")
         ctx.aux = None
-        if a32.dim() == 3 and b32.dim() == 3 and _use_fast_log(a32.shape[1], a32.shape[2], b32.shape[-1]):
-            out, rowmax, colmax, flags = _native.logbmm_fast_forward(a32, b32)
-            ctx.aux = (rowmax, colmax, flags)
+        path = _log_path(a32.shape[1], a32.shape[2], b32.shape[-1]) if a32.dim() == 3 and b32.dim() == 3 else "exact"
+        if path != "exact":
+            tc = path == "tensor"
+            out, rowmax, colmax, flags = _native.logbmm_fast_forward(a32, b32, tensor_cores=tc)
+            ctx.aux = (rowmax, colmax, flags, tc)
         else:
             out, _ = _native.forward(a32, b32, _native.MODE_LOG, want_maxes=False)
         ctx.save_for_backward(a32, b32, out)

@@ -158,6 +158,22 @@ int gbmm_logbmm_backward_f32(const float* a, const float* b, const float* grad_o
 int gbmm_logbmm_check(const void* workspace, void* stream);
 
 /*
+ * Tensor-core variants of gbmm_logbmm_forward_f32 / _backward_f32: the same factorised products computed as
+ * 3xTF32 on tcgen05 (each exponentiated operand split into tf32 hi + lo parts; accumulators in
+ * TMEM).  Same arguments and outputs; its own, larger workspace
+ * (gbmm_logbmm_tc_workspace_bytes).  rowmax / colmax / flags are interchangeable with the ones of
+ * gbmm_logbmm_forward_f32 for the purposes of gbmm_logbmm_backward_f32.
+ */
+int64_t gbmm_logbmm_tc_workspace_bytes(int backward, int64_t B, int64_t M, int64_t K, int64_t N);
+int gbmm_logbmm_tc_forward_f32(const float* a, const float* b, float* out, float* rowmax, float* colmax,
+                               int32_t* flags, void* workspace, int64_t workspace_bytes,
+                               int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+int gbmm_logbmm_tc_backward_f32(const float* a, const float* b, const float* grad_out, const float* out,
+                                const float* rowmax, const float* colmax, const int32_t* flags,
+                                float* grad_a, float* grad_b, void* workspace, int64_t workspace_bytes,
+                                int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+
+/*
  * logbmm forward for callers that cannot allocate device memory.  (No counterpart in the
  * reference, whose every entry point allocates its outputs with torch.)
  *

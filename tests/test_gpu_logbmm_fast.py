@@ -19,20 +19,21 @@ def nat():
     return _native
 
 
-def fast_fwd_bwd(nat, a, b, g):
+def fast_fwd_bwd(nat, a, b, g, tc=False):
     ad, bd, gd = a.cuda(), b.cuda(), g.cuda()
-    out, rowmax, colmax, flags = nat.logbmm_fast_forward(ad, bd, check=True)
-    ga, gb = nat.logbmm_fast_backward(ad, bd, gd, out, rowmax, colmax, flags, check=True)
+    out, rowmax, colmax, flags = nat.logbmm_fast_forward(ad, bd, check=True, tensor_cores=tc)
+    ga, gb = nat.logbmm_fast_backward(ad, bd, gd, out, rowmax, colmax, flags, check=True, tensor_cores=tc)
     return out, ga, gb, flags
 
 
+@pytest.mark.parametrize("tc", [False, True], ids=["fp32", "tcgen05"])
 @pytest.mark.parametrize("shape", SHAPES)
-def test_fast_path_matches_oracle(nat, shape):
+def test_fast_path_matches_oracle(nat, shape, tc):
     B, M, K, N = shape
     gen = torch.Generator().manual_seed(sum(shape))
     a, b = torch.randn(B, M, K, generator=gen), torch.randn(B, K, N, generator=gen)
     g = torch.randn(B, M, N, generator=gen)
-    out, ga, gb, flags = fast_fwd_bwd(nat, a, b, g)
+    out, ga, gb, flags = fast_fwd_bwd(nat, a, b, g, tc)
     want, maxes = oracle.dense_fwd(0, a, b, dtype=np.float64)
     dA, dB = oracle.dense_bwd(0, a, b, g, want, maxes, dtype=np.float64)
     assert int(flags.sum()) == 0          # well-conditioned inputs never need the guard
@@ -44,7 +45,8 @@ def test_fast_path_matches_oracle(nat, shape):
     assert torch.allclose(out, exact, rtol=1e-5, atol=2e-6)
 
 
-def test_guard_recomputes_underflowing_tiles(nat):
+@pytest.mark.parametrize("tc", [False, True], ids=["fp32", "tcgen05"])
+def test_guard_recomputes_underflowing_tiles(nat, tc):
     """Row and column supports that do not meet: row maximum + column maximum overshoots the true
     maximum by hundreds of nats, the factorised sum underflows, the tile is flagged and redone."""
     gen = torch.Generator().manual_seed(1)
@@ -53,7 +55,7 @@ def test_guard_recomputes_underflowing_tiles(nat):
     g = torch.rand(B, M, N, generator=gen)
     a[:, :60, :48] -= 400.0      # rows 0..59 live on k >= 48 ...
     b[:, 48:, :70] -= 400.0      # ... columns 0..69 live on k < 48
-    out, ga, gb, flags = fast_fwd_bwd(nat, a, b, g)
+    out, ga, gb, flags = fast_fwd_bwd(nat, a, b, g, tc)
     nflag = int(flags.sum())
     assert 0 < nflag < flags.numel()      # some tiles take the exact kernels, some the fast ones
     want, maxes = oracle.dense_fwd(0, a, b, dtype=np.float64)
@@ -107,12 +109,33 @@ def test_autograd_uses_fast_path_for_large_products(monkeypatch):
     a, b = torch.randn(2, 192, 160, generator=gen), torch.randn(2, 160, 136, generator=gen)
     g = torch.rand(2, 192, 136, generator=gen)
     res = {}
-    for mode in ("fast", "exact"):
+    for mode in ("tensor", "fp32", "exact"):
         monkeypatch.setenv("GENBMM_B200_LOGBMM", mode)
         ad, bd = a.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
         c = gb.logbmm(ad, bd)
         res[mode] = (c.detach(),) + torch.autograd.grad(c, (ad, bd), g.cuda())
-    for x, y in zip(res["fast"], res["exact"]):
-        assert torch.allclose(x, y, rtol=1e-5, atol=5e-6)
+    for mode in ("tensor", "fp32"):
+        for x, y in zip(res[mode], res["exact"]):
+            assert torch.allclose(x, y, rtol=1e-5, atol=5e-6)
     want, maxes = oracle.dense_fwd(0, a, b, dtype=np.float64)
-    assert_close(res["fast"][0], want)
+    assert_close(res["tensor"][0], want)
+    assert_close(res["fp32"][0], want)
+
+
+def test_tensor_core_path_at_the_benchmark_shape(nat):
+    """1024^3: 3xTF32 on tcgen05 against the float64 oracle on a slice and against the FP32-pipe path."""
+    gen = torch.Generator().manual_seed(9)
+    a, b = torch.randn(2, 1024, 1024, generator=gen), torch.randn(2, 1024, 1024, generator=gen)
+    g = torch.randn(2, 1024, 1024, generator=gen)
+    out, ga, gb, flags = fast_fwd_bwd(nat, a, b, g, tc=True)
+    ref, ra, rb, _ = fast_fwd_bwd(nat, a, b, g, tc=False)
+    assert int(flags.sum()) == 0
+    want, maxes = oracle.dense_fwd(0, a[:1, :96], b[:1], dtype=np.float64)
+    dA, _ = oracle.dense_bwd(0, a[:1, :96], b[:1], g[:1, :96], want, maxes, dtype=np.float64)
+    assert_close(out[:1, :96], want, what="fwd")
+    assert_close(ga[:1, :96], dA, 1e-5, 1e-5, what="grad_a")
+    assert torch.allclose(out, ref, rtol=1e-5, atol=2e-6)
+    # mixed-sign cotangents: each gradient is a sum of 1024 terms of both signs, so the two paths
+    # are compared against the size of the terms (about 1e-2 .. 1 here), not of the cancelled sum
+    print("max |tc - fp32| grad_a %.3e grad_b %.3e" % ((ga - ra).abs().max().item(), (gb - rb).abs().max().item()))
+    assert torch.allclose(ga, ra, rtol=1e-5, atol=5e-5) and torch.allclose(gb, rb, rtol=1e-5, atol=5e-5)
