@@ -26,7 +26,10 @@
 namespace gbmm {
 namespace {
 
-constexpr int TM = 128, TN = 128, TK = 32, TST = 3, TNT = 192;
+constexpr int TM = 128, TN = 128, TK = 32, TST = 3;
+constexpr int TEW = 8;                 // epilogue warps: two per TMEM lane quarter, 64 columns each
+constexpr int TNT = (2 + TEW) * 32;
+constexpr int TEC = TN * 4 / TEW;      // columns per epilogue warp
 constexpr float kTiny = 8.0779356694631609e-28f;  // 2^-90
 constexpr uint32_t kTileBytes = TM * TK * sizeof(float);  // 16 KB per operand tile
 constexpr uint32_t kTmemCols = 256;  // two 128-column accumulators
@@ -141,7 +144,7 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
     }
     for (int q = 0; q < 2; ++q) {
       mbar_init(&sm.chunk_full[q], 1);
-      mbar_init(&sm.chunk_empty[q], 4);  // one arrival per epilogue warp
+      mbar_init(&sm.chunk_empty[q], TEW);  // one arrival per epilogue warp
     }
     fence_barrier_init();
   }
@@ -204,9 +207,10 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
     __syncwarp();
   } else {
     const int quad = warp % 4;  // TMEM lanes this warp may read: 32*quad .. 32*quad+31
-    float sum[TN];
+    const int cbase = ((warp - 2) / 4) * TEC;  // first of this warp's columns
+    float sum[TEC];
 #pragma unroll
-    for (int q = 0; q < TN; ++q) sum[q] = 0.f;
+    for (int q = 0; q < TEC; ++q) sum[q] = 0.f;
     const int nchunks = (nt + TCH - 1) / TCH;
     for (int chunk = 0; chunk < nchunks && !fail; ++chunk) {
       const int buf = chunk & 1;
@@ -216,9 +220,9 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
       }
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < TN / 32; ++c) {
+      for (int c = 0; c < TEC / 32; ++c) {
         float v[32];
-        tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * TN + c * 32), v);
+        tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * TN + cbase + c * 32), v);
 #pragma unroll
         for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q];
       }
@@ -227,24 +231,64 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
       if (lane == 0)
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.chunk_empty[buf])) : "memory");
     }
-    const int ii = i0 + quad * 32 + lane;
-    const float rv = (ii < I && ep.row_v) ? __ldg(ep.row_v + (int64_t)bt * I + ii) : 0.f;
+    // Hand the sums over through shared memory (the pipeline stages are idle by now) so that
+    // global memory is touched along rows: lane = row when writing the warp's private 32x64 block,
+    // half a warp per row (16 lanes x 4 columns) when reading it back.
     bool bad = false;
-    if (ii < I && !fail) {
-      float* op = ep.out + ((int64_t)bt * I + ii) * J + j0;
+    if (!fail) {
+      float* blk = reinterpret_cast<float*>(&sm.a_hi[0][0]) + (warp - 2) * (32 * (TEC + 1));
 #pragma unroll
-      for (int q = 0; q < TN; ++q) {
-        const int jj = j0 + q;
-        if (jj < J) {
-          const float cv = ep.col_v ? __ldg(ep.col_v + (int64_t)bt * J + jj) : 0.f;
-          if (EPI == TC_LOG) {
-            const float shift = rv + cv;
-            bad |= !(sum[q] >= kTiny) || !(sum[q] <= 3.0e38f) || (shift < kFloor);
-            op[q] = logf(sum[q]) + shift;
-          } else {
-            const float x = __ldg(ep.src + ((int64_t)bt * I + ii) * J + jj);
-            op[q] = exp_sfu(x - (rv + cv)) * sum[q];
+      for (int q = 0; q < TEC; ++q) blk[lane * (TEC + 1) + q] = sum[q];
+      __syncwarp();
+      const int hl = lane % 16, hr = lane / 16;
+      const bool vec = (J % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) &&
+                       (!ep.src || (reinterpret_cast<uintptr_t>(ep.src) & 15) == 0) &&
+                       (!ep.col_v || (reinterpret_cast<uintptr_t>(ep.col_v) & 15) == 0);
+#pragma unroll 4
+      for (int it = 0; it < 16; ++it) {
+        const int r = it * 2 + hr;
+        const int ii = i0 + quad * 32 + r;
+        const int jj = j0 + cbase + hl * 4;
+        if (ii >= I || jj >= J) continue;
+        float v[4], cv[4] = {0.f, 0.f, 0.f, 0.f}, x[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = blk[r * (TEC + 1) + hl * 4 + k];
+        const float rv = ep.row_v ? __ldg(ep.row_v + (int64_t)bt * I + ii) : 0.f;
+        const int64_t orow = ((int64_t)bt * I + ii) * J;
+        const bool full4 = vec && jj + 3 < J;
+        if (full4) {
+          if (ep.col_v) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(ep.col_v + (int64_t)bt * J + jj));
+            cv[0] = t.x; cv[1] = t.y; cv[2] = t.z; cv[3] = t.w;
           }
+          if (EPI == TC_GRAD) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(ep.src + orow + jj));
+            x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (jj + k < J) {
+              if (ep.col_v) cv[k] = __ldg(ep.col_v + (int64_t)bt * J + jj + k);
+              if (EPI == TC_GRAD) x[k] = __ldg(ep.src + orow + jj + k);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (EPI == TC_LOG) {
+            const float shift = rv + cv[k];
+            if (jj + k < J) bad |= !(v[k] >= kTiny) || !(v[k] <= 3.0e38f) || (shift < kFloor);
+            o[k] = __logf(v[k]) + shift;  // lg2.approx: absolute error below 2e-7 on the logarithm
+          } else {
+            o[k] = exp_sfu(x[k] - (rv + cv[k])) * v[k];
+          }
+        }
+        if (full4) {
+          *reinterpret_cast<float4*>(ep.out + orow + jj) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (jj + k < J) ep.out[orow + jj + k] = o[k];
         }
       }
     }
