@@ -32,7 +32,8 @@ constexpr int TNT = (2 + TEW) * 32;
 constexpr int TEC = TN * 4 / TEW;      // columns per epilogue warp
 constexpr float kTiny = 8.0779356694631609e-28f;  // 2^-90
 constexpr uint32_t kTileBytes = TM * TK * sizeof(float);  // 16 KB per operand tile
-constexpr uint32_t kTmemCols = 256;  // two 128-column accumulators
+constexpr int TNB = 4;                 // TMEM accumulation buffers of 128 columns
+constexpr uint32_t kTmemCols = TNB * 128;
 constexpr int TCH = 8;                // stages per accumulation chunk (256 reduction steps)
 
 __host__ __device__ inline int64_t pad4(int64_t x) { return (x + 3) & ~int64_t(3); }
@@ -43,10 +44,11 @@ struct alignas(1024) TcSmem {
   float a_lo[TST][TM * TK];
   float b_hi[TST][TN * TK];
   float b_lo[TST][TN * TK];
+  float epi[TEW][32 * 33];  // per epilogue warp: a 32x32 block on its way to global memory
   uint64_t full[TST];
   uint64_t empty[TST];
-  uint64_t chunk_full[2];
-  uint64_t chunk_empty[2];
+  uint64_t chunk_full[TNB];
+  uint64_t chunk_empty[TNB];
   uint32_t tmem_base;
 };
 
@@ -122,19 +124,21 @@ struct TcEpi {
 };
 
 // D[i,j] = sum_r A[i,r] B[j,r] with A:(batch,I,R) and B:(batch,J,R), reduction index contiguous.
+// Persistent: the grid has one CTA per SM and CTA c takes tiles c, c + gridDim.x, ...; the three
+// roles keep running stage and chunk counters across tiles, so the loads and MMAs of the next tile
+// proceed (up to TNB chunks ahead) while the epilogue warps are still writing the previous one.
 template <int EPI>
 __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap ma_hi,
                                                          const __grid_constant__ CUtensorMap ma_lo,
                                                          const __grid_constant__ CUtensorMap mb_hi,
                                                          const __grid_constant__ CUtensorMap mb_lo, TcEpi ep, int R,
-                                                         int I, int J, int tiles_i, int tiles_j) {
+                                                         int I, int J, int tiles_i, int tiles_j,
+                                                         int64_t total_tiles) {
   extern __shared__ unsigned char smem_raw[];
   TcSmem& sm = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int64_t id = blockIdx.x;
-  const int j0 = (int)(id % tiles_j) * TN, i0 = (int)((id / tiles_j) % tiles_i) * TM;
-  const int bt = (int)(id / ((int64_t)tiles_j * tiles_i));
   const int nt = (R + TK - 1) / TK;
+  const int nchunks = (nt + TCH - 1) / TCH;
 
   if (tid == 0) {
 #pragma unroll
@@ -142,7 +146,8 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], 1);
     }
-    for (int q = 0; q < 2; ++q) {
+#pragma unroll
+    for (int q = 0; q < TNB; ++q) {
       mbar_init(&sm.chunk_full[q], 1);
       mbar_init(&sm.chunk_empty[q], TEW);  // one arrival per epilogue warp
     }
@@ -162,140 +167,161 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int t = 0; t < nt && !fail; ++t) {
-        const int s = t % TST;
-        if (t >= TST && !mbar_wait_bounded(&sm.empty[s], ((t / TST) - 1) & 1)) {
-          fail = true;
-          break;
+      uint32_t it = 0;  // stages issued so far, over all tiles of this CTA
+      for (int64_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+        const int j0 = (int)(tile % tiles_j) * TN, i0 = (int)((tile / tiles_j) % tiles_i) * TM;
+        const int bt = (int)(tile / ((int64_t)tiles_j * tiles_i));
+        for (int t = 0; t < nt; ++t, ++it) {
+          const int s = it % TST;
+          if (it >= TST && !mbar_wait_bounded(&sm.empty[s], ((it / TST) - 1) & 1)) {
+            fail = true;
+            break;
+          }
+          mbar_arrive_expect_tx(&sm.full[s], 4 * kTileBytes);
+          tma_tile(sm.a_hi[s], &ma_hi, &sm.full[s], t * TK, i0, bt);
+          tma_tile(sm.a_lo[s], &ma_lo, &sm.full[s], t * TK, i0, bt);
+          tma_tile(sm.b_hi[s], &mb_hi, &sm.full[s], t * TK, j0, bt);
+          tma_tile(sm.b_lo[s], &mb_lo, &sm.full[s], t * TK, j0, bt);
         }
-        mbar_arrive_expect_tx(&sm.full[s], 4 * kTileBytes);
-        tma_tile(sm.a_hi[s], &ma_hi, &sm.full[s], t * TK, i0, bt);
-        tma_tile(sm.a_lo[s], &ma_lo, &sm.full[s], t * TK, i0, bt);
-        tma_tile(sm.b_hi[s], &mb_hi, &sm.full[s], t * TK, j0, bt);
-        tma_tile(sm.b_lo[s], &mb_lo, &sm.full[s], t * TK, j0, bt);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      for (int t = 0; t < nt; ++t) {
-        const int s = t % TST, chunk = t / TCH, buf = chunk & 1;
-        const bool chunk_start = (t % TCH) == 0;
-        if (chunk_start && chunk >= 2 && !mbar_wait_bounded(&sm.chunk_empty[buf], ((chunk >> 1) - 1) & 1)) {
-          fail = true;
-          break;
-        }
-        if (!mbar_wait_bounded(&sm.full[s], (t / TST) & 1)) {
-          fail = true;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t acc = tmem + (uint32_t)(buf * TN);
+      uint32_t it = 0, gc = 0;  // stages and chunks consumed so far
+      for (int64_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+        for (int t = 0; t < nt; ++t, ++it) {
+          const int s = it % TST, buf = gc % TNB;
+          const bool chunk_start = (t % TCH) == 0;
+          if (chunk_start && gc >= TNB && !mbar_wait_bounded(&sm.chunk_empty[buf], ((gc / TNB) - 1) & 1)) {
+            fail = true;
+            break;
+          }
+          if (!mbar_wait_bounded(&sm.full[s], (it / TST) & 1)) {
+            fail = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t acc = tmem + (uint32_t)(buf * TN);
 #pragma unroll
-        for (int kk = 0; kk < TK / 8; ++kk) {
-          const int ko = kk * 8 * (int)sizeof(float);  // 32 bytes per K=8 step inside the 128-byte row
-          const uint64_t ah = umma_desc(sm.a_hi[s], ko), al = umma_desc(sm.a_lo[s], ko);
-          const uint64_t bh = umma_desc(sm.b_hi[s], ko), bl = umma_desc(sm.b_lo[s], ko);
-          umma_tf32(acc, al, bh, (!chunk_start || kk > 0) ? 1u : 0u);
-          umma_tf32(acc, ah, bl, 1u);
-          umma_tf32(acc, ah, bh, 1u);
+          for (int kk = 0; kk < TK / 8; ++kk) {
+            const int ko = kk * 8 * (int)sizeof(float);  // 32 bytes per K=8 step inside the 128-byte row
+            const uint64_t ah = umma_desc(sm.a_hi[s], ko), al = umma_desc(sm.a_lo[s], ko);
+            const uint64_t bh = umma_desc(sm.b_hi[s], ko), bl = umma_desc(sm.b_lo[s], ko);
+            umma_tf32(acc, al, bh, (!chunk_start || kk > 0) ? 1u : 0u);
+            umma_tf32(acc, ah, bl, 1u);
+            umma_tf32(acc, ah, bh, 1u);
+          }
+          umma_commit(&sm.empty[s]);  // stage s may be refilled once these MMAs have read it
+          if ((t % TCH) == TCH - 1 || t == nt - 1) {
+            umma_commit(&sm.chunk_full[buf]);
+            ++gc;
+          }
         }
-        umma_commit(&sm.empty[s]);  // stage s may be refilled once these MMAs have read it
-        if ((t % TCH) == TCH - 1 || t == nt - 1) umma_commit(&sm.chunk_full[buf]);
       }
     }
     __syncwarp();
   } else {
-    const int quad = warp % 4;  // TMEM lanes this warp may read: 32*quad .. 32*quad+31
+    const int quad = warp % 4;                 // TMEM lanes this warp may read: 32*quad .. 32*quad+31
     const int cbase = ((warp - 2) / 4) * TEC;  // first of this warp's columns
-    float sum[TEC];
+    float* blk = sm.epi[warp - 2];
+    uint32_t gc = 0;
+    bool bad_any = false;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+      const int j0 = (int)(tile % tiles_j) * TN, i0 = (int)((tile / tiles_j) % tiles_i) * TM;
+      const int bt = (int)(tile / ((int64_t)tiles_j * tiles_i));
+      float sum[TEC];
 #pragma unroll
-    for (int q = 0; q < TEC; ++q) sum[q] = 0.f;
-    const int nchunks = (nt + TCH - 1) / TCH;
-    for (int chunk = 0; chunk < nchunks && !fail; ++chunk) {
-      const int buf = chunk & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.chunk_full[buf], (chunk >> 1) & 1))) {
-        fail = true;
-        break;
+      for (int q = 0; q < TEC; ++q) sum[q] = 0.f;
+      for (int chunk = 0; chunk < nchunks; ++chunk, ++gc) {
+        const int buf = gc % TNB;
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.chunk_full[buf], (gc / TNB) & 1))) {
+          fail = true;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < TEC / 32; ++c) {
+          float v[32];
+          tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * TN + cbase + c * 32), v);
+#pragma unroll
+          for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.chunk_empty[buf])) : "memory");
       }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < TEC / 32; ++c) {
-        float v[32];
-        tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * TN + cbase + c * 32), v);
-#pragma unroll
-        for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q];
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0)
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.chunk_empty[buf])) : "memory");
-    }
-    // Hand the sums over through shared memory (the pipeline stages are idle by now) so that
-    // global memory is touched along rows: lane = row when writing the warp's private 32x64 block,
-    // half a warp per row (16 lanes x 4 columns) when reading it back.
-    bool bad = false;
-    if (!fail) {
-      float* blk = reinterpret_cast<float*>(&sm.a_hi[0][0]) + (warp - 2) * (32 * (TEC + 1));
-#pragma unroll
-      for (int q = 0; q < TEC; ++q) blk[lane * (TEC + 1) + q] = sum[q];
-      __syncwarp();
-      const int hl = lane % 16, hr = lane / 16;
+      if (fail) break;
+      // Hand the sums over through shared memory so that global memory is touched along rows:
+      // lane = row when writing the warp's private 32x32 block, 8 lanes x 4 columns per row when
+      // reading it back; two passes cover the warp's 64 columns.
+      bool bad = false;
+      const int hl = lane % 8, hr = lane / 8;
       const bool vec = (J % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) &&
                        (!ep.src || (reinterpret_cast<uintptr_t>(ep.src) & 15) == 0) &&
                        (!ep.col_v || (reinterpret_cast<uintptr_t>(ep.col_v) & 15) == 0);
-#pragma unroll 4
-      for (int it = 0; it < 16; ++it) {
-        const int r = it * 2 + hr;
-        const int ii = i0 + quad * 32 + r;
-        const int jj = j0 + cbase + hl * 4;
-        if (ii >= I || jj >= J) continue;
-        float v[4], cv[4] = {0.f, 0.f, 0.f, 0.f}, x[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[k] = blk[r * (TEC + 1) + hl * 4 + k];
-        const float rv = ep.row_v ? __ldg(ep.row_v + (int64_t)bt * I + ii) : 0.f;
-        const int64_t orow = ((int64_t)bt * I + ii) * J;
-        const bool full4 = vec && jj + 3 < J;
-        if (full4) {
-          if (ep.col_v) {
-            const float4 t = __ldg(reinterpret_cast<const float4*>(ep.col_v + (int64_t)bt * J + jj));
-            cv[0] = t.x; cv[1] = t.y; cv[2] = t.z; cv[3] = t.w;
-          }
-          if (EPI == TC_GRAD) {
-            const float4 t = __ldg(reinterpret_cast<const float4*>(ep.src + orow + jj));
-            x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
-          }
-        } else {
+      for (int pass = 0; pass < TEC / 32; ++pass) {
+        __syncwarp();
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            if (jj + k < J) {
-              if (ep.col_v) cv[k] = __ldg(ep.col_v + (int64_t)bt * J + jj + k);
-              if (EPI == TC_GRAD) x[k] = __ldg(ep.src + orow + jj + k);
+        for (int q = 0; q < 32; ++q) blk[lane * 33 + q] = sum[pass * 32 + q];
+        __syncwarp();
+#pragma unroll 2
+        for (int itr = 0; itr < 8; ++itr) {
+          const int r = itr * 4 + hr;
+          const int ii = i0 + quad * 32 + r;
+          const int jj = j0 + cbase + pass * 32 + hl * 4;
+          if (ii >= I || jj >= J) continue;
+          float v[4], cv[4] = {0.f, 0.f, 0.f, 0.f}, x[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) v[k] = blk[r * 33 + hl * 4 + k];
+          const float rv = ep.row_v ? __ldg(ep.row_v + (int64_t)bt * I + ii) : 0.f;
+          const int64_t orow = ((int64_t)bt * I + ii) * J;
+          const bool full4 = vec && jj + 3 < J;
+          if (full4) {
+            if (ep.col_v) {
+              const float4 t4 = __ldg(reinterpret_cast<const float4*>(ep.col_v + (int64_t)bt * J + jj));
+              cv[0] = t4.x; cv[1] = t4.y; cv[2] = t4.z; cv[3] = t4.w;
             }
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (EPI == TC_LOG) {
-            const float shift = rv + cv[k];
-            if (jj + k < J) bad |= !(v[k] >= kTiny) || !(v[k] <= 3.0e38f) || (shift < kFloor);
-            o[k] = __logf(v[k]) + shift;  // lg2.approx: absolute error below 2e-7 on the logarithm
+            if (EPI == TC_GRAD) {
+              const float4 t4 = __ldg(reinterpret_cast<const float4*>(ep.src + orow + jj));
+              x[0] = t4.x; x[1] = t4.y; x[2] = t4.z; x[3] = t4.w;
+            }
           } else {
-            o[k] = exp_sfu(x[k] - (rv + cv[k])) * v[k];
-          }
-        }
-        if (full4) {
-          *reinterpret_cast<float4*>(ep.out + orow + jj) = make_float4(o[0], o[1], o[2], o[3]);
-        } else {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            if (jj + k < J) ep.out[orow + jj + k] = o[k];
+            for (int k = 0; k < 4; ++k)
+              if (jj + k < J) {
+                if (ep.col_v) cv[k] = __ldg(ep.col_v + (int64_t)bt * J + jj + k);
+                if (EPI == TC_GRAD) x[k] = __ldg(ep.src + orow + jj + k);
+              }
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (EPI == TC_LOG) {
+              const float shift = rv + cv[k];
+              if (jj + k < J) bad |= !(v[k] >= kTiny) || !(v[k] <= 3.0e38f) || (shift < kFloor);
+              o[k] = __logf(v[k]) + shift;  // lg2.approx: absolute error below 2e-7 on the logarithm
+            } else {
+              o[k] = exp_sfu(x[k] - (rv + cv[k])) * v[k];
+            }
+          }
+          if (full4) {
+            *reinterpret_cast<float4*>(ep.out + orow + jj) = make_float4(o[0], o[1], o[2], o[3]);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              if (jj + k < J) ep.out[orow + jj + k] = o[k];
+          }
         }
       }
+      if (EPI == TC_LOG) {
+        // flags were zeroed before the launch; any epilogue warp that saw a bad sum raises the tile's
+        if (__any_sync(0xffffffffu, bad) && lane == 0) atomicExch(ep.flags + tile, 1);
+      }
+      bad_any |= bad;
     }
-    if (EPI == TC_LOG) {
-      // flags were zeroed before the launch; any epilogue warp that saw a bad sum raises the tile's
-      if (__any_sync(0xffffffffu, bad) && lane == 0) atomicExch(ep.flags + blockIdx.x, 1);
-    }
+    (void)bad_any;
   }
   if (__any_sync(0xffffffffu, fail) && lane == 0) atomicExch(ep.error, 1);
   tc_fence_before();
@@ -450,15 +476,19 @@ int launch_tc(const float* a_hi, const float* a_lo, int64_t a_pitch, const float
   if (!make_map_sw128(&m0, a_hi, B, I, R, a_pitch) || !make_map_sw128(&m1, a_lo, B, I, R, a_pitch) ||
       !make_map_sw128(&m2, b_hi, B, J, R, b_pitch) || !make_map_sw128(&m3, b_lo, B, J, R, b_pitch))
     return GBMM_ERR_LAUNCH;
-  const int64_t ti = ceil_div(I, TM), tj = ceil_div(J, TN), blocks = B * ti * tj;
-  if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  const int64_t ti = ceil_div(I, TM), tj = ceil_div(J, TN), tiles = B * ti * tj;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    return GBMM_ERR_DEVICE;
+  const unsigned blocks = (unsigned)(tiles < sms ? tiles : sms);  // one persistent CTA per SM
   const size_t smem = sizeof(TcSmem) + 1024;
   if (cudaFuncSetAttribute(tc_gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return GBMM_ERR_LAUNCH;
   const bool timed = profile_begin(slot, st);
-  tc_gemm_kernel<EPI><<<(unsigned)blocks, TNT, smem, st>>>(m0, m1, m2, m3, ep, (int)R, (int)I, (int)J, (int)ti,
-                                                          (int)tj);
+  tc_gemm_kernel<EPI><<<blocks, TNT, smem, st>>>(m0, m1, m2, m3, ep, (int)R, (int)I, (int)J, (int)ti, (int)tj,
+                                                tiles);
   if (timed) profile_end(slot, st);
   return launch_status();
 }
