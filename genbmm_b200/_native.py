@@ -305,8 +305,10 @@ def logbmm_fast_forward(a, b, check=False, tensor_cores=False):
     return out, rowmax, colmax, flags
 
 
-def logbmm_fast_backward(a, b, grad_output, out, rowmax, colmax, flags, check=False, tensor_cores=False):
-    """(grad_a, grad_b) of logbmm by the factorised kernels, from what the fast forward saved."""
+def logbmm_fast_backward(a, b, grad_output, out, rowmax, colmax, flags, check=False, tensor_cores=False,
+                         out_grads=None):
+    """(grad_a, grad_b) of logbmm by the factorised kernels, from what the fast forward saved.
+    `out_grads` = (grad_a, grad_b) buffers to fill instead of allocating new ones."""
     for x, name in ((a, "a"), (b, "b"), (grad_output, "grad_output"), (out, "out"), (rowmax, "rowmax"),
                     (colmax, "colmax")):
         _check_input(x, name)
@@ -314,8 +316,9 @@ def logbmm_fast_backward(a, b, grad_output, out, rowmax, colmax, flags, check=Fa
     N = b.shape[2]
     lib = load()
     with torch.cuda.device(a.device):
-        grad_a = torch.empty_like(a)
-        grad_b = torch.empty_like(b)
+        grad_a, grad_b = (torch.empty_like(a), torch.empty_like(b)) if out_grads is None else out_grads
+        _check_input(grad_a, "grad_a")
+        _check_input(grad_b, "grad_b")
         sizer = lib.gbmm_logbmm_tc_workspace_bytes if tensor_cores else lib.gbmm_logbmm_workspace_bytes
         fn = lib.gbmm_logbmm_tc_backward_f32 if tensor_cores else lib.gbmm_logbmm_backward_f32
         ws = _workspace(sizer(1, B, M, K, N), a.device)

@@ -1,0 +1,71 @@
+"""Host-resident operands: logbmm forward + backward with the PCIe copies overlapped.
+
+A caller whose operands live in (pinned) host memory pays two copies per step, each of the size
+of the operands; done one after the other with the kernels they cost more than the kernels.
+`HostPipeline` cuts the batch into chunks and runs three CUDA streams — host-to-device copies,
+kernels, device-to-host copies — so that chunk i+1 is arriving and chunk i-1 is leaving while
+chunk i is being multiplied (PCIe is full duplex; the GPU has separate copy engines for the two
+directions).  Device buffers are allocated once and reused by every step.
+
+    pipe = HostPipeline(B, M, K, N, chunks=4)
+    loss = pipe.step(a_host, b_host, grad_a_host, grad_b_host)   # loss = logbmm(a, b).sum()
+
+The reference has no counterpart: it takes device tensors only (matmul_cuda.cpp:65).
+"""
+import torch
+
+from . import _native
+
+
+class HostPipeline:
+    def __init__(self, B, M, K, N, chunks=4, device=None, tensor_cores=True):
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.shape = (B, M, K, N)
+        self.tensor_cores = tensor_cores
+        chunks = max(1, min(chunks, B))
+        self.bounds = [(i * B // chunks, (i + 1) * B // chunks) for i in range(chunks)]
+        with torch.cuda.device(self.device):
+            self.a = torch.empty((B, M, K), device=self.device)
+            self.b = torch.empty((B, K, N), device=self.device)
+            self.grad_a = torch.empty_like(self.a)
+            self.grad_b = torch.empty_like(self.b)
+            self.ones = torch.ones((max(hi - lo for lo, hi in self.bounds), M, N), device=self.device)
+            self.loss = torch.zeros((), device=self.device, dtype=torch.float64)
+            self.s_in = torch.cuda.Stream(self.device)
+            self.s_out = torch.cuda.Stream(self.device)
+            self.ev_in = [torch.cuda.Event() for _ in self.bounds]
+            self.ev_done = [torch.cuda.Event() for _ in self.bounds]
+            self.ev_step = torch.cuda.Event()
+
+    def step(self, a_host, b_host, grad_a_host, grad_b_host):
+        """One forward + backward of loss = logbmm(a, b).sum().  All four host tensors should be
+        pinned; the gradients are complete in grad_*_host when this returns.  Returns the loss."""
+        B, M, K, N = self.shape
+        assert tuple(a_host.shape) == (B, M, K) and tuple(b_host.shape) == (B, K, N)
+        comp = torch.cuda.current_stream(self.device)
+        with torch.cuda.device(self.device):
+            self.loss.zero_()
+            # the copy streams start after whatever the compute stream was doing with the buffers
+            self.ev_step.record(comp)
+            self.s_in.wait_event(self.ev_step)
+            self.s_out.wait_event(self.ev_step)
+            for i, (lo, hi) in enumerate(self.bounds):
+                with torch.cuda.stream(self.s_in):
+                    self.a[lo:hi].copy_(a_host[lo:hi], non_blocking=True)
+                    self.b[lo:hi].copy_(b_host[lo:hi], non_blocking=True)
+                    self.ev_in[i].record(self.s_in)
+            for i, (lo, hi) in enumerate(self.bounds):
+                comp.wait_event(self.ev_in[i])
+                a, b = self.a[lo:hi], self.b[lo:hi]
+                out, rowmax, colmax, flags = _native.logbmm_fast_forward(a, b, tensor_cores=self.tensor_cores)
+                self.loss += out.sum(dtype=torch.float64)
+                ga, gb = _native.logbmm_fast_backward(a, b, self.ones[: hi - lo], out, rowmax, colmax, flags,
+                                                      tensor_cores=self.tensor_cores,
+                                                      out_grads=(self.grad_a[lo:hi], self.grad_b[lo:hi]))
+                self.ev_done[i].record(comp)
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(self.ev_done[i])
+                    grad_a_host[lo:hi].copy_(ga, non_blocking=True)
+                    grad_b_host[lo:hi].copy_(gb, non_blocking=True)
+            comp.wait_stream(self.s_out)
+            return float(self.loss.item())
