@@ -21,7 +21,8 @@ _P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
 _SIGNATURES = {
     "gbmm_status_string": ([_I], ctypes.c_char_p),
     "gbmm_abi_version": ([], _I),
-    "gbmm_dense_forward_f32": ([_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
+    "gbmm_dense_forward_workspace_bytes": ([_I, _L, _L, _L, _L], _L),
+    "gbmm_dense_forward_f32": ([_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _L, _P], _I),
     "gbmm_dense_backward_f32": ([_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
     "gbmm_dense_backbackward_f32": ([_P] * 9 + [_L] * 4 + [_P], _I),
     "gbmm_band_workspace_bytes": ([_L, _L], _L),
@@ -132,8 +133,10 @@ def forward(a, b, mode, u=None, want_maxes=True):
             _check_input(u, "u")
             if tuple(u.shape) != (B, M, N):
                 raise RuntimeError("u must have shape %s" % ((B, M, N),))
+        nbytes = load().gbmm_dense_forward_workspace_bytes(mode, B, M, K, N)
+        ws = torch.empty((nbytes,), dtype=torch.uint8, device=a.device) if nbytes > 0 else None
         st = load().gbmm_dense_forward_f32(mode, _ptr(a), _ptr(b), _ptr(u) if mode == MODE_SAMPLE else None,
-                                           _ptr(out), _ptr(aux), B, M, K, N, _stream(a.device))
+                                           _ptr(out), _ptr(aux), B, M, K, N, _ptr(ws), nbytes, _stream(a.device))
     _check(st, "gbmm_dense_forward_f32")
     return [out, aux]
 

@@ -290,38 +290,52 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_grad_a_kernel(const fl
   }
 }
 
-// grad_b: one warp per (batch, 32 consecutive n); each lane owns a column and walks m in
-// ascending order into its private column of the [KT][32] histogram.
+// grad_b: one warp per (batch, 32 consecutive n, slice of KT buckets); each lane owns a column
+// and walks m in ascending order into its private column of the [KT][32] histogram.  Slicing K
+// over CTAs multiplies the number of independent (latency-bound) walks.
 template <bool MUL>
 __global__ void __launch_bounds__(32) route_grad_b_kernel(const float* __restrict__ a,
                                                           const int* __restrict__ idx,
                                                           const float* __restrict__ g,
                                                           float* __restrict__ grad_b, int M, int K, int N,
-                                                          int tiles_n, int KT) {
+                                                          int tiles_n, int slices, int KT) {
   extern __shared__ float hist[];
   const int lane = threadIdx.x;
-  const int bt = blockIdx.x / tiles_n;
-  const int n = (blockIdx.x % tiles_n) * 32 + lane;
+  const int slice = blockIdx.x % slices;
+  const int tile = (blockIdx.x / slices) % tiles_n;
+  const int bt = blockIdx.x / (slices * tiles_n);
+  const int n = tile * 32 + lane;
   const bool live = n < N;
   const int* ib = idx + (int64_t)bt * M * N;
   const float* gb = g + (int64_t)bt * M * N;
   const float* ab = a + (int64_t)bt * M * K;
   float* ob = grad_b + (int64_t)bt * K * N;
-  for (int kbase = 0; kbase < K; kbase += KT) {
-    const int kend = min(kbase + KT, K);
-    for (int k = 0; k < kend - kbase; ++k) hist[k * 32 + lane] = 0.f;
-    if (live) {
-#pragma unroll 4
-      for (int m = 0; m < M; ++m) {
-        const int k = __ldg(ib + (int64_t)m * N + n);
-        float gv = __ldg(gb + (int64_t)m * N + n);
-        if (k >= kbase && k < kend) {
-          if (MUL) gv = __fmul_rn(__ldg(ab + (int64_t)m * K + k), gv);
-          hist[(k - kbase) * 32 + lane] = __fadd_rn(hist[(k - kbase) * 32 + lane], gv);
-        }
+  const int kbase = slice * KT, kend = min(kbase + KT, K);
+  if (kbase >= kend) return;
+  for (int k = 0; k < kend - kbase; ++k) hist[k * 32 + lane] = 0.f;
+  if (live) {
+    // 16 rows at a time: all their loads are issued before the (ordered) bucket updates
+    for (int m0 = 0; m0 < M; m0 += 16) {
+      int kk[16];
+      float gg[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const bool ok = m0 + u < M;
+        kk[u] = ok ? __ldg(ib + (int64_t)(m0 + u) * N + n) : -1;
+        gg[u] = ok ? __ldg(gb + (int64_t)(m0 + u) * N + n) : 0.f;
       }
-      for (int k = 0; k < kend - kbase; ++k) ob[(int64_t)(kbase + k) * N + n] = hist[k * 32 + lane];
+      if (MUL) {
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+          if (kk[u] >= kbase && kk[u] < kend)
+            gg[u] = __fmul_rn(__ldg(ab + (int64_t)(m0 + u) * K + kk[u]), gg[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        if (kk[u] >= kbase && kk[u] < kend)
+          hist[(kk[u] - kbase) * 32 + lane] = __fadd_rn(hist[(kk[u] - kbase) * 32 + lane], gg[u]);
     }
+    for (int k = 0; k < kend - kbase; ++k) ob[(int64_t)(kbase + k) * N + n] = hist[k * 32 + lane];
   }
 }
 
@@ -409,19 +423,17 @@ extern "C" int gbmm_dense_backward_f32(int mode, const float* a, const float* b,
     if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
   }
   if (grad_b) {
-    const int KT = (int)(K < 1024 ? K : 1024);
-    const int64_t tiles_n = ceil_div(N, 32), blocks = B * tiles_n;
+    // bucket slices of 128: B * ceil(N/32) * ceil(K/128) single-warp CTAs
+    const int KT = (int)(K < 128 ? K : 128);
+    const int64_t tiles_n = ceil_div(N, 32), slices = ceil_div(K, KT), blocks = B * tiles_n * slices;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
     const size_t smem = sizeof(float) * 32 * KT;
-    if (mul) {
-      cudaFuncSetAttribute(route_grad_b_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (mul)
       route_grad_b_kernel<true><<<(unsigned)blocks, 32, smem, st>>>(a, idx, grad_out, grad_b, m, k, n,
-                                                                   (int)tiles_n, KT);
-    } else {
-      cudaFuncSetAttribute(route_grad_b_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                                                                   (int)tiles_n, (int)slices, KT);
+    else
       route_grad_b_kernel<false><<<(unsigned)blocks, 32, smem, st>>>(a, idx, grad_out, grad_b, m, k, n,
-                                                                    (int)tiles_n, KT);
-    }
+                                                                    (int)tiles_n, (int)slices, KT);
   }
   return launch_status();
 }

@@ -38,12 +38,55 @@ struct TileCoord {
 __device__ __forceinline__ float nan_f() { return __int_as_float(0x7fc00000); }
 __device__ __forceinline__ float ninf_f() { return __int_as_float(0xff800000); }
 // ------------------------------------------------------------------ max-plus / prod-max
+// Packed pairs (sm_100): the two terms of a reduction-step pair are formed by one add.f32x2 /
+// mul.f32x2 and folded into the tile maximum by one 3-input max, i.e. one FP32-pipe and one ALU
+// instruction per two terms.  The shared tiles therefore hold (k, k+1) pairs side by side:
+// element (k, m) at ((k/2) * LD + m) * 2 + (k & 1).
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+// a tile (k contiguous in global memory): float4 = 4 consecutive k of one row -> two pairs
+__device__ __forceinline__ void store_pairs_a(float* s, const TileLoader<BM, BK, NT, true>& l) {
+#pragma unroll
+  for (int q = 0; q < TileLoader<BM, BK, NT, true>::NV; ++q) {
+    const int f = threadIdx.x + q * NT;
+    const int o = f / (BK / 4), r = (f % (BK / 4)) * 4;
+    *reinterpret_cast<float2*>(s + ((r / 2) * LDX + o) * 2) = make_float2(l.v[q].x, l.v[q].y);
+    *reinterpret_cast<float2*>(s + ((r / 2 + 1) * LDX + o) * 2) = make_float2(l.v[q].z, l.v[q].w);
+  }
+}
+// b tile (n contiguous in global memory): float4 = 4 consecutive columns at one k
+__device__ __forceinline__ void store_pairs_b(float* s, const TileLoader<BN, BK, NT, false>& l) {
+#pragma unroll
+  for (int q = 0; q < TileLoader<BN, BK, NT, false>::NV; ++q) {
+    const int f = threadIdx.x + q * NT;
+    const int r = f / (BN / 4), o = (f % (BN / 4)) * 4;
+    float* p = s + ((r / 2) * LDY + o) * 2 + (r & 1);
+    p[0] = l.v[q].x;
+    p[2] = l.v[q].y;
+    p[4] = l.v[q].z;
+    p[6] = l.v[q].w;
+  }
+}
+
 template <bool MUL>
 __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restrict__ a,
                                                            const float* __restrict__ b,
                                                            float* __restrict__ out,
                                                            int* __restrict__ idx, int M, int K, int N,
-                                                           int tiles_m, int tiles_n) {
+                                                           int tiles_m, int tiles_n,
+                                                           const float* __restrict__ b_t, int kp) {
   __shared__ __align__(16) float sx[2][BK * LDX];
   __shared__ __align__(16) float sy[2][BK * LDY];
   const TileCoord tc(tiles_m, tiles_n);
@@ -70,8 +113,8 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
   // a NaN in the padded reduction steps makes the term a NaN, which the maximum ignores
   la.load(ab, K, 1, tc.m0, 0, M, K, vec_a, nan_f());
   lb.load(bb, 1, N, tc.n0, 0, N, K, vec_b, 0.f);
-  la.store(sx[0], LDX);
-  lb.store(sy[0], LDY);
+  store_pairs_a(sx[0], la);
+  store_pairs_b(sy[0], lb);
   __syncthreads();
 
   for (int t = 0; t < nt; ++t) {
@@ -81,18 +124,23 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
       lb.load(bb, 1, N, tc.n0, (t + 1) * BK, N, K, vec_b, 0.f);
     }
 #pragma unroll
-    for (int kk = 0; kk < BK; kk += 2) {
-      float x0[8], x1[8], y0[4], y1[4];
-      mt.load_x(sx[cur] + kk * LDX, LDX, x0);
-      mt.load_y(sy[cur] + kk * LDY, y0);
-      mt.load_x(sx[cur] + (kk + 1) * LDX, LDX, x1);
-      mt.load_y(sy[cur] + (kk + 1) * LDY, y1);
+    for (int kp = 0; kp < BK / 2; ++kp) {
+      const float* xs = sx[cur] + (kp * LDX + mt.ty * 4) * 2;
+      const float* ys = sy[cur] + (kp * LDY + mt.tx * 4) * 2;
+      const ulonglong2 x01 = *reinterpret_cast<const ulonglong2*>(xs);
+      const ulonglong2 x23 = *reinterpret_cast<const ulonglong2*>(xs + 4);
+      const ulonglong2 x45 = *reinterpret_cast<const ulonglong2*>(xs + 128);
+      const ulonglong2 x67 = *reinterpret_cast<const ulonglong2*>(xs + 132);
+      const ulonglong2 y01 = *reinterpret_cast<const ulonglong2*>(ys);
+      const ulonglong2 y23 = *reinterpret_cast<const ulonglong2*>(ys + 4);
+      const unsigned long long xp[8] = {x01.x, x01.y, x23.x, x23.y, x45.x, x45.y, x67.x, x67.y};
+      const unsigned long long yp[4] = {y01.x, y01.y, y23.x, y23.y};
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float v0 = MUL ? __fmul_rn(x0[i], y0[j]) : __fadd_rn(x0[i], y0[j]);
-          const float v1 = MUL ? __fmul_rn(x1[i], y1[j]) : __fadd_rn(x1[i], y1[j]);
+          float v0, v1;
+          unpack2(MUL ? mul2(xp[i], yp[j]) : add2(xp[i], yp[j]), v0, v1);
           cm[i][j] = max3(cm[i][j], v0, v1);
         }
     }
@@ -107,8 +155,8 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
         cm[i][j] = ninf_f();
       }
     if (t + 1 < nt) {
-      la.store(sx[cur ^ 1], LDX);
-      lb.store(sy[cur ^ 1], LDY);
+      store_pairs_a(sx[cur ^ 1], la);
+      store_pairs_b(sy[cur ^ 1], lb);
     }
     __syncthreads();
   }
@@ -131,17 +179,38 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
       ind[j] = -1;
       if (n < N && cid[i][j] >= 0) {
         // all loads of the tile are issued before any is used; the scan runs from the last k
-        // down, so the lowest matching k is the assignment that sticks
+        // down, so the lowest matching k is the assignment that sticks.  With a transposed copy
+        // of b (b_t: (batch, N, kp), kp a multiple of 16) both 16-term segments are contiguous:
+        // 8 128-bit loads and 4 sectors per result instead of 32 loads and 18 sectors.
         const int k0 = cid[i][j] * BK;
         const float* ap = ab + (int64_t)m * K + k0;
-        const float* bp = bb + (int64_t)k0 * N + n;
-        float v[BK];
+        float xv[BK], yv[BK], v[BK];
+        if (vec_a && k0 + BK <= K) {
+#pragma unroll
+          for (int q = 0; q < BK / 4; ++q) {
+            const float4 t4 = __ldg(reinterpret_cast<const float4*>(ap) + q);
+            xv[4 * q] = t4.x; xv[4 * q + 1] = t4.y; xv[4 * q + 2] = t4.z; xv[4 * q + 3] = t4.w;
+          }
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < BK; ++kk) xv[kk] = (k0 + kk < K) ? __ldg(ap + kk) : nan_f();
+        }
+        if (b_t) {
+          const float4* bp = reinterpret_cast<const float4*>(b_t + ((int64_t)tc.bt * N + n) * kp + k0);
+#pragma unroll
+          for (int q = 0; q < BK / 4; ++q) {
+            const float4 t4 = __ldg(bp + q);
+            yv[4 * q] = t4.x; yv[4 * q + 1] = t4.y; yv[4 * q + 2] = t4.z; yv[4 * q + 3] = t4.w;
+          }
+        } else {
+          const float* bp = bb + (int64_t)k0 * N + n;
+#pragma unroll
+          for (int kk = 0; kk < BK; ++kk) yv[kk] = (k0 + kk < K) ? __ldg(bp + (int64_t)kk * N) : 0.f;
+        }
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
-          const bool ok = k0 + kk < K;
-          const float x = ok ? __ldg(ap + kk) : nan_f();
-          const float y = ok ? __ldg(bp + (int64_t)kk * N) : 0.f;
-          v[kk] = MUL ? __fmul_rn(x, y) : __fadd_rn(x, y);
+          const float t = MUL ? __fmul_rn(xv[kk], yv[kk]) : __fadd_rn(xv[kk], yv[kk]);
+          v[kk] = (k0 + kk < K) ? t : nan_f();
         }
 #pragma unroll
         for (int kk = BK - 1; kk >= 0; --kk)
@@ -163,6 +232,27 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
           ib[(int64_t)m * N + nb + j] = ind[j];
         }
     }
+  }
+}
+
+// b:(batch, K, N) -> b_t:(batch, N, kp) for the rescan of the max kernels (plain 32x32 tile transpose)
+__global__ void __launch_bounds__(256) transpose_b_kernel(const float* __restrict__ b, float* __restrict__ b_t,
+                                                          int K, int N, int kp, int tiles_k, int tiles_n) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+  const int64_t id = blockIdx.x;
+  const int n0 = (int)(id % tiles_n) * 32, k0 = (int)((id / tiles_n) % tiles_k) * 32;
+  const int64_t bt = id / ((int64_t)tiles_n * tiles_k);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int k = k0 + ty + q * 8, n = n0 + tx;
+    tile[ty + q * 8][tx] = (k < K && n < N) ? __ldg(b + (bt * K + k) * N + n) : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int n = n0 + ty + q * 8, k = k0 + tx;
+    if (n < N && k < kp) b_t[(bt * N + n) * kp + k] = tile[tx][ty + q * 8];
   }
 }
 
@@ -392,8 +482,15 @@ int launch_log_fwd_flagged(const float* a, const float* b, float* out, const int
 
 using namespace gbmm;
 
+extern "C" int64_t gbmm_dense_forward_workspace_bytes(int mode, int64_t B, int64_t M, int64_t K, int64_t N) {
+  if (B < 0 || M < 0 || K < 0 || N < 0) return -1;
+  if (mode != GBMM_MODE_MAX && mode != GBMM_MODE_PRODMAX) return 0;
+  return (int64_t)sizeof(float) * B * N * ((K + 15) / 16 * 16);
+}
+
 extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, const float* u, float* out,
-                                      void* aux, int64_t B, int64_t M, int64_t K, int64_t N, void* stream) {
+                                      void* aux, int64_t B, int64_t M, int64_t K, int64_t N, void* workspace,
+                                      int64_t workspace_bytes, void* stream) {
   if (mode < 0 || mode > 3) return GBMM_ERR_INVALID_ARG;
   if (B < 0 || M < 0 || K < 0 || N < 0) return GBMM_ERR_INVALID_ARG;
   if (B == 0 || M == 0 || N == 0) return GBMM_OK;
@@ -414,11 +511,26 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
       dense_log_fwd_kernel<<<grid, block, 0, st>>>(a, b, out, static_cast<float*>(aux), m, k, n, tm, tn, nullptr);
       break;
     case GBMM_MODE_MAX:
-      dense_max_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, static_cast<int*>(aux), m, k, n, tm, tn);
+    case GBMM_MODE_PRODMAX: {
+      // with scratch for a transposed copy of b the final index search reads contiguous segments
+      float* b_t = nullptr;
+      const int kp = (int)((K + 15) / 16 * 16);
+      if (workspace && K > 0 && workspace_bytes >= gbmm_dense_forward_workspace_bytes(mode, B, M, K, N) &&
+          (reinterpret_cast<uintptr_t>(workspace) & 63) == 0) {
+        b_t = static_cast<float*>(workspace);
+        const int64_t tk = ceil_div(kp, 32), tnn = ceil_div(N, 32), tb = B * tk * tnn;
+        if (tb >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+        transpose_b_kernel<<<(unsigned)tb, 256, 0, st>>>(b, b_t, k, n, kp, (int)tk, (int)tnn);
+        if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+      }
+      if (mode == GBMM_MODE_MAX)
+        dense_max_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, static_cast<int*>(aux), m, k, n, tm, tn, b_t,
+                                                            kp);
+      else
+        dense_max_fwd_kernel<true><<<grid, block, 0, st>>>(a, b, out, static_cast<int*>(aux), m, k, n, tm, tn, b_t,
+                                                           kp);
       break;
-    case GBMM_MODE_PRODMAX:
-      dense_max_fwd_kernel<true><<<grid, block, 0, st>>>(a, b, out, static_cast<int*>(aux), m, k, n, tm, tn);
-      break;
+    }
     case GBMM_MODE_SAMPLE:
       dense_log_fwd_kernel<<<grid, block, 0, st>>>(a, b, out, nullptr, m, k, n, tm, tn, nullptr);
       if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;

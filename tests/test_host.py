@@ -35,10 +35,10 @@ def test_status_strings_and_argument_validation_without_a_gpu():
     assert lib.gbmm_status_string(0) == b"ok"
     assert lib.gbmm_status_string(1) == b"invalid argument"
     # validation happens before any CUDA call, so these return without a device
-    assert lib.gbmm_dense_forward_f32(9, None, None, None, None, None, 1, 1, 1, 1, None) == 1
-    assert lib.gbmm_dense_forward_f32(0, None, None, None, None, None, 1, 1, 1, 1, None) == 1
-    assert lib.gbmm_dense_forward_f32(0, None, None, None, None, None, 0, 1, 1, 1, None) == 0
-    assert lib.gbmm_dense_forward_f32(0, None, None, None, None, None, -1, 1, 1, 1, None) == 1
+    assert lib.gbmm_dense_forward_f32(9, None, None, None, None, None, 1, 1, 1, 1, None, 0, None) == 1
+    assert lib.gbmm_dense_forward_f32(0, None, None, None, None, None, 1, 1, 1, 1, None, 0, None) == 1
+    assert lib.gbmm_dense_forward_f32(0, None, None, None, None, None, 0, 1, 1, 1, None, 0, None) == 0
+    assert lib.gbmm_dense_forward_f32(0, None, None, None, None, None, -1, 1, 1, 1, None, 0, None) == 1
     assert lib.gbmm_band_forward_f32(2, None, 1, 1, None, 1, 1, None, None, None, 1, 4, None, 0, None) == 1
     assert lib.gbmm_band_forward_f32(3, None, -1, 1, None, 1, 1, None, None, None, 1, 4, None, 0, None) == 1
     assert lib.gbmm_band_backward_f32(0, None, 1, 1, None, 1, 1, None, None, None, None, 0, 4, None, 0, None) == 0
