@@ -28,6 +28,7 @@ _SIGNATURES = {
     "gbmm_band_workspace_bytes": ([_L, _L], _L),
     "gbmm_band_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L, _P, _L, _P], _I),
     "gbmm_band_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P, _L, _P], _I),
+    "gbmm_band_backbackward_f32": ([_P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _P], _I),
     "gbmm_logbmm_workspace_bytes": ([_I, _L, _L, _L, _L], _L),
     "gbmm_logbmm_flag_count": ([_L, _L, _L], _L),
     "gbmm_logbmm_forward_f32": ([_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
@@ -331,3 +332,26 @@ def logbmm_fast_backward(a, b, grad_output, out, rowmax, colmax, flags, check=Fa
         if check:
             _check(lib.gbmm_logbmm_check(_ptr(ws), _stream(a.device)), "gbmm_logbmm_backward_f32 (device)")
     return grad_a, grad_b
+
+
+def backbackward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, maxes, grad_out_a, mode=0, grad_out_b=None):
+    """`_genbmm.backbackward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, maxes, grad_out_a,
+    mode)` -> [grad_a, grad_b, grad_grad] for the banded log product (mode 0).  `grad_out_a` /
+    `grad_out_b` are the cotangents of the first-order grad_a / grad_b; `maxes` is not read."""
+    if mode != BAND_LOG:
+        raise RuntimeError("backbackward_band is defined for mode 0 (log) only")
+    _check_band(a, a_lu, a_lb, b, b_lu, b_lb)
+    _check_input(grad_output, "grad_output")
+    _check_input(part, "part")
+    B, n, _ = a.shape
+    with torch.cuda.device(a.device):
+        h_a = torch.zeros_like(a) if grad_out_a is None else grad_out_a.contiguous()
+        h_b = torch.zeros_like(b) if grad_out_b is None else grad_out_b.contiguous()
+        _check_input(h_a, "grad_out_a")
+        _check_input(h_b, "grad_out_b")
+        d_a, d_b, d_g = torch.empty_like(a), torch.empty_like(b), torch.empty_like(grad_output)
+        st = load().gbmm_band_backbackward_f32(_ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(grad_output),
+                                               _ptr(part), _ptr(h_a), _ptr(h_b), _ptr(d_a), _ptr(d_b), _ptr(d_g),
+                                               B, n, _stream(a.device))
+    _check(st, "gbmm_band_backbackward_f32")
+    return [d_a, d_b, d_g]

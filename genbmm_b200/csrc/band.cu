@@ -372,6 +372,98 @@ __global__ void __launch_bounds__(32) band_route_b_kernel(const int* __restrict_
     for (int k = lane; k < Wb; k += 32) ob[(o0 + ol) * Wb + k] = hist[k * 33 + ol];
 }
 
+// ------------------------------------------------------------------ log semiring, second order
+// With the weight s = exp(a[i][ja] + b[o][k2] - out[i][jo]) of a triple, cotangents h_a, h_b of
+// the first-order gradients, H = h_a[i][ja] + h_b[o][k2] and t[i][jo] = sum_ja s H:
+//   d/da[i][ja] = sum_jo g s (H - t),   d/db[o][k2] = sum_i g s (H - t),   d/dg[i][jo] = t.
+// Two passes of O(n*Wa*Wb) replace banded_cuda_backbackward_kernel_A/B/C
+// (banded_cuda_kernel.cu:154-350), whose A and B are O(n*Wa*Wo*Wa).  One thread per band cell,
+// operands read from global memory (this is not a hot path).
+__global__ void __launch_bounds__(NT) band_bwd2_t_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                         const float* __restrict__ out, const float* __restrict__ ha,
+                                                         const float* __restrict__ hb, float* __restrict__ t,
+                                                         BandDims d, int64_t cells) {
+  const int64_t e = (int64_t)blockIdx.x * NT + threadIdx.x;
+  if (e >= cells) return;
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
+  const int64_t n = d.n;
+  const int jo = (int)(e % Wo);
+  const int64_t i = (e / Wo) % n, bt = e / (Wo * n);
+  const int64_t o = i + jo - r_lu;
+  float val = 0.f;
+  if (o >= 0 && o < n) {
+    int lo = max(0, jo - (Wb - 1)), hi = min(Wa - 1, jo);
+    lo = (int)max((int64_t)lo, (int64_t)d.a_lu - i);
+    hi = (int)min((int64_t)hi, n - 1 - i + d.a_lu);
+    const float c = __ldg(out + e);
+    const int64_t ar = (bt * n + i) * Wa, br = (bt * n + o) * Wb;
+    const int kofs = Wb - 1 - jo;
+    for (int ja = lo; ja <= hi; ++ja) {
+      const float s = exp_sfu((__ldg(a + ar + ja) + __ldg(b + br + ja + kofs)) - c);
+      val = fmaf(s, __ldg(ha + ar + ja) + __ldg(hb + br + ja + kofs), val);
+    }
+  }
+  t[e] = val;
+}
+
+__global__ void __launch_bounds__(NT) band_bwd2_a_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                         const float* __restrict__ out, const float* __restrict__ g,
+                                                         const float* __restrict__ t, const float* __restrict__ ha,
+                                                         const float* __restrict__ hb, float* __restrict__ da,
+                                                         BandDims d, int64_t cells) {
+  const int64_t e = (int64_t)blockIdx.x * NT + threadIdx.x;
+  if (e >= cells) return;
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
+  const int64_t n = d.n;
+  const int ja = (int)(e % Wa);
+  const int64_t i = (e / Wa) % n, bt = e / (Wa * n);
+  const int64_t p = i + ja - d.a_lu;
+  float val = 0.f;
+  if (p >= 0 && p < n) {
+    int lo = ja, hi = min(Wo - 1, ja + Wb - 1);
+    lo = (int)max((int64_t)lo, (int64_t)r_lu - i);
+    hi = (int)min((int64_t)hi, n - 1 - i + r_lu);
+    const float av = __ldg(a + e), hv = __ldg(ha + e);
+    const int64_t orow = (bt * n + i) * Wo;
+    for (int jo = lo; jo <= hi; ++jo) {
+      const int64_t o = i + jo - r_lu;
+      const int64_t bi = (bt * n + o) * Wb + (ja - jo + Wb - 1);
+      const float w = exp_sfu((av + __ldg(b + bi)) - __ldg(out + orow + jo)) * __ldg(g + orow + jo);
+      val = fmaf(w, (hv + __ldg(hb + bi)) - __ldg(t + orow + jo), val);
+    }
+  }
+  da[e] = val;
+}
+
+__global__ void __launch_bounds__(NT) band_bwd2_b_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                         const float* __restrict__ out, const float* __restrict__ g,
+                                                         const float* __restrict__ t, const float* __restrict__ ha,
+                                                         const float* __restrict__ hb, float* __restrict__ db,
+                                                         BandDims d, int64_t cells) {
+  const int64_t e = (int64_t)blockIdx.x * NT + threadIdx.x;
+  if (e >= cells) return;
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
+  const int64_t n = d.n;
+  const int k2 = (int)(e % Wb);
+  const int64_t o = (e / Wb) % n, bt = e / (Wb * n);
+  const int64_t p = o + k2 - d.b_lu;
+  float val = 0.f;
+  if (p >= 0 && p < n) {
+    // i = o - jo + r_lu with ja = k2 + jo - (Wb-1) in [0, Wa)
+    int64_t lo = o + r_lu - (Wb - 1 - k2 + Wa - 1), hi = o + r_lu - (Wb - 1 - k2);
+    lo = max(lo, (int64_t)0);
+    hi = min(hi, n - 1);
+    const float bv = __ldg(b + e), hv = __ldg(hb + e);
+    for (int64_t i = lo; i <= hi; ++i) {
+      const int jo = (int)(o - i + r_lu), ja = k2 + jo - (Wb - 1);
+      const int64_t ai = (bt * n + i) * Wa + ja, oi = (bt * n + i) * Wo + jo;
+      const float w = exp_sfu((__ldg(a + ai) + bv) - __ldg(out + oi)) * __ldg(g + oi);
+      val = fmaf(w, (__ldg(ha + ai) + hv) - __ldg(t + oi), val);
+    }
+  }
+  db[e] = val;
+}
+
 int pick_rows(size_t fixed_floats, size_t per_row_floats) {
   for (int t = 32; t >= 1; t >>= 1)
     if ((fixed_floats + per_row_floats * t) * sizeof(float) <= (size_t)kSmemBudget) return t;
@@ -549,4 +641,26 @@ extern "C" int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_
                                     workspace, &flags, st);
   if (rc != GBMM_OK || mode != GBMM_BAND_LOG) return rc;
   return exact_backward(mode, a, b, grad_out, part, grad_a, grad_b, d, B, flags, st);
+}
+
+extern "C" int gbmm_band_backbackward_f32(const float* a, int a_lu, int a_ld, const float* b, int b_lu, int b_ld,
+                                          const float* grad_out, const float* part, const float* h_a,
+                                          const float* h_b, float* d_a, float* d_b, float* d_grad_out, int64_t B,
+                                          int64_t n, void* stream) {
+  const int st0 = check_band(GBMM_BAND_LOG, B, n, a_lu, a_ld, b_lu, b_ld);
+  if (st0 != GBMM_OK) return st0;
+  if (B == 0 || n == 0) return GBMM_OK;
+  if (!a || !b || !grad_out || !part || !h_a || !h_b || !d_a || !d_b || !d_grad_out) return GBMM_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const BandDims d{n, a_lu, a_ld, b_lu, b_ld};
+  const int64_t co = B * n * d.Wo(), ca = B * n * d.Wa(), cb = B * n * d.Wb();
+  if (ceil_div(co, NT) >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  band_bwd2_t_kernel<<<(unsigned)ceil_div(co, NT), NT, 0, st>>>(a, b, part, h_a, h_b, d_grad_out, d, co);
+  if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+  band_bwd2_a_kernel<<<(unsigned)ceil_div(ca, NT), NT, 0, st>>>(a, b, part, grad_out, d_grad_out, h_a, h_b, d_a, d,
+                                                                ca);
+  if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+  band_bwd2_b_kernel<<<(unsigned)ceil_div(cb, NT), NT, 0, st>>>(a, b, part, grad_out, d_grad_out, h_a, h_b, d_b, d,
+                                                                cb);
+  return launch_status();
 }

@@ -219,6 +219,27 @@ class BandedMul(_BandedProduct):
         return BandedMul._backward(ctx, grad_output)
 
 
+class BandedLogMulBack(torch.autograd.Function):
+    """First-order gradients of the banded log product as a differentiable node (sparse.py:466-508);
+    forward returns (grad_a, grad_b), backward the second-order terms."""
+
+    @staticmethod
+    def forward(ctx, a, b, grad_out, part, bands):
+        ctx.save_for_backward(a, b, grad_out, part)
+        ctx.bands = bands
+        a_lu, a_ld, b_lu, b_ld = bands
+        grad_a, grad_b = _native.backward_band(a, a_lu, a_ld, b, b_lu, b_ld, grad_out, part, _native.BAND_LOG,
+                                               both=True)
+        return grad_a, grad_b
+
+    @staticmethod
+    def backward(ctx, h_a, h_b):
+        a, b, grad_out, part = ctx.saved_tensors
+        a_lu, a_ld, b_lu, b_ld = ctx.bands
+        d_a, d_b, d_g = _native.backbackward_band(a, a_lu, a_ld, b, b_lu, b_ld, grad_out, part, None, h_a, 0, h_b)
+        return d_a, d_b, d_g, None, None
+
+
 class BandedLogMul(_BandedProduct):
     MODE = _native.BAND_LOG
 
@@ -228,7 +249,9 @@ class BandedLogMul(_BandedProduct):
 
     @staticmethod
     def backward(ctx, grad_output):
-        return BandedLogMul._backward(ctx, grad_output)
+        a, b, out = ctx.saved_tensors
+        grad_a, grad_b = BandedLogMulBack.apply(a, b, grad_output.contiguous(), out.detach(), ctx.bands)
+        return grad_a, None, None, grad_b, None, None, None, None
 
 
 class BandedMaxMul(_BandedProduct):

@@ -135,6 +135,19 @@ int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_ld,
                            int64_t B, int64_t n, void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * Banded log-semiring second-order terms.  Replaces `_genbmm.backbackward_band(a, a_lu, a_lb, b,
+ * b_lu, b_lb, grad_output, part, maxes, grad_out_a, 0)` — banded_backbackward,
+ * matmul_cuda.cpp:145-161 -> banded_cuda_backbackward, banded_cuda_kernel.cu:453-546 — extended to
+ * the cotangents of both first-order gradients: for L = <grad_a, h_a> + <grad_b, h_b> it fills
+ * d_a:(B,n,Wa), d_b:(B,n,Wb) and d_grad_out:(B,n,Wo).  part = the forward's out.  Pass zeros for
+ * an absent cotangent.
+ */
+int gbmm_band_backbackward_f32(const float* a, int a_lu, int a_ld, const float* b, int b_lu, int b_ld,
+                               const float* grad_out, const float* part, const float* h_a, const float* h_b,
+                               float* d_a, float* d_b, float* d_grad_out,
+                               int64_t B, int64_t n, void* stream);
+
+/*
  * Factorised log-semiring product (fast path of logbmm).  Same result as
  * gbmm_dense_forward_f32(GBMM_MODE_LOG, ...) / gbmm_dense_backward_f32 within fp32 rounding,
  * computed as ordinary fp32 matrix products of exponentiated operands

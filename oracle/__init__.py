@@ -36,6 +36,7 @@ def lib():
             getattr(_LIB, "orc_dense_bwdbwd_" + suf).argtypes = [_P] * 9 + [_L] * 4
             getattr(_LIB, "orc_band_fwd_" + suf).argtypes = [_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L]
             getattr(_LIB, "orc_band_bwd_" + suf).argtypes = [_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L]
+            getattr(_LIB, "orc_band_bwdbwd_" + suf).argtypes = [_P, _I, _I, _P, _I, _I] + [_P] * 7 + [_L, _L]
             getattr(_LIB, "orc_band_transpose_" + suf).argtypes = [_P, _I, _I, _P, _L, _L]
             for n in ("dense_fwd", "sample_margin", "dense_bwd", "dense_bwdbwd", "band_fwd", "band_bwd",
                       "band_transpose"):
@@ -147,6 +148,18 @@ def band_bwd(mode, a, a_lu, a_ld, b, b_lu, b_ld, g, part, dtype=np.float32):
     getattr(lib(), "orc_band_bwd_" + _suf(dtype))(mode, _ptr(a), a_lu, a_ld, _ptr(b), b_lu, b_ld, _ptr(g),
                                                   _ptr(part), _ptr(dA), B, n)
     return dA
+
+
+def band_bwdbwd(a, a_lu, a_ld, b, b_lu, b_ld, g, part, h_a, h_b=None, dtype=np.float32):
+    """Second-order terms of the banded log product (banded_cuda_kernel.cu:154-350, 453-546): for
+    L = <grad_a, h_a> + <grad_b, h_b> returns (dL/da, dL/db, dL/dg).  The reference has h_a only."""
+    a, b, g, part, h_a = (_np(x, dtype) for x in (a, b, g, part, h_a))
+    h_b = np.zeros_like(b) if h_b is None else _np(h_b, dtype)
+    B, n, _ = a.shape
+    dA, dB, dG = np.zeros_like(a), np.zeros_like(b), np.zeros_like(g)
+    getattr(lib(), "orc_band_bwdbwd_" + _suf(dtype))(_ptr(a), a_lu, a_ld, _ptr(b), b_lu, b_ld, _ptr(g), _ptr(part),
+                                                     _ptr(h_a), _ptr(h_b), _ptr(dA), _ptr(dB), _ptr(dG), B, n)
+    return dA, dB, dG
 
 
 def band_transpose(x, lu, ld, dtype=np.float32):

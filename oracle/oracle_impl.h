@@ -338,6 +338,90 @@ void FN(orc_band_bwd_)(int mode, const REAL *a, int a_lu, int a_ld,
       }
 }
 
+/* banded_cuda_kernel.cu:154-350 (kernels A, B, C): second-order terms of the
+ * log product.  The reference differentiates grad_a only and contracts with
+ * its cotangent h_a[i][m]; here the contracted value of an inner triple is
+ * h_a[i][m] + h_b[o2][m2], which also covers the cotangent of grad_b (h_b all
+ * zero gives the reference's three outputs exactly).  The reference's
+ * exp(x - mx) / exp(part - mx) is written exp(x - part). */
+void FN(orc_band_bwdbwd_)(const REAL *a, int a_lu, int a_ld, const REAL *b,
+                          int b_lu, int b_ld, const REAL *g, const REAL *part,
+                          const REAL *ha, const REAL *hb, REAL *dA, REAL *dB,
+                          REAL *dG, int64_t B, int64_t n) {
+  const int Wa = a_lu + a_ld + 1, Wb = b_lu + b_ld + 1;
+  const int r_lu = a_lu + b_ld, r_ld = a_ld + b_lu, Wo = r_lu + r_ld + 1;
+#define INNER_(i_, k_, jsel_, s_, res_)                                       \
+  do {                                                                        \
+    const int64_t o2_ = (i_) + ((k_) - r_lu);                                 \
+    REAL inner_ = 0;                                                          \
+    for (int m = 0; m < Wa; ++m) {                                            \
+      const int64_t pin_ = (i_) + (m - a_lu), m2_ = (pin_ - o2_) + b_lu;      \
+      if (m2_ < 0 || m2_ >= Wb || pin_ < 0 || pin_ >= n) continue;            \
+      REAL s2_ = EXP(a[(bt * n + (i_)) * Wa + m] +                            \
+                     b[(bt * n + o2_) * Wb + m2_] -                           \
+                     part[(bt * n + (i_)) * Wo + (k_)]);                      \
+      REAL v_ = ((jsel_) == m) ? (s_) - (s_) * s2_ : -(s_) * s2_;             \
+      inner_ += v_ * (ha[(bt * n + (i_)) * Wa + m] +                          \
+                      hb[(bt * n + o2_) * Wb + m2_]);                         \
+    }                                                                         \
+    res_ = inner_;                                                            \
+  } while (0)
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t bt = 0; bt < B; ++bt)
+    for (int64_t i = 0; i < n; ++i)
+      for (int j = 0; j < Wa; ++j) { /* kernel A */
+        const int64_t o = i + (j - a_lu);
+        if (o < 0 || o >= n) continue;
+        REAL val = 0;
+        for (int k = 0; k < Wo; ++k) {
+          const int64_t pos = i + (k - r_lu), k2 = (o - pos) + b_lu;
+          if (k2 < 0 || k2 >= Wb || pos < 0 || pos >= n) continue;
+          REAL s = EXP(a[(bt * n + i) * Wa + j] + b[(bt * n + pos) * Wb + k2] -
+                       part[(bt * n + i) * Wo + k]);
+          REAL inner;
+          INNER_(i, k, j, s, inner);
+          val += inner * g[(bt * n + i) * Wo + k];
+        }
+        dA[(bt * n + i) * Wa + j] = val;
+      }
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t bt = 0; bt < B; ++bt)
+    for (int64_t pos = 0; pos < n; ++pos)
+      for (int k2 = 0; k2 < Wb; ++k2) { /* kernel B */
+        const int64_t check = pos + (k2 - b_lu);
+        if (check < 0 || check >= n) continue;
+        REAL val = 0;
+        for (int k = 0; k < Wo; ++k) {
+          const int64_t i = pos - (k - r_lu);
+          const int64_t j = k2 + pos - b_lu - (i - a_lu);
+          if (j < 0 || j >= Wa || i < 0 || i >= n) continue;
+          REAL s = EXP(a[(bt * n + i) * Wa + j] + b[(bt * n + pos) * Wb + k2] -
+                       part[(bt * n + i) * Wo + k]);
+          REAL inner;
+          INNER_(i, k, (int)j, s, inner);
+          val += inner * g[(bt * n + i) * Wo + k];
+        }
+        dB[(bt * n + pos) * Wb + k2] = val;
+      }
+#undef INNER_
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t bt = 0; bt < B; ++bt)
+    for (int64_t i = 0; i < n; ++i)
+      for (int j = 0; j < Wo; ++j) { /* kernel C */
+        const int64_t o = i + (j - r_lu);
+        if (o < 0 || o >= n) continue;
+        REAL val = 0;
+        for (int k = 0; k < Wa; ++k) {
+          const int64_t pos = i + (k - a_lu), k2 = (pos - o) + b_lu;
+          if (k2 < 0 || k2 >= Wb || pos < 0 || pos >= n) continue;
+          val += EXP(a[(bt * n + i) * Wa + k] + b[(bt * n + o) * Wb + k2] -
+                     part[(bt * n + i) * Wo + j]) *
+                 (ha[(bt * n + i) * Wa + k] + hb[(bt * n + o) * Wb + k2]);
+        }
+        dG[(bt * n + i) * Wo + j] = val;
+      }
+}
+
 /* sparse.py:33-47 with :65-70 — BandedMatrix.transpose() as
  * repdiag(data.flip(-1), lu, ld): out[i,j] = data[i+j-ld, lu+ld-j], zero
  * where the source row is outside [0,n).  The result has (lu,ld) swapped. */

@@ -110,6 +110,18 @@ def banded_cases():
         X, Y = BandedMatrix(xa, alu, ald), BandedMatrix(xb, blu, bld)
         G = BandedMatrix(gout, olu, old)
         put(pre + "mul_back_simple", X.multiply_back_simple(Y, G).data)
+        # second order of the log product (genbmm/test_cuda.py:113-143): gradient of
+        # <grad_a, h_a> + <grad_b, h_b> w.r.t. (a, b, cotangent), by autograd through the loops
+        A = xa.clone().requires_grad_(True)
+        Bm = xb.clone().requires_grad_(True)
+        go = gout.clone().requires_grad_(True)
+        R = BandedMatrix(A, alu, ald, 0).multiply_log_simple(BandedMatrix(Bm, blu, bld, 0))
+        ga, gb = torch.autograd.grad(R.data, (A, Bm), go, create_graph=True)
+        ha = torch.rand(ga.shape, generator=gen)
+        hb = torch.rand(gb.shape, generator=gen)
+        hh = torch.autograd.grad((ga, gb), (A, Bm, go), (ha, hb))
+        for k, v in dict(h_a=ha, h_b=hb, hh_a=hh[0], hh_b=hh[1], hh_g=hh[2]).items():
+            put(pre + "log_" + k, v)
 
 
 def main():

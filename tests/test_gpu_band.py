@@ -165,3 +165,37 @@ def test_band_log_guard_recomputes_flagged_row_blocks(gb, monkeypatch):
     out2, ga2, gb2 = run(gb, "multiply_log", a, lu, ld, b, lu, ld, g)
     assert torch.allclose(out.data, out2.data, rtol=1e-5, atol=2e-5)
     assert torch.allclose(ga, ga2, rtol=3e-4, atol=1e-5) and torch.allclose(gb_, gb2, rtol=3e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("ci", [0, 1, 2, 3, 4])
+def test_band_log_second_order_matches_reference_fixture(gb, golden, ci):
+    """genbmm/test_cuda.py:113-143: gradient of (grad_a, grad_b) w.r.t. (a, b, cotangent); the fixture is
+    float64 autograd through the reference's multiply_log_simple; the reference's own test accepts 1e-2."""
+    B, n, alu, ald, blu, bld = (int(v) for v in golden["band%d_dims" % ci])
+    f = lambda k: torch.from_numpy(golden["band%d_%s" % (ci, k)]).float().cuda()
+    a, b, g = f("a").requires_grad_(True), f("b").requires_grad_(True), f("g").requires_grad_(True)
+    r = gb.BandedMatrix(a, alu, ald).multiply_log(gb.BandedMatrix(b, blu, bld))
+    ga, gb_ = torch.autograd.grad(r.data, (a, b), g, create_graph=True)
+    hh = torch.autograd.grad((ga, gb_), (a, b, g), (f("log_h_a"), f("log_h_b")))
+    ins = lambda lu, ld: band_inside(B, n, lu, ld)
+    assert_close(hh[0], golden["band%d_log_hh_a" % ci] * ins(alu, ald), 1e-4, 1e-5, "d/da")
+    assert_close(hh[1], golden["band%d_log_hh_b" % ci] * ins(blu, bld), 1e-4, 1e-5, "d/db")
+    assert_close(hh[2], golden["band%d_log_hh_g" % ci] * ins(alu + bld, ald + blu), 1e-4, 1e-5, "d/dg")
+
+
+@pytest.mark.parametrize("B,n,alu,ald,blu,bld", [(2, 70, 3, 2, 1, 4), (1, 33, 0, 0, 2, 2), (3, 129, 17, 9, 12, 20)])
+def test_backbackward_band_entry_matches_oracle(B, n, alu, ald, blu, bld):
+    """The reference's call shape `backbackward_band(a, .., grad_out, part, maxes, grad_out_a, 0)`:
+    cotangent of grad_a only (banded_cuda_kernel.cu:453-546)."""
+    from genbmm_b200 import _native
+    rng = np.random.default_rng(n)
+    mk = lambda w: rng.standard_normal((B, n, w)).astype(np.float32)
+    a, b = mk(alu + ald + 1), mk(blu + bld + 1)
+    wo = alu + bld + ald + blu + 1
+    g, h = mk(wo), mk(alu + ald + 1)
+    out, _, _ = oracle.band_fwd(0, a, alu, ald, b, blu, bld)
+    want = oracle.band_bwdbwd(a, alu, ald, b, blu, bld, g, out, h)
+    t = lambda x: torch.from_numpy(x).cuda()
+    got = _native.backbackward_band(t(a), alu, ald, t(b), blu, bld, t(g), t(out), None, t(h), 0)
+    for w, r, name in zip(want, got, ("grad_a", "grad_b", "grad_grad")):
+        assert_close(r, w, 2e-4, 2e-5, name)

@@ -131,3 +131,16 @@ def test_band_mul_back_simple(golden, ci):
     want = oracle.band_transpose(g("mul_back_simple"), ald, alu, dtype=np.float64)
     inside = _inside(B, n, alu, ald)
     assert close(dA[inside], want[inside], 1e-8, 1e-11)
+
+
+@pytest.mark.parametrize("ci", BAND)
+def test_band_log_second_order_f64(golden, ci):
+    """Autograd through the reference's multiply_log_simple (float64) pins the restated kernels A/B/C."""
+    B, n, alu, ald, blu, bld = _dims(golden, ci)
+    g = lambda k: golden["band%d_%s" % (ci, k)]
+    dA, dB, dG = oracle.band_bwdbwd(g("a"), alu, ald, g("b"), blu, bld, g("g"), g("log_out"), g("log_h_a"),
+                                    g("log_h_b"), dtype=np.float64)
+    ins = lambda lu, ld: _inside(B, n, lu, ld)
+    np.testing.assert_allclose(dA, g("log_hh_a") * ins(alu, ald), rtol=1e-9, atol=1e-11)
+    np.testing.assert_allclose(dB, g("log_hh_b") * ins(blu, bld), rtol=1e-9, atol=1e-11)
+    np.testing.assert_allclose(dG, g("log_hh_g") * ins(alu + bld, ald + blu), rtol=1e-9, atol=1e-11)
