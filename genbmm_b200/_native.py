@@ -36,7 +36,7 @@ _SIGNATURES = {
     "gbmm_logbmm_check": ([_P, _P], _I),
     "gbmm_logbmm_tc_workspace_bytes": ([_I, _L, _L, _L, _L], _L),
     "gbmm_logbmm_tc_forward_f32": ([_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
-    "gbmm_logbmm_tc_backward_f32": ([_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
+    "gbmm_logbmm_tc_backward_f32": ([_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
     "gbmm_logbmm_forward_noalloc_max_bytes": ([], _L),
     "gbmm_logbmm_forward_noalloc_need_bytes": ([_L, _L, _L, _L], _L),
     "gbmm_logbmm_forward_noalloc_f32": ([_P, _P, _P, _L, _L, _L, _L, _P], _I),
@@ -282,10 +282,12 @@ def _workspace(nbytes, device):
     return torch.empty((max(int(nbytes), 256),), dtype=torch.uint8, device=device)
 
 
-def logbmm_fast_forward(a, b, check=False, tensor_cores=False):
+def logbmm_fast_forward(a, b, check=False, tensor_cores=False, keep_factors=False):
     """c = logbmm(a, b) by the factorised kernels.  Returns (out, rowmax, colmax, flags); the last
     three are what `logbmm_fast_backward` needs.  Requires K > 0.  tensor_cores=True runs the
-    product as 3xTF32 on tcgen05 instead of the FP32 pipe."""
+    product as 3xTF32 on tcgen05 instead of the FP32 pipe.  keep_factors=True appends the
+    workspace holding the split exponentiated operands (None on the FP32 pipe) for
+    `logbmm_fast_backward(factors=...)`; it is four times the size of a and b."""
     _check_input(a, "a")
     _check_input(b, "b")
     if a.dim() != 3 or b.dim() != 3 or a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1]:
@@ -306,13 +308,16 @@ def logbmm_fast_forward(a, b, check=False, tensor_cores=False):
         _check(st, "gbmm_logbmm_forward_f32")
         if check:
             _check(lib.gbmm_logbmm_check(_ptr(ws), _stream(a.device)), "gbmm_logbmm_forward_f32 (device)")
+    if keep_factors:
+        return out, rowmax, colmax, flags, (ws if tensor_cores else None)
     return out, rowmax, colmax, flags
 
 
 def logbmm_fast_backward(a, b, grad_output, out, rowmax, colmax, flags, check=False, tensor_cores=False,
-                         out_grads=None):
+                         out_grads=None, factors=None):
     """(grad_a, grad_b) of logbmm by the factorised kernels, from what the fast forward saved.
-    `out_grads` = (grad_a, grad_b) buffers to fill instead of allocating new ones."""
+    `out_grads` = (grad_a, grad_b) buffers to fill instead of allocating new ones; `factors` = the
+    workspace `logbmm_fast_forward(keep_factors=True)` returned for the same a, b (tensor cores only)."""
     for x, name in ((a, "a"), (b, "b"), (grad_output, "grad_output"), (out, "out"), (rowmax, "rowmax"),
                     (colmax, "colmax")):
         _check_input(x, name)
@@ -326,8 +331,14 @@ def logbmm_fast_backward(a, b, grad_output, out, rowmax, colmax, flags, check=Fa
         sizer = lib.gbmm_logbmm_tc_workspace_bytes if tensor_cores else lib.gbmm_logbmm_workspace_bytes
         fn = lib.gbmm_logbmm_tc_backward_f32 if tensor_cores else lib.gbmm_logbmm_backward_f32
         ws = _workspace(sizer(1, B, M, K, N), a.device)
-        st = fn(_ptr(a), _ptr(b), _ptr(grad_output), _ptr(out), _ptr(rowmax), _ptr(colmax), _ptr(flags),
-                _ptr(grad_a), _ptr(grad_b), _ptr(ws), ws.numel(), B, M, K, N, _stream(a.device))
+        args = [_ptr(a), _ptr(b), _ptr(grad_output), _ptr(out), _ptr(rowmax), _ptr(colmax), _ptr(flags),
+                _ptr(grad_a), _ptr(grad_b)]
+        if tensor_cores:
+            if factors is not None and (factors.device != a.device or
+                                        factors.numel() < lib.gbmm_logbmm_tc_workspace_bytes(0, B, M, K, N)):
+                raise RuntimeError("factors do not belong to a forward of these shapes on this device")
+            args.append(None if factors is None else _ptr(factors))
+        st = fn(*args, _ptr(ws), ws.numel(), B, M, K, N, _stream(a.device))
         _check(st, "gbmm_logbmm_backward_f32")
         if check:
             _check(lib.gbmm_logbmm_check(_ptr(ws), _stream(a.device)), "gbmm_logbmm_backward_f32 (device)")

@@ -6,8 +6,12 @@
 // split once, while it is exponentiated, into hi = tf32(x) and lo = x - hi, and the product is
 // accumulated as  A_lo*B_hi + A_hi*B_lo + A_hi*B_hi  in one fp32 TMEM accumulator (the dropped
 // lo*lo term is below 2^-22 relative).  Per 128x128 result tile and 32-wide reduction stage:
-// four TMA loads (A_hi, A_lo, B_hi, B_lo: 128 rows x 128 bytes each, 128-byte swizzle) and
+// four TMA loads (A_hi, A_lo, B_hi, B_lo: 16 KB each, 128-byte swizzle) and
 // 12 tcgen05.mma.kind::tf32 instructions (M=128, N=128, K=8).
+// Either operand may be stored with the reduction index contiguous ("K-major": 128 rows of 128
+// bytes) or with the result index contiguous ("MN-major": 4 blocks of 32 reduction rows x 32
+// result indices), so the three products of a step all read EA, EB and G' in the layout a, b and
+// grad_out already have and no transposed copy is made.
 //
 // CTA = 6 warps: warp 0 issues the TMA loads, warp 1 owns the TMEM allocation and issues the
 // MMAs (one elected lane each), warps 2-5 read the accumulator back with tcgen05.ld (each warp
@@ -36,7 +40,7 @@ constexpr int TNB = 4;                 // TMEM accumulation buffers of 128 colum
 constexpr uint32_t kTmemCols = TNB * 128;
 constexpr int TCH = 8;                // stages per accumulation chunk (256 reduction steps)
 
-__host__ __device__ inline int64_t pad4(int64_t x) { return (x + 3) & ~int64_t(3); }
+__host__ __device__ inline int64_t pad32(int64_t x) { return (x + 31) & ~int64_t(31); }
 __host__ __device__ inline int64_t pad64(int64_t x) { return (x + 63) & ~int64_t(63); }
 
 struct alignas(1024) TcSmem {
@@ -69,15 +73,34 @@ __device__ __forceinline__ uint64_t umma_desc(const void* smem_tile, int k_byte_
   return d;
 }
 
-// Instruction descriptor for kind::tf32, fp32 accumulate, both operands K-major, M=128, N=128:
-// c_format F32 (1) at bit 4, a/b format TF32 (2) at bits 7 and 10, N/8 at bit 17, M/16 at bit 24.
+// Descriptor of an MN-major tile.  For 32-bit operands the tensor core reads MN-major tiles only in
+// the "128-byte swizzle with 32-byte atoms" layout (layout type 1; TMA writes it with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B): 32 result indices (128 bytes) contiguous per reduction row,
+// 4 reduction rows per 512-byte swizzle atom.  Here the atoms of one 32-index block are stacked along
+// the reduction (32 rows = 4 KB) and the four blocks of the 128 result indices follow one another:
+// leading byte offset = distance between blocks (4096 B), stride byte offset = distance between
+// 4-row groups (512 B); one K=8 instruction reads two groups, the next starts 1 KB further on.
+__device__ __forceinline__ uint64_t umma_desc_mn(const void* smem_tile, int k_step) {
+  const uint32_t addr = smem_u32(smem_tile) + k_step * 1024;
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(4096 >> 4) << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::tf32, fp32 accumulate, M=128, N=128: c_format F32 (1) at bit 4,
+// a/b format TF32 (2) at bits 7 and 10, a/b MN-major at bits 15 and 16, N/8 at bit 17, M/16 at bit 24.
 constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | ((TN >> 3) << 17) | ((TM >> 4) << 24);
 
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -107,9 +130,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 
-// TMA load of one (128 rows x 32 fp32) box of a 3-D tensor map into a swizzled tile.
+// TMA load of one operand tile (128 result indices from `row`, 32 reduction steps from `k`).
+// K-major: one (128 rows x 32 fp32) box of a 3-D map.  MN-major: one (4 blocks x 32 rows x 32 fp32)
+// box of a 4-D map whose dimensions are (index % 32, reduction row, index / 32, batch).
+template <bool MN>
 __device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* map, uint64_t* bar, int k, int row, int bt) {
-  tma_load_3d(dst, map, bar, k, row, bt);
+  if (MN)
+    tma_load_4d(dst, map, bar, 0, k, row / 32, bt);
+  else
+    tma_load_3d(dst, map, bar, k, row, bt);
 }
 
 enum { TC_LOG = 0, TC_GRAD = 1 };
@@ -123,11 +152,12 @@ struct TcEpi {
   int* error;
 };
 
-// D[i,j] = sum_r A[i,r] B[j,r] with A:(batch,I,R) and B:(batch,J,R), reduction index contiguous.
+// D[i,j] = sum_r A[i,r] B[j,r].  A is stored (batch,I,R) when !A_MN and (batch,R,I) when A_MN; B
+// likewise (batch,J,R) or (batch,R,J).
 // Persistent: the grid has one CTA per SM and CTA c takes tiles c, c + gridDim.x, ...; the three
 // roles keep running stage and chunk counters across tiles, so the loads and MMAs of the next tile
 // proceed (up to TNB chunks ahead) while the epilogue warps are still writing the previous one.
-template <int EPI>
+template <int EPI, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap ma_hi,
                                                          const __grid_constant__ CUtensorMap ma_lo,
                                                          const __grid_constant__ CUtensorMap mb_hi,
@@ -178,16 +208,17 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
             break;
           }
           mbar_arrive_expect_tx(&sm.full[s], 4 * kTileBytes);
-          tma_tile(sm.a_hi[s], &ma_hi, &sm.full[s], t * TK, i0, bt);
-          tma_tile(sm.a_lo[s], &ma_lo, &sm.full[s], t * TK, i0, bt);
-          tma_tile(sm.b_hi[s], &mb_hi, &sm.full[s], t * TK, j0, bt);
-          tma_tile(sm.b_lo[s], &mb_lo, &sm.full[s], t * TK, j0, bt);
+          tma_tile<A_MN>(sm.a_hi[s], &ma_hi, &sm.full[s], t * TK, i0, bt);
+          tma_tile<A_MN>(sm.a_lo[s], &ma_lo, &sm.full[s], t * TK, i0, bt);
+          tma_tile<B_MN>(sm.b_hi[s], &mb_hi, &sm.full[s], t * TK, j0, bt);
+          tma_tile<B_MN>(sm.b_lo[s], &mb_lo, &sm.full[s], t * TK, j0, bt);
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
+      constexpr uint32_t idesc = kIdesc | (A_MN ? 1u << 15 : 0u) | (B_MN ? 1u << 16 : 0u);
       uint32_t it = 0, gc = 0;  // stages and chunks consumed so far
       for (int64_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
         for (int t = 0; t < nt; ++t, ++it) {
@@ -206,11 +237,13 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
 #pragma unroll
           for (int kk = 0; kk < TK / 8; ++kk) {
             const int ko = kk * 8 * (int)sizeof(float);  // 32 bytes per K=8 step inside the 128-byte row
-            const uint64_t ah = umma_desc(sm.a_hi[s], ko), al = umma_desc(sm.a_lo[s], ko);
-            const uint64_t bh = umma_desc(sm.b_hi[s], ko), bl = umma_desc(sm.b_lo[s], ko);
-            umma_tf32(acc, al, bh, (!chunk_start || kk > 0) ? 1u : 0u);
-            umma_tf32(acc, ah, bl, 1u);
-            umma_tf32(acc, ah, bh, 1u);
+            const uint64_t ah = A_MN ? umma_desc_mn(sm.a_hi[s], kk) : umma_desc(sm.a_hi[s], ko);
+            const uint64_t al = A_MN ? umma_desc_mn(sm.a_lo[s], kk) : umma_desc(sm.a_lo[s], ko);
+            const uint64_t bh = B_MN ? umma_desc_mn(sm.b_hi[s], kk) : umma_desc(sm.b_hi[s], ko);
+            const uint64_t bl = B_MN ? umma_desc_mn(sm.b_lo[s], kk) : umma_desc(sm.b_lo[s], ko);
+            umma_tf32(acc, al, bh, idesc, (!chunk_start || kk > 0) ? 1u : 0u);
+            umma_tf32(acc, ah, bl, idesc, 1u);
+            umma_tf32(acc, ah, bh, idesc, 1u);
           }
           umma_commit(&sm.empty[s]);  // stage s may be refilled once these MMAs have read it
           if ((t % TCH) == TCH - 1 || t == nt - 1) {
@@ -338,143 +371,134 @@ __device__ __forceinline__ float tf32_round(float x) {
   return __uint_as_float(r);
 }
 
-// 64x64 tiles of a (batch, R, C) tensor: v = transform(src), then hi = tf32(v), lo = v - hi written
-// in the same orientation (n_hi/n_lo, pitch pad4(C)) and/or transposed (t_hi/t_lo: (batch, C, R),
-// pitch pad4(R)); null destinations are skipped.  KIND as in dense_fast.cu:
+// v = transform(src) over a (batch, R, C) tensor, then hi = tf32(v), lo = v - hi written in the same
+// orientation with rows `pitch` (a multiple of 32) floats apart; the padding columns are never
+// written: as reduction steps the tensor map cuts them off, as result indices they only reach
+// results the epilogue does not store.  KIND as in dense_fast.cu:
 //   0: exp(src - shift[r])   1: exp(src - shift[c])   2: g * exp(shift[r] + shift2[c] - src), 0 if flagged
-// VEC: C % 4 == 0 and every pointer 16-byte aligned -> 128-bit loads and stores.
-struct SplitDst {
-  float* n_hi;
-  float* n_lo;
-  float* t_hi;
-  float* t_lo;
-};
-
+// One thread per 4 consecutive columns; VEC: C % 4 == 0 and src, g 16-byte aligned -> 128-bit loads.
 template <int KIND, bool VEC>
 __global__ void __launch_bounds__(256) split_transform_kernel(const float* __restrict__ src,
                                                               const float* __restrict__ shift,
                                                               const float* __restrict__ shift2,
                                                               const float* __restrict__ g,
-                                                              const int* __restrict__ flags, SplitDst d, int R, int C,
-                                                              int tiles_r, int tiles_c) {
-  __shared__ float tile[64][65];
-  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
-  const int64_t id = blockIdx.x;
-  const int c0 = (int)(id % tiles_c) * 64, r0 = (int)((id / tiles_c) % tiles_r) * 64;
-  const int64_t bt = id / ((int64_t)tiles_c * tiles_r);
-  const float* sb = src + bt * R * C;
-  const float* gb = KIND == 2 ? g + bt * R * C : nullptr;
-  const int64_t pc = pad4(C), pr = pad4(R);
-  bool dead = false;
-  if (KIND == 2) dead = __ldg(flags + (bt * ((R + 127) / 128) + r0 / 128) * ((C + 127) / 128) + c0 / 128) != 0;
-  const int c = c0 + tx * 4;
+                                                              const int* __restrict__ flags, float* __restrict__ hi_out,
+                                                              float* __restrict__ lo_out, int R, int C, int64_t pitch,
+                                                              int64_t groups) {
+  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (e >= groups) return;
+  const int gpr = (C + 3) / 4;  // groups per row
+  const int c = (int)(e % gpr) * 4;
+  const int64_t row = e / gpr;  // bt * R + r
+  const int r = (int)(row % R);
+  const int64_t bt = row / R;
+  float x[4] = {0.f, 0.f, 0.f, 0.f}, gv[4] = {0.f, 0.f, 0.f, 0.f}, sc[4] = {0.f, 0.f, 0.f, 0.f};
+  const float* sp = src + row * C + c;
+  const bool full = c + 3 < C;
+  if (VEC) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(sp));
+    x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+    if (KIND == 2) {
+      const float4 u = __ldg(reinterpret_cast<const float4*>(g + row * C + c));
+      gv[0] = u.x; gv[1] = u.y; gv[2] = u.z; gv[3] = u.w;
+    }
+  } else {
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const int rl = ty + q * 16, r = r0 + rl;
-    float x[4] = {0.f, 0.f, 0.f, 0.f}, gv[4] = {0.f, 0.f, 0.f, 0.f}, v[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool row_ok = r < R;
-    if (row_ok) {
-      if (VEC) {
-        if (c < C) {
-          const float4 t = __ldg(reinterpret_cast<const float4*>(sb + (int64_t)r * C + c));
-          x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
-          if (KIND == 2) {
-            const float4 u = __ldg(reinterpret_cast<const float4*>(gb + (int64_t)r * C + c));
-            gv[0] = u.x; gv[1] = u.y; gv[2] = u.z; gv[3] = u.w;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          if (c + k < C) {
-            x[k] = __ldg(sb + (int64_t)r * C + c + k);
-            if (KIND == 2) gv[k] = __ldg(gb + (int64_t)r * C + c + k);
-          }
+    for (int k = 0; k < 4; ++k)
+      if (c + k < C) {
+        x[k] = __ldg(sp + k);
+        if (KIND == 2) gv[k] = __ldg(g + row * C + c + k);
       }
-      const float sr = KIND != 1 ? __ldg(shift + bt * R + r) : 0.f;
+  }
+  if (KIND != 0) {
+    const float* cs = (KIND == 1 ? shift : shift2) + bt * C + c;
+    if (VEC) {  // C % 4 == 0: bt * C + c is a multiple of 4; the shift vectors are 16-byte aligned
+      const float4 t = __ldg(reinterpret_cast<const float4*>(cs));
+      sc[0] = t.x; sc[1] = t.y; sc[2] = t.z; sc[3] = t.w;
+    } else {
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        if (c + k < C) {
-          if (KIND == 0) v[k] = exp_sfu(x[k] - sr);
-          if (KIND == 1) v[k] = exp_sfu(x[k] - __ldg(shift + bt * C + c + k));
-          if (KIND == 2) v[k] = dead ? 0.f : gv[k] * exp_sfu((sr + __ldg(shift2 + bt * C + c + k)) - x[k]);
-        }
-      if (d.n_hi) {
-        float hi[4], lo[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          hi[k] = tf32_round(v[k]);
-          lo[k] = v[k] - hi[k];
-        }
-        float* ph = d.n_hi + (bt * R + r) * pc + c;
-        float* pl = d.n_lo + (bt * R + r) * pc + c;
-        if (c < C) {  // pitch pad4(C): a group that straddles C lands in the row's padding
-          *reinterpret_cast<float4*>(ph) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-          *reinterpret_cast<float4*>(pl) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-        }
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < 4; ++k) tile[rl][tx * 4 + k] = v[k];
-  }
-  if (d.t_hi) {
-    __syncthreads();
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int cl = ty + q * 16, cc = c0 + cl, r = r0 + tx * 4;
-      if (cc < C && r < R) {
-        float hi[4], lo[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float v = tile[tx * 4 + k][cl];
-          hi[k] = tf32_round(v);
-          lo[k] = v - hi[k];
-        }
-        *reinterpret_cast<float4*>(d.t_hi + (bt * C + cc) * pr + r) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<float4*>(d.t_lo + (bt * C + cc) * pr + r) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-      }
+        if (c + k < C) sc[k] = __ldg(cs + k);
     }
   }
+  const float sr = KIND != 1 ? __ldg(shift + row) : 0.f;
+  bool dead = false;
+  if (KIND == 2) dead = __ldg(flags + (bt * ((R + 127) / 128) + r / 128) * ((C + 127) / 128) + c / 128) != 0;
+  float hi[4], lo[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float v;
+    if (KIND == 0) v = exp_sfu(x[k] - sr);
+    if (KIND == 1) v = exp_sfu(x[k] - sc[k]);
+    if (KIND == 2) v = dead ? 0.f : gv[k] * exp_sfu((sr + sc[k]) - x[k]);
+    if (!full && c + k >= C) v = 0.f;
+    hi[k] = tf32_round(v);
+    lo[k] = v - hi[k];
+  }
+  // pitch % 32 == 0 and c % 4 == 0: the group is 16-byte aligned and lies inside the row's pitch
+  *reinterpret_cast<float4*>(hi_out + row * pitch + c) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+  *reinterpret_cast<float4*>(lo_out + row * pitch + c) = make_float4(lo[0], lo[1], lo[2], lo[3]);
 }
 
 template <int KIND>
 int launch_split(const float* src, const float* shift, const float* shift2, const float* g, const int* flags,
-                 const SplitDst& d, int64_t B, int64_t R, int64_t C, cudaStream_t st) {
-  const int64_t tr = ceil_div(R, 64), tcn = ceil_div(C, 64), blocks = B * tr * tcn;
+                 float* hi, float* lo, int64_t B, int64_t R, int64_t C, cudaStream_t st) {
+  const int64_t groups = B * R * ceil_div(C, 4), blocks = ceil_div(groups, 256);
   if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  const bool vec = (C % 4 == 0) && al16(src) && (!g || al16(g));
+  const bool vec = (C % 4 == 0) && al16(src) && (!g || al16(g)) && (KIND == 0 || al16(KIND == 1 ? shift : shift2));
   if (vec)
-    split_transform_kernel<KIND, true><<<(unsigned)blocks, 256, 0, st>>>(src, shift, shift2, g, flags, d, (int)R,
-                                                                        (int)C, (int)tr, (int)tcn);
+    split_transform_kernel<KIND, true><<<(unsigned)blocks, 256, 0, st>>>(src, shift, shift2, g, flags, hi, lo, (int)R,
+                                                                        (int)C, pad32(C), groups);
   else
-    split_transform_kernel<KIND, false><<<(unsigned)blocks, 256, 0, st>>>(src, shift, shift2, g, flags, d, (int)R,
-                                                                         (int)C, (int)tr, (int)tcn);
+    split_transform_kernel<KIND, false><<<(unsigned)blocks, 256, 0, st>>>(src, shift, shift2, g, flags, hi, lo,
+                                                                         (int)R, (int)C, pad32(C), groups);
   return launch_status();
 }
 
-// (batch, rows, cols) fp32, pitch % 4 == 0; boxes of 128 rows x 32 columns, 128-byte swizzle
+// Tensor map over a (batch, rows, cols) fp32 array with rows `pitch` (a multiple of 32) apart, 128-byte
+// swizzle (16-byte atoms for !MN, 32-byte atoms for MN).  !MN: the columns are the reduction index; boxes of 128 rows x 32 columns.  MN: the rows are
+// the reduction index; dimensions (col % 32, row, col / 32, batch), boxes of 32 x 32 rows x 4 blocks.
+// Reduction steps outside the array read as zero.
+template <bool MN>
 bool make_map_sw128(CUtensorMap* map, const float* base, uint64_t batch, uint64_t rows, uint64_t cols,
                     uint64_t pitch) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch & 3)) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch & 31)) return false;
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (MN) {
+    const cuuint64_t dims[4] = {32, rows, pitch / 32, batch};
+    const cuuint64_t strides[3] = {pitch * sizeof(float), 32 * sizeof(float), rows * pitch * sizeof(float)};
+    const cuuint32_t box[4] = {32, TK, TM / 32, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
   const cuuint64_t dims[3] = {cols, rows, batch};
   const cuuint64_t strides[2] = {pitch * sizeof(float), rows * pitch * sizeof(float)};
   const cuuint32_t box[3] = {TK, TM, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int EPI>
-int launch_tc(const float* a_hi, const float* a_lo, int64_t a_pitch, const float* b_hi, const float* b_lo,
-              int64_t b_pitch, const TcEpi& ep, int64_t B, int64_t R, int64_t I, int64_t J, cudaStream_t st,
-              int slot) {
+// One operand of a product: hi/lo arrays of shape (batch, rows, cols) with the given pitch.
+struct TcOperand {
+  const float* hi;
+  const float* lo;
+  int64_t rows, cols, pitch;
+};
+
+// D:(batch,I,J) = A B^T over R reduction steps.  !A_MN: A is (batch, I, R); A_MN: (batch, R, I); B likewise.
+template <int EPI, bool A_MN, bool B_MN>
+int launch_tc(const TcOperand& A, const TcOperand& Bo, const TcEpi& ep, int64_t B, int64_t R, int64_t I, int64_t J,
+              cudaStream_t st, int slot) {
   CUtensorMap m0, m1, m2, m3;
-  if (!make_map_sw128(&m0, a_hi, B, I, R, a_pitch) || !make_map_sw128(&m1, a_lo, B, I, R, a_pitch) ||
-      !make_map_sw128(&m2, b_hi, B, J, R, b_pitch) || !make_map_sw128(&m3, b_lo, B, J, R, b_pitch))
+  if (!make_map_sw128<A_MN>(&m0, A.hi, B, A.rows, A.cols, A.pitch) ||
+      !make_map_sw128<A_MN>(&m1, A.lo, B, A.rows, A.cols, A.pitch) ||
+      !make_map_sw128<B_MN>(&m2, Bo.hi, B, Bo.rows, Bo.cols, Bo.pitch) ||
+      !make_map_sw128<B_MN>(&m3, Bo.lo, B, Bo.rows, Bo.cols, Bo.pitch))
     return GBMM_ERR_LAUNCH;
   const int64_t ti = ceil_div(I, TM), tj = ceil_div(J, TN), tiles = B * ti * tj;
   int dev = 0, sms = 0;
@@ -483,12 +507,12 @@ int launch_tc(const float* a_hi, const float* a_lo, int64_t a_pitch, const float
     return GBMM_ERR_DEVICE;
   const unsigned blocks = (unsigned)(tiles < sms ? tiles : sms);  // one persistent CTA per SM
   const size_t smem = sizeof(TcSmem) + 1024;
-  if (cudaFuncSetAttribute(tc_gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-      cudaSuccess)
+  if (cudaFuncSetAttribute(tc_gemm_kernel<EPI, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem) != cudaSuccess)
     return GBMM_ERR_LAUNCH;
   const bool timed = profile_begin(slot, st);
-  tc_gemm_kernel<EPI><<<blocks, TNT, smem, st>>>(m0, m1, m2, m3, ep, (int)R, (int)I, (int)J, (int)ti, (int)tj,
-                                                tiles);
+  tc_gemm_kernel<EPI, A_MN, B_MN><<<blocks, TNT, smem, st>>>(m0, m1, m2, m3, ep, (int)R, (int)I, (int)J, (int)ti,
+                                                            (int)tj, tiles);
   if (timed) profile_end(slot, st);
   return launch_status();
 }
@@ -499,6 +523,29 @@ float* carve(float*& cursor, int64_t floats) {
   return p;
 }
 
+// The exponentiated, split operands EA:(B,M,pad32(K)) and EB:(B,K,pad32(N)); the forward writes them
+// behind the 64-float header of its workspace, the backward reads them from there or rebuilds them.
+struct Factors {
+  float *ea_hi, *ea_lo, *eb_hi, *eb_lo;
+};
+int64_t factor_floats(int64_t B, int64_t M, int64_t K, int64_t N) {
+  return 2 * pad64(B * M * pad32(K)) + 2 * pad64(B * K * pad32(N));
+}
+Factors carve_factors(float*& cur, int64_t B, int64_t M, int64_t K, int64_t N) {
+  Factors f;
+  f.ea_hi = carve(cur, B * M * pad32(K));
+  f.ea_lo = carve(cur, B * M * pad32(K));
+  f.eb_hi = carve(cur, B * K * pad32(N));
+  f.eb_lo = carve(cur, B * K * pad32(N));
+  return f;
+}
+int build_factors(const float* a, const float* b, const float* rowmax, const float* colmax, const Factors& f,
+                  int64_t B, int64_t M, int64_t K, int64_t N, cudaStream_t st) {
+  int rc = launch_split<0>(a, rowmax, nullptr, nullptr, nullptr, f.ea_hi, f.ea_lo, B, M, K, st);
+  if (rc != GBMM_OK) return rc;
+  return launch_split<1>(b, colmax, nullptr, nullptr, nullptr, f.eb_hi, f.eb_lo, B, K, N, st);
+}
+
 }  // namespace
 }  // namespace gbmm
 
@@ -506,11 +553,8 @@ using namespace gbmm;
 
 extern "C" int64_t gbmm_logbmm_tc_workspace_bytes(int backward, int64_t B, int64_t M, int64_t K, int64_t N) {
   if (B < 0 || M < 0 || K < 0 || N < 0) return -1;
-  int64_t floats = 64;
-  if (!backward)
-    floats += 2 * pad64(B * M * pad4(K)) + 2 * pad64(B * N * pad4(K));
-  else
-    floats += 2 * (pad64(B * M * pad4(N)) + pad64(B * K * pad4(N)) + pad64(B * K * pad4(M)) + pad64(B * N * pad4(M)));
+  int64_t floats = 64 + factor_floats(B, M, K, N);
+  if (backward) floats += 2 * pad64(B * M * pad32(N));
   return floats * (int64_t)sizeof(float);
 }
 
@@ -528,29 +572,27 @@ extern "C" int gbmm_logbmm_tc_forward_f32(const float* a, const float* b, float*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* cur = static_cast<float*>(workspace);
   int* error = reinterpret_cast<int*>(carve(cur, 64));
-  float* ea_hi = carve(cur, B * M * pad4(K));
-  float* ea_lo = carve(cur, B * M * pad4(K));
-  float* ebt_hi = carve(cur, B * N * pad4(K));
-  float* ebt_lo = carve(cur, B * N * pad4(K));
+  const Factors f = carve_factors(cur, B, M, K, N);
   if (cudaMemsetAsync(error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
   int rc = launch_rowcol_max(a, b, rowmax, colmax, B, M, K, N, st);
   if (rc != GBMM_OK) return rc;
-  rc = launch_split<0>(a, rowmax, nullptr, nullptr, nullptr, SplitDst{ea_hi, ea_lo, nullptr, nullptr}, B, M, K, st);
-  if (rc != GBMM_OK) return rc;
-  rc = launch_split<1>(b, colmax, nullptr, nullptr, nullptr, SplitDst{nullptr, nullptr, ebt_hi, ebt_lo}, B, K, N, st);
+  rc = build_factors(a, b, rowmax, colmax, f, B, M, K, N, st);
   if (rc != GBMM_OK) return rc;
   if (cudaMemsetAsync(flags, 0, sizeof(int) * B * ceil_div(M, TM) * ceil_div(N, TN), st) != cudaSuccess)
     return GBMM_ERR_LAUNCH;
+  // out[m,n] = ra[m] + rb[n] + log sum_k EA[m,k] EB[k,n]
   TcEpi ep{out, rowmax, colmax, nullptr, flags, error};
-  rc = launch_tc<TC_LOG>(ea_hi, ea_lo, pad4(K), ebt_hi, ebt_lo, pad4(K), ep, B, K, M, N, st, 0);
+  rc = launch_tc<TC_LOG, false, true>(TcOperand{f.ea_hi, f.ea_lo, M, K, pad32(K)},
+                                      TcOperand{f.eb_hi, f.eb_lo, K, N, pad32(N)}, ep, B, K, M, N, st, 0);
   if (rc != GBMM_OK) return rc;
   return launch_log_fwd_flagged(a, b, out, flags, B, M, K, N, st);
 }
 
 extern "C" int gbmm_logbmm_tc_backward_f32(const float* a, const float* b, const float* grad_out, const float* out,
                                            const float* rowmax, const float* colmax, const int32_t* flags,
-                                           float* grad_a, float* grad_b, void* workspace, int64_t workspace_bytes,
-                                           int64_t B, int64_t M, int64_t K, int64_t N, void* stream) {
+                                           float* grad_a, float* grad_b, const void* factors, void* workspace,
+                                           int64_t workspace_bytes, int64_t B, int64_t M, int64_t K, int64_t N,
+                                           void* stream) {
   if (B < 0 || M < 0 || K < 0 || N < 0) return GBMM_ERR_INVALID_ARG;
   if (B == 0 || K == 0) return GBMM_OK;
   if (M == 0 || N == 0) return GBMM_ERR_UNSUPPORTED;
@@ -558,37 +600,37 @@ extern "C" int gbmm_logbmm_tc_backward_f32(const float* a, const float* b, const
   const int64_t lim = (1LL << 31) - 256;
   if (M >= lim || K >= lim || N >= lim) return GBMM_ERR_UNSUPPORTED;
   if (workspace_bytes < gbmm_logbmm_tc_workspace_bytes(1, B, M, K, N)) return GBMM_ERR_INVALID_ARG;
-  if (reinterpret_cast<uintptr_t>(workspace) & 255) return GBMM_ERR_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(factors) & 255))
+    return GBMM_ERR_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* cur = static_cast<float*>(workspace);
   int* error = reinterpret_cast<int*>(carve(cur, 64));
-  float* gp_hi = carve(cur, B * M * pad4(N));   // G'   : (B, M, pad4(N))
-  float* gp_lo = carve(cur, B * M * pad4(N));
-  float* eb_hi = carve(cur, B * K * pad4(N));   // EB   : (B, K, pad4(N))
-  float* eb_lo = carve(cur, B * K * pad4(N));
-  float* eat_hi = carve(cur, B * K * pad4(M));  // EA^T : (B, K, pad4(M))
-  float* eat_lo = carve(cur, B * K * pad4(M));
-  float* gt_hi = carve(cur, B * N * pad4(M));   // G'^T : (B, N, pad4(M))
-  float* gt_lo = carve(cur, B * N * pad4(M));
+  Factors f = carve_factors(cur, B, M, K, N);
+  float* gp_hi = carve(cur, B * M * pad32(N));  // G' : (B, M, pad32(N))
+  float* gp_lo = carve(cur, B * M * pad32(N));
   if (cudaMemsetAsync(error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
-  int rc = launch_split<2>(out, rowmax, colmax, grad_out, flags,
-                           SplitDst{grad_a ? gp_hi : nullptr, gp_lo, grad_b ? gt_hi : nullptr, gt_lo}, B, M, N, st);
+  int rc = GBMM_OK;
+  if (factors) {  // the forward's workspace: same header, same carving
+    float* fc = const_cast<float*>(static_cast<const float*>(factors)) + 64;
+    f = carve_factors(fc, B, M, K, N);
+  } else {
+    rc = build_factors(a, b, rowmax, colmax, f, B, M, K, N, st);
+    if (rc != GBMM_OK) return rc;
+  }
+  rc = launch_split<2>(out, rowmax, colmax, grad_out, flags, gp_hi, gp_lo, B, M, N, st);
   if (rc != GBMM_OK) return rc;
+  const TcOperand EA{f.ea_hi, f.ea_lo, M, K, pad32(K)}, EB{f.eb_hi, f.eb_lo, K, N, pad32(N)};
+  const TcOperand GP{gp_hi, gp_lo, M, N, pad32(N)};
   if (grad_a) {
     // grad_a[m,k] = EA[m,k] * sum_n G'[m,n] EB[k,n]
-    rc = launch_split<1>(b, colmax, nullptr, nullptr, nullptr, SplitDst{eb_hi, eb_lo, nullptr, nullptr}, B, K, N, st);
-    if (rc != GBMM_OK) return rc;
     TcEpi ep{grad_a, rowmax, nullptr, a, nullptr, error};
-    rc = launch_tc<TC_GRAD>(gp_hi, gp_lo, pad4(N), eb_hi, eb_lo, pad4(N), ep, B, N, M, K, st, 1);
+    rc = launch_tc<TC_GRAD, false, false>(GP, EB, ep, B, N, M, K, st, 1);
     if (rc != GBMM_OK) return rc;
   }
   if (grad_b) {
     // grad_b[k,n] = EB[k,n] * sum_m EA[m,k] G'[m,n]
-    rc = launch_split<0>(a, rowmax, nullptr, nullptr, nullptr, SplitDst{nullptr, nullptr, eat_hi, eat_lo}, B, M, K,
-                         st);
-    if (rc != GBMM_OK) return rc;
     TcEpi ep{grad_b, nullptr, colmax, b, nullptr, error};
-    rc = launch_tc<TC_GRAD>(eat_hi, eat_lo, pad4(M), gt_hi, gt_lo, pad4(M), ep, B, M, K, N, st, 2);
+    rc = launch_tc<TC_GRAD, true, true>(EA, GP, ep, B, M, K, N, st, 2);
     if (rc != GBMM_OK) return rc;
   }
   return launch_log_bwd_flagged(a, b, out, grad_out, grad_a, grad_b, flags, B, M, K, N, st);

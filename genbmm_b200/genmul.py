@@ -49,7 +49,7 @@ class LogMatMulBack(torch.autograd.Function):
     """First-order gradients of logbmm as a differentiable node (genmul.py:11-24).
 
     forward returns (grad_a, grad_b) in one call.  `aux` is None after the exact forward, or
-    (rowmax, colmax, flags, tensor_cores) of the factorised forward.
+    (rowmax, colmax, flags, tensor_cores, factors) of the factorised forward.
     """
 
     @staticmethod
@@ -58,7 +58,8 @@ class LogMatMulBack(torch.autograd.Function):
         if aux is None:
             grad_a, grad_b = _native.backward(a, b, grad_out, part, None, _native.MODE_LOG)
         else:
-            grad_a, grad_b = _native.logbmm_fast_backward(a, b, grad_out, part, *aux[:3], tensor_cores=aux[3])
+            grad_a, grad_b = _native.logbmm_fast_backward(a, b, grad_out, part, *aux[:3], tensor_cores=aux[3],
+                                                          factors=aux[4])
         return grad_a, grad_b
 
     @staticmethod
@@ -78,8 +79,12 @@ class LogMatMul(torch.autograd.Function):
         path = _log_path(a32.shape[1], a32.shape[2], b32.shape[-1]) if a32.dim() == 3 and b32.dim() == 3 else "exact"
         if path != "exact":
             tc = path == "tensor"
-            out, rowmax, colmax, flags = _native.logbmm_fast_forward(a32, b32, tensor_cores=tc)
-            ctx.aux = (rowmax, colmax, flags, tc)
+            # the split exponentiated operands (4x the size of a and b) stay alive until the backward
+            # unless GENBMM_B200_KEEP_FACTORS=0, in which case the backward rebuilds them
+            keep = tc and os.environ.get("GENBMM_B200_KEEP_FACTORS", "1") != "0"
+            out, rowmax, colmax, flags, factors = _native.logbmm_fast_forward(a32, b32, tensor_cores=tc,
+                                                                              keep_factors=True)
+            ctx.aux = (rowmax, colmax, flags, tc, factors if keep else None)
         else:
             out, _ = _native.forward(a32, b32, _native.MODE_LOG, want_maxes=False)
         ctx.save_for_backward(a32, b32, out)

@@ -57,10 +57,11 @@ class HostPipeline:
             for i, (lo, hi) in enumerate(self.bounds):
                 comp.wait_event(self.ev_in[i])
                 a, b = self.a[lo:hi], self.b[lo:hi]
-                out, rowmax, colmax, flags = _native.logbmm_fast_forward(a, b, tensor_cores=self.tensor_cores)
+                out, rowmax, colmax, flags, factors = _native.logbmm_fast_forward(
+                    a, b, tensor_cores=self.tensor_cores, keep_factors=True)
                 self.loss += out.sum(dtype=torch.float64)
                 ga, gb = _native.logbmm_fast_backward(a, b, self.ones[: hi - lo], out, rowmax, colmax, flags,
-                                                      tensor_cores=self.tensor_cores,
+                                                      tensor_cores=self.tensor_cores, factors=factors,
                                                       out_grads=(self.grad_a[lo:hi], self.grad_b[lo:hi]))
                 self.ev_done[i].record(comp)
                 with torch.cuda.stream(self.s_out):

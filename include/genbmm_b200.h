@@ -182,6 +182,9 @@ int gbmm_logbmm_check(const void* workspace, void* stream);
  * TMEM).  Same arguments and outputs; its own, larger workspace
  * (gbmm_logbmm_tc_workspace_bytes).  rowmax / colmax / flags are interchangeable with the ones of
  * gbmm_logbmm_forward_f32 for the purposes of gbmm_logbmm_backward_f32.
+ * The forward leaves the split operands exp(a - rowmax), exp(b - colmax) in its workspace; passed
+ * unmodified to the backward of the same (a, b) as `factors`, they are reused instead of rebuilt
+ * (null = rebuild them; the backward workspace is sized for that case either way).
  */
 int64_t gbmm_logbmm_tc_workspace_bytes(int backward, int64_t B, int64_t M, int64_t K, int64_t N);
 int gbmm_logbmm_tc_forward_f32(const float* a, const float* b, float* out, float* rowmax, float* colmax,
@@ -189,7 +192,8 @@ int gbmm_logbmm_tc_forward_f32(const float* a, const float* b, float* out, float
                                int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
 int gbmm_logbmm_tc_backward_f32(const float* a, const float* b, const float* grad_out, const float* out,
                                 const float* rowmax, const float* colmax, const int32_t* flags,
-                                float* grad_a, float* grad_b, void* workspace, int64_t workspace_bytes,
+                                float* grad_a, float* grad_b, const void* factors,
+                                void* workspace, int64_t workspace_bytes,
                                 int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
 
 /*

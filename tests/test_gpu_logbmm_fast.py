@@ -21,8 +21,14 @@ def nat():
 
 def fast_fwd_bwd(nat, a, b, g, tc=False):
     ad, bd, gd = a.cuda(), b.cuda(), g.cuda()
-    out, rowmax, colmax, flags = nat.logbmm_fast_forward(ad, bd, check=True, tensor_cores=tc)
+    out, rowmax, colmax, flags, factors = nat.logbmm_fast_forward(ad, bd, check=True, tensor_cores=tc,
+                                                                  keep_factors=True)
     ga, gb = nat.logbmm_fast_backward(ad, bd, gd, out, rowmax, colmax, flags, check=True, tensor_cores=tc)
+    if tc:  # reusing the forward's split operands gives the same bits as rebuilding them
+        assert factors is not None
+        ga2, gb2 = nat.logbmm_fast_backward(ad, bd, gd, out, rowmax, colmax, flags, check=True, tensor_cores=True,
+                                            factors=factors)
+        assert torch.equal(ga, ga2) and torch.equal(gb, gb2)
     return out, ga, gb, flags
 
 
