@@ -24,6 +24,8 @@
 // chunk_full: commit -> epilogue; chunk_empty: epilogue -> MMA).  Every wait is bounded; a wait that gives up sets the error
 // word, and all paths meet at the final barrier so that the TMEM columns are always released.
 // No cluster launch, no multicast, cta_group::1 only.
+#include <cstdlib>
+
 #include "dense.cuh"
 #include "tma.cuh"
 
@@ -152,6 +154,101 @@ struct TcEpi {
   int* error;
 };
 
+// Pulls the part of `src` that store_sums will read for this warp (32 rows x NSUM columns) into L2
+// while the tile is still being accumulated; lane = row, one request per 128-byte line.
+template <int NSUM>
+__device__ __forceinline__ void prefetch_src(const float* src, int bt, int row0, int col0, int I, int J, int lane) {
+  const int ii = row0 + lane;
+  if (!src || ii >= I) return;
+  const float* p = src + ((int64_t)bt * I + ii) * J + col0;
+#pragma unroll
+  for (int q = 0; q < NSUM; q += 32)
+    if (col0 + q < J) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + q));
+}
+
+// Epilogue of one warp: its NSUM sums per lane (lane = result row row0 + lane, columns col0 ..
+// col0 + NSUM - 1) become log(S) + shifts (TC_LOG) or exp(src - shift) * S (TC_GRAD) in global memory.
+template <int EPI, int NSUM>
+__device__ __forceinline__ void store_sums(const float (&sum)[NSUM], float* blk, const TcEpi& ep, int bt, int row0,
+                                           int col0, int I, int J, int lane, bool& bad) {
+  // Hand the sums over through shared memory so that global memory is touched along rows:
+  // lane = row when writing the warp's private 32x32 block, 8 lanes x 4 columns per row when
+  // reading it back; one pass per 32 of the warp's columns.  All global loads of a pass are issued
+  // before any is used (the registers of the sums just handed over hold them).
+  const int hl = lane % 8, hr = lane / 8;
+  const bool vec = (J % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) &&
+                   (!ep.src || (reinterpret_cast<uintptr_t>(ep.src) & 15) == 0) &&
+                   (!ep.col_v || (reinterpret_cast<uintptr_t>(ep.col_v) & 15) == 0);
+#pragma unroll
+  for (int pass = 0; pass < NSUM / 32; ++pass) {
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < 32; ++q) blk[lane * 33 + q] = sum[pass * 32 + q];
+    __syncwarp();
+    const int jj = col0 + pass * 32 + hl * 4;
+    if (jj >= J) continue;
+    const bool full4 = vec && jj + 3 < J;
+    float cv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ep.col_v) {
+      if (full4) {
+        const float4 t4 = __ldg(reinterpret_cast<const float4*>(ep.col_v + (int64_t)bt * J + jj));
+        cv[0] = t4.x; cv[1] = t4.y; cv[2] = t4.z; cv[3] = t4.w;
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (jj + k < J) cv[k] = __ldg(ep.col_v + (int64_t)bt * J + jj + k);
+      }
+    }
+    float x[8][4], rv[8];
+#pragma unroll
+    for (int itr = 0; itr < 8; ++itr) {
+      const int ii = row0 + itr * 4 + hr;
+      rv[itr] = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[itr][k] = 0.f;
+      if (ii >= I) continue;
+      if (ep.row_v) rv[itr] = __ldg(ep.row_v + (int64_t)bt * I + ii);
+      if (EPI == TC_GRAD) {
+        const float* sp = ep.src + ((int64_t)bt * I + ii) * J + jj;
+        if (full4) {
+          const float4 t4 = __ldg(reinterpret_cast<const float4*>(sp));
+          x[itr][0] = t4.x; x[itr][1] = t4.y; x[itr][2] = t4.z; x[itr][3] = t4.w;
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (jj + k < J) x[itr][k] = __ldg(sp + k);
+        }
+      }
+    }
+#pragma unroll
+    for (int itr = 0; itr < 8; ++itr) {
+      const int r = itr * 4 + hr;
+      const int ii = row0 + r;
+      if (ii >= I) continue;
+      float o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float v = blk[r * 33 + hl * 4 + k];
+        if (EPI == TC_LOG) {
+          const float shift = rv[itr] + cv[k];
+          if (jj + k < J) bad |= !(v >= kTiny) || !(v <= 3.0e38f) || (shift < kFloor);
+          o[k] = __logf(v) + shift;  // lg2.approx: absolute error below 2e-7 on the logarithm
+        } else {
+          o[k] = exp_sfu(x[itr][k] - (rv[itr] + cv[k])) * v;
+        }
+      }
+      float* op = ep.out + ((int64_t)bt * I + ii) * J + jj;
+      if (full4) {
+        *reinterpret_cast<float4*>(op) = make_float4(o[0], o[1], o[2], o[3]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (jj + k < J) op[k] = o[k];
+      }
+    }
+  }
+}
+
 // D[i,j] = sum_r A[i,r] B[j,r].  A is stored (batch,I,R) when !A_MN and (batch,R,I) when A_MN; B
 // likewise (batch,J,R) or (batch,R,J).
 // Persistent: the grid has one CTA per SM and CTA c takes tiles c, c + gridDim.x, ...; the three
@@ -266,6 +363,7 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
       float sum[TEC];
 #pragma unroll
       for (int q = 0; q < TEC; ++q) sum[q] = 0.f;
+      if (EPI == TC_GRAD) prefetch_src<TEC>(ep.src, bt, i0 + quad * 32, j0 + cbase, I, J, lane);
       for (int chunk = 0; chunk < nchunks; ++chunk, ++gc) {
         const int buf = gc % TNB;
         if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.chunk_full[buf], (gc / TNB) & 1))) {
@@ -286,68 +384,8 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
           asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.chunk_empty[buf])) : "memory");
       }
       if (fail) break;
-      // Hand the sums over through shared memory so that global memory is touched along rows:
-      // lane = row when writing the warp's private 32x32 block, 8 lanes x 4 columns per row when
-      // reading it back; two passes cover the warp's 64 columns.
       bool bad = false;
-      const int hl = lane % 8, hr = lane / 8;
-      const bool vec = (J % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) &&
-                       (!ep.src || (reinterpret_cast<uintptr_t>(ep.src) & 15) == 0) &&
-                       (!ep.col_v || (reinterpret_cast<uintptr_t>(ep.col_v) & 15) == 0);
-#pragma unroll
-      for (int pass = 0; pass < TEC / 32; ++pass) {
-        __syncwarp();
-#pragma unroll
-        for (int q = 0; q < 32; ++q) blk[lane * 33 + q] = sum[pass * 32 + q];
-        __syncwarp();
-#pragma unroll 2
-        for (int itr = 0; itr < 8; ++itr) {
-          const int r = itr * 4 + hr;
-          const int ii = i0 + quad * 32 + r;
-          const int jj = j0 + cbase + pass * 32 + hl * 4;
-          if (ii >= I || jj >= J) continue;
-          float v[4], cv[4] = {0.f, 0.f, 0.f, 0.f}, x[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) v[k] = blk[r * 33 + hl * 4 + k];
-          const float rv = ep.row_v ? __ldg(ep.row_v + (int64_t)bt * I + ii) : 0.f;
-          const int64_t orow = ((int64_t)bt * I + ii) * J;
-          const bool full4 = vec && jj + 3 < J;
-          if (full4) {
-            if (ep.col_v) {
-              const float4 t4 = __ldg(reinterpret_cast<const float4*>(ep.col_v + (int64_t)bt * J + jj));
-              cv[0] = t4.x; cv[1] = t4.y; cv[2] = t4.z; cv[3] = t4.w;
-            }
-            if (EPI == TC_GRAD) {
-              const float4 t4 = __ldg(reinterpret_cast<const float4*>(ep.src + orow + jj));
-              x[0] = t4.x; x[1] = t4.y; x[2] = t4.z; x[3] = t4.w;
-            }
-          } else {
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              if (jj + k < J) {
-                if (ep.col_v) cv[k] = __ldg(ep.col_v + (int64_t)bt * J + jj + k);
-                if (EPI == TC_GRAD) x[k] = __ldg(ep.src + orow + jj + k);
-              }
-          }
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            if (EPI == TC_LOG) {
-              const float shift = rv + cv[k];
-              if (jj + k < J) bad |= !(v[k] >= kTiny) || !(v[k] <= 3.0e38f) || (shift < kFloor);
-              o[k] = __logf(v[k]) + shift;  // lg2.approx: absolute error below 2e-7 on the logarithm
-            } else {
-              o[k] = exp_sfu(x[k] - (rv + cv[k])) * v[k];
-            }
-          }
-          if (full4) {
-            *reinterpret_cast<float4*>(ep.out + orow + jj) = make_float4(o[0], o[1], o[2], o[3]);
-          } else {
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              if (jj + k < J) ep.out[orow + jj + k] = o[k];
-          }
-        }
-      }
+      store_sums<EPI, TEC>(sum, blk, ep, bt, i0 + quad * 32, j0 + cbase, I, J, lane, bad);
       if (EPI == TC_LOG) {
         // flags were zeroed before the launch; any epilogue warp that saw a bad sum raises the tile's
         if (__any_sync(0xffffffffu, bad) && lane == 0) atomicExch(ep.flags + tile, 1);
@@ -361,6 +399,210 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- CTA-pair variant ------------------------------------------------------------------------
+// The same product with tcgen05.mma.cta_group::2: a cluster of two CTAs (two SMs) owns a 256x256
+// result tile.  Each CTA loads 128 rows of A and 128 of the 256 columns of B; one thread of the
+// leader CTA (cluster rank 0) issues M=256, N=256, K=8 instructions that read A from each CTA's own
+// shared memory and the two halves of B from both, and leave rows 128*rank .. 128*rank+127 of the
+// tile in that CTA's TMEM.  Per multiply-add each SM reads half as many operand bytes from shared
+// memory as with 128x128 tiles, which is what bounds the single-CTA kernel.
+//   full[s]       (leader)   : the leader's producer arrives with the byte count of both CTAs' loads;
+//                              both CTAs' TMA loads report to it
+//   empty[s]      (each CTA) : tcgen05.commit from the leader, multicast to both CTAs
+//   chunk_full[q] (each CTA) : tcgen05.commit multicast; wakes that CTA's epilogue warps
+//   chunk_empty[q](leader)   : one arrival per epilogue warp of both CTAs
+// TMEM holds two accumulation buffers of 256 columns.  The cluster barrier at the start orders the
+// barrier initialisation before any remote arrival, the one at the end keeps both CTAs resident until
+// neither can signal the other any more.  No multicast loads; every wait is bounded.
+constexpr int PN = 256;           // columns of the pair tile = accumulator columns per buffer
+constexpr int PNB = 2;            // TMEM buffers
+constexpr int PEC = PN * 4 / TEW; // columns per epilogue warp (128)
+constexpr uint32_t kIdescPair = (1u << 4) | (2u << 7) | (2u << 10) | ((PN >> 3) << 17) | ((256 >> 4) << 24);
+
+__device__ __forceinline__ void umma_pair_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// one arrival on the barrier at this shared-memory offset in both CTAs of the pair, once every MMA
+// issued so far by this thread has finished
+__device__ __forceinline__ void umma_pair_commit(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"((uint16_t)3)
+      : "memory");
+}
+
+template <bool MN>
+__device__ __forceinline__ void tma_pair_tile(void* dst, const CUtensorMap* map, uint32_t bar, int k, int row,
+                                              int bt) {
+  if (MN)
+    tma_pair_load_4d(dst, map, bar, 0, k, row / 32, bt);
+  else
+    tma_pair_load_3d(dst, map, bar, k, row, bt);
+}
+
+template <int EPI, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TNT, 1)
+    tc_pair_gemm_kernel(const __grid_constant__ CUtensorMap ma_hi, const __grid_constant__ CUtensorMap ma_lo,
+                        const __grid_constant__ CUtensorMap mb_hi, const __grid_constant__ CUtensorMap mb_lo, TcEpi ep,
+                        int R, int I, int J, int tiles_i, int tiles_j, int64_t total_tiles) {
+  extern __shared__ unsigned char smem_raw[];
+  TcSmem& sm = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const uint32_t rank = cluster_ctarank();
+  const int64_t pair = blockIdx.x / 2, npairs = gridDim.x / 2;
+  const int nt = (R + TK - 1) / TK;
+  const int nchunks = (nt + TCH - 1) / TCH;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < TST; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+#pragma unroll
+    for (int q = 0; q < PNB; ++q) {
+      mbar_init(&sm.chunk_full[q], 1);
+      mbar_init(&sm.chunk_empty[q], 2 * TEW);  // the epilogue warps of both CTAs
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {  // the same warp of both CTAs allocates, and frees at the end
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  bool fail = false;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t full_addr[TST];
+#pragma unroll
+      for (int s = 0; s < TST; ++s) full_addr[s] = cluster_map(smem_u32(&sm.full[s]), 0);
+      uint32_t it = 0;
+      for (int64_t tile = pair; tile < total_tiles && !fail; tile += npairs) {
+        const int j0 = (int)(tile % tiles_j) * PN + (int)rank * TN;   // this CTA's half of the B columns
+        const int i0 = (int)((tile / tiles_j) % tiles_i) * (2 * TM) + (int)rank * TM;
+        const int bt = (int)(tile / ((int64_t)tiles_j * tiles_i));
+        for (int t = 0; t < nt; ++t, ++it) {
+          const int s = it % TST;
+          if (it >= TST && !mbar_wait_bounded_cluster(&sm.empty[s], ((it / TST) - 1) & 1)) {
+            fail = true;
+            break;
+          }
+          if (rank == 0) mbar_arrive_expect_tx(&sm.full[s], 8 * kTileBytes);
+          tma_pair_tile<A_MN>(sm.a_hi[s], &ma_hi, full_addr[s], t * TK, i0, bt);
+          tma_pair_tile<A_MN>(sm.a_lo[s], &ma_lo, full_addr[s], t * TK, i0, bt);
+          tma_pair_tile<B_MN>(sm.b_hi[s], &mb_hi, full_addr[s], t * TK, j0, bt);
+          tma_pair_tile<B_MN>(sm.b_lo[s], &mb_lo, full_addr[s], t * TK, j0, bt);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = kIdescPair | (A_MN ? 1u << 15 : 0u) | (B_MN ? 1u << 16 : 0u);
+      uint32_t it = 0, gc = 0;
+      for (int64_t tile = pair; tile < total_tiles && !fail; tile += npairs) {
+        for (int t = 0; t < nt; ++t, ++it) {
+          const int s = it % TST, buf = gc % PNB;
+          const bool chunk_start = (t % TCH) == 0;
+          if (chunk_start && gc >= PNB && !mbar_wait_bounded_cluster(&sm.chunk_empty[buf], ((gc / PNB) - 1) & 1)) {
+            fail = true;
+            break;
+          }
+          if (!mbar_wait_bounded_cluster(&sm.full[s], (it / TST) & 1)) {
+            fail = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t acc = tmem + (uint32_t)(buf * PN);
+#pragma unroll
+          for (int kk = 0; kk < TK / 8; ++kk) {
+            const int ko = kk * 8 * (int)sizeof(float);
+            const uint64_t ah = A_MN ? umma_desc_mn(sm.a_hi[s], kk) : umma_desc(sm.a_hi[s], ko);
+            const uint64_t al = A_MN ? umma_desc_mn(sm.a_lo[s], kk) : umma_desc(sm.a_lo[s], ko);
+            const uint64_t bh = B_MN ? umma_desc_mn(sm.b_hi[s], kk) : umma_desc(sm.b_hi[s], ko);
+            const uint64_t bl = B_MN ? umma_desc_mn(sm.b_lo[s], kk) : umma_desc(sm.b_lo[s], ko);
+            umma_pair_tf32(acc, al, bh, idesc, (!chunk_start || kk > 0) ? 1u : 0u);
+            umma_pair_tf32(acc, ah, bl, idesc, 1u);
+            umma_pair_tf32(acc, ah, bh, idesc, 1u);
+          }
+          umma_pair_commit(&sm.empty[s]);
+          if ((t % TCH) == TCH - 1 || t == nt - 1) {
+            umma_pair_commit(&sm.chunk_full[buf]);
+            ++gc;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp % 4;
+    const int cbase = ((warp - 2) / 4) * PEC;
+    float* blk = sm.epi[warp - 2];
+    uint32_t empty_addr[PNB];
+#pragma unroll
+    for (int q = 0; q < PNB; ++q) empty_addr[q] = cluster_map(smem_u32(&sm.chunk_empty[q]), 0);
+    uint32_t gc = 0;
+    for (int64_t tile = pair; tile < total_tiles && !fail; tile += npairs) {
+      const int j0 = (int)(tile % tiles_j) * PN;
+      const int i0 = (int)((tile / tiles_j) % tiles_i) * (2 * TM) + (int)rank * TM;
+      const int bt = (int)(tile / ((int64_t)tiles_j * tiles_i));
+      float sum[PEC];
+#pragma unroll
+      for (int q = 0; q < PEC; ++q) sum[q] = 0.f;
+      if (EPI == TC_GRAD) prefetch_src<PEC>(ep.src, bt, i0 + quad * 32, j0 + cbase, I, J, lane);
+      for (int chunk = 0; chunk < nchunks; ++chunk, ++gc) {
+        const int buf = gc % PNB;
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded_cluster(&sm.chunk_full[buf], (gc / PNB) & 1))) {
+          fail = true;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < PEC / 32; ++c) {
+          float v[32];
+          tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * PN + cbase + c * 32), v);
+#pragma unroll
+          for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(empty_addr[buf]);
+      }
+      if (fail) break;
+      bool bad = false;
+      store_sums<EPI, PEC>(sum, blk, ep, bt, i0 + quad * 32, j0 + cbase, I, J, lane, bad);
+      if (EPI == TC_LOG) {
+        // one flag per 128x128 block of the result: this warp's 128 columns lie in one of them
+        const int fi = i0 / TM, fj = (j0 + cbase) / TN;
+        if (__any_sync(0xffffffffu, bad) && lane == 0 && fi < (I + TM - 1) / TM && fj < (J + TN - 1) / TN)
+          atomicExch(ep.flags + ((int64_t)bt * ((I + TM - 1) / TM) + fi) * ((J + TN - 1) / TN) + fj, 1);
+      }
+    }
+  }
+  if (__any_sync(0xffffffffu, fail) && lane == 0) atomicExch(ep.error, 1);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -500,13 +742,31 @@ int launch_tc(const TcOperand& A, const TcOperand& Bo, const TcEpi& ep, int64_t 
       !make_map_sw128<B_MN>(&m2, Bo.hi, B, Bo.rows, Bo.cols, Bo.pitch) ||
       !make_map_sw128<B_MN>(&m3, Bo.lo, B, Bo.rows, Bo.cols, Bo.pitch))
     return GBMM_ERR_LAUNCH;
-  const int64_t ti = ceil_div(I, TM), tj = ceil_div(J, TN), tiles = B * ti * tj;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
     return GBMM_ERR_DEVICE;
-  const unsigned blocks = (unsigned)(tiles < sms ? tiles : sms);  // one persistent CTA per SM
   const size_t smem = sizeof(TcSmem) + 1024;
+  // 256x256 tiles on CTA pairs once the result is larger than one 128-row or 128-column tile
+  // (GENBMM_B200_TC_PAIR=0 keeps the single-CTA kernel)
+  static const bool pair_ok = [] {
+    const char* e = getenv("GENBMM_B200_TC_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  if (pair_ok && I > TM && J > TN && sms >= 2) {
+    const int64_t ti = ceil_div(I, 2 * TM), tj = ceil_div(J, PN), tiles = B * ti * tj;
+    const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+    if (cudaFuncSetAttribute(tc_pair_gemm_kernel<EPI, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return GBMM_ERR_LAUNCH;
+    const bool timed = profile_begin(slot, st);
+    tc_pair_gemm_kernel<EPI, A_MN, B_MN><<<(unsigned)(2 * pairs), TNT, smem, st>>>(m0, m1, m2, m3, ep, (int)R, (int)I,
+                                                                                  (int)J, (int)ti, (int)tj, tiles);
+    if (timed) profile_end(slot, st);
+    return launch_status();
+  }
+  const int64_t ti = ceil_div(I, TM), tj = ceil_div(J, TN), tiles = B * ti * tj;
+  const unsigned blocks = (unsigned)(tiles < sms ? tiles : sms);  // one persistent CTA per SM
   if (cudaFuncSetAttribute(tc_gemm_kernel<EPI, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem) != cudaSuccess)
     return GBMM_ERR_LAUNCH;
