@@ -290,52 +290,74 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_grad_a_kernel(const fl
   }
 }
 
-// grad_b: one warp per (batch, 32 consecutive n, slice of KT buckets); each lane owns a column
-// and walks m in ascending order into its private column of the [KT][32] histogram.  Slicing K
-// over CTAs multiplies the number of independent (latency-bound) walks.
+// grad_b: one CTA of 32 warps per (batch, 32 consecutive n).  Rows of idx / g are read 32 at a time
+// as coalesced 32x32 tiles and turned through shared memory, after which warp w owns column n0 + w:
+// its lanes hold 32 consecutive m, and lanes that target the same bucket add one after another in
+// lane (= m) order, so every bucket is the reference's ascending-m sum.  hist: [32 columns][KB + 1].
+constexpr int RB_WARPS = 32;
 template <bool MUL>
-__global__ void __launch_bounds__(32) route_grad_b_kernel(const float* __restrict__ a,
-                                                          const int* __restrict__ idx,
-                                                          const float* __restrict__ g,
-                                                          float* __restrict__ grad_b, int M, int K, int N,
-                                                          int tiles_n, int slices, int KT) {
-  extern __shared__ float hist[];
-  const int lane = threadIdx.x;
-  const int slice = blockIdx.x % slices;
-  const int tile = (blockIdx.x / slices) % tiles_n;
-  const int bt = blockIdx.x / (slices * tiles_n);
-  const int n = tile * 32 + lane;
-  const bool live = n < N;
+__global__ void __launch_bounds__(RB_WARPS * 32) route_grad_b_kernel(const float* __restrict__ a,
+                                                                     const int* __restrict__ idx,
+                                                                     const float* __restrict__ g,
+                                                                     float* __restrict__ grad_b, int M, int K, int N,
+                                                                     int tiles_n, int KB) {
+  extern __shared__ float hist_all[];
+  __shared__ int si[2][32][33];
+  __shared__ float sg[2][32][33];
+  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  const int n0 = (blockIdx.x % tiles_n) * 32;
+  const int bt = blockIdx.x / tiles_n;
   const int* ib = idx + (int64_t)bt * M * N;
   const float* gb = g + (int64_t)bt * M * N;
   const float* ab = a + (int64_t)bt * M * K;
   float* ob = grad_b + (int64_t)bt * K * N;
-  const int kbase = slice * KT, kend = min(kbase + KT, K);
-  if (kbase >= kend) return;
-  for (int k = 0; k < kend - kbase; ++k) hist[k * 32 + lane] = 0.f;
-  if (live) {
-    // 16 rows at a time: all their loads are issued before the (ordered) bucket updates
-    for (int m0 = 0; m0 < M; m0 += 16) {
-      int kk[16];
-      float gg[16];
-#pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        const bool ok = m0 + u < M;
-        kk[u] = ok ? __ldg(ib + (int64_t)(m0 + u) * N + n) : -1;
-        gg[u] = ok ? __ldg(gb + (int64_t)(m0 + u) * N + n) : 0.f;
+  float* hist = hist_all + warp * (KB + 1);
+  const int nl = n0 + lane;  // column this thread loads; warp = row offset within the tile
+  for (int kbase = 0; kbase < K; kbase += KB) {
+    const int kend = min(kbase + KB, K);
+    for (int k = lane; k < kend - kbase; k += 32) hist[k] = 0.f;
+    // tile 0 into buffer 0
+    int kn = -1;
+    float gn = 0.f;
+    auto fetch = [&](int m) {
+      kn = -1;
+      gn = 0.f;
+      if (m < M && nl < N) {
+        kn = __ldg(ib + (int64_t)m * N + nl);
+        gn = __ldg(gb + (int64_t)m * N + nl);
+        if (kn < kbase || kn >= kend) kn = -1;
+        if (MUL && kn >= 0) gn = __fmul_rn(__ldg(ab + (int64_t)m * K + kn), gn);
       }
-      if (MUL) {
-#pragma unroll
-        for (int u = 0; u < 16; ++u)
-          if (kk[u] >= kbase && kk[u] < kend)
-            gg[u] = __fmul_rn(__ldg(ab + (int64_t)(m0 + u) * K + kk[u]), gg[u]);
+    };
+    fetch(warp);
+    si[0][warp][lane] = kn;
+    sg[0][warp][lane] = gn;
+    __syncthreads();
+    for (int m0 = 0, cur = 0; m0 < M; m0 += 32, cur ^= 1) {
+      const bool more = m0 + 32 < M;
+      if (more) fetch(m0 + 32 + warp);
+      const int k = si[cur][lane][warp];  // lane = m offset, warp = column
+      const float gv = sg[cur][lane][warp];
+      const bool hit = k >= 0;
+      // lanes without a target get distinct negative keys so they group with nobody
+      const unsigned peers = __match_any_sync(0xffffffffu, hit ? k : -1 - lane);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
+      for (int r = 0; r <= last; ++r) {
+        if (hit && rank == r) hist[k - kbase] = __fadd_rn(hist[k - kbase], gv);
+        __syncwarp();
       }
-#pragma unroll
-      for (int u = 0; u < 16; ++u)
-        if (kk[u] >= kbase && kk[u] < kend)
-          hist[(kk[u] - kbase) * 32 + lane] = __fadd_rn(hist[(kk[u] - kbase) * 32 + lane], gg[u]);
+      if (more) {
+        si[cur ^ 1][warp][lane] = kn;
+        sg[cur ^ 1][warp][lane] = gn;
+      }
+      __syncthreads();
     }
-    for (int k = 0; k < kend - kbase; ++k) ob[(int64_t)(kbase + k) * N + n] = hist[k * 32 + lane];
+    // bucket k of all 32 columns is one 128-byte row of grad_b
+    if (nl < N)
+      for (int k = warp; k < kend - kbase; k += RB_WARPS)
+        ob[(int64_t)(kbase + k) * N + nl] = hist_all[lane * (KB + 1) + k];
+    __syncthreads();
   }
 }
 
@@ -423,17 +445,20 @@ extern "C" int gbmm_dense_backward_f32(int mode, const float* a, const float* b,
     if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
   }
   if (grad_b) {
-    // bucket slices of 128: B * ceil(N/32) * ceil(K/128) single-warp CTAs
-    const int KT = (int)(K < 128 ? K : 128);
-    const int64_t tiles_n = ceil_div(N, 32), slices = ceil_div(K, KT), blocks = B * tiles_n * slices;
+    // up to 1024 buckets per column (131 KB of shared memory) per pass
+    const int KB = (int)(K < 1024 ? K : 1024);
+    const int64_t tiles_n = ceil_div(N, 32), blocks = B * tiles_n;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
-    const size_t smem = sizeof(float) * 32 * KT;
-    if (mul)
-      route_grad_b_kernel<true><<<(unsigned)blocks, 32, smem, st>>>(a, idx, grad_out, grad_b, m, k, n,
-                                                                   (int)tiles_n, (int)slices, KT);
-    else
-      route_grad_b_kernel<false><<<(unsigned)blocks, 32, smem, st>>>(a, idx, grad_out, grad_b, m, k, n,
-                                                                    (int)tiles_n, (int)slices, KT);
+    const size_t smem = sizeof(float) * 32 * (KB + 1);
+    if (mul) {
+      cudaFuncSetAttribute(route_grad_b_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      route_grad_b_kernel<true><<<(unsigned)blocks, RB_WARPS * 32, smem, st>>>(a, idx, grad_out, grad_b, m, k, n,
+                                                                              (int)tiles_n, KB);
+    } else {
+      cudaFuncSetAttribute(route_grad_b_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      route_grad_b_kernel<false><<<(unsigned)blocks, RB_WARPS * 32, smem, st>>>(a, idx, grad_out, grad_b, m, k, n,
+                                                                               (int)tiles_n, KB);
+    }
   }
   return launch_status();
 }

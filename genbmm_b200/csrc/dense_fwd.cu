@@ -80,13 +80,15 @@ __device__ __forceinline__ void store_pairs_b(float* s, const TileLoader<BN, BK,
   }
 }
 
-template <bool MUL>
-__global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restrict__ a,
-                                                           const float* __restrict__ b,
-                                                           float* __restrict__ out,
-                                                           int* __restrict__ idx, int M, int K, int N,
-                                                           int tiles_m, int tiles_n,
-                                                           const float* __restrict__ b_t, int kp) {
+// PACK: the index of the winning reduction tile is kept in one byte (4 results per register), which
+// needs at most 255 tiles (K <= 4080) and lets two CTAs share an SM; otherwise one int per result.
+template <bool MUL, bool PACK>
+__global__ void __launch_bounds__(NT, PACK ? 2 : 1) dense_max_fwd_kernel(const float* __restrict__ a,
+                                                                         const float* __restrict__ b,
+                                                                         float* __restrict__ out,
+                                                                         int* __restrict__ idx, int M, int K, int N,
+                                                                         int tiles_m, int tiles_n,
+                                                                         const float* __restrict__ b_t, int kp) {
   __shared__ __align__(16) float sx[2][BK * LDX];
   __shared__ __align__(16) float sy[2][BK * LDY];
   const TileCoord tc(tiles_m, tiles_n);
@@ -96,16 +98,22 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
   const bool vec_a = aligned16(ab) && (K % 4 == 0);
   const bool vec_b = aligned16(bb) && (N % 4 == 0);
 
-  float best[8][4], cm[8][4];
-  int cid[8][4];
+  // Two sets of running maxima: a reduction tile folds its terms into one set starting from the
+  // other (the first 3-input max of the tile reads the old maximum), so "this tile raised the
+  // maximum" is one comparison of the two sets afterwards, and the roles swap for the next tile.
+  float X[8][4], Y[8][4];
+  int cid[PACK ? 1 : 8][4];
+  unsigned cidp[PACK ? 8 : 1];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < 8; ++i) {
+    if (PACK) cidp[i] = 0xffffffffu;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      best[i][j] = kFloor;
-      cm[i][j] = ninf_f();
-      cid[i][j] = -1;
+      X[i][j] = kFloor;
+      Y[i][j] = kFloor;
+      if (!PACK) cid[i][j] = -1;
     }
+  }
 
   TileLoader<BM, BK, NT, true> la;
   TileLoader<BN, BK, NT, false> lb;
@@ -117,16 +125,16 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
   store_pairs_b(sy[0], lb);
   __syncthreads();
 
-  for (int t = 0; t < nt; ++t) {
+  auto tile_step = [&](int t, float (&acc)[8][4], const float (&prev)[8][4]) {
     const int cur = t & 1;
     if (t + 1 < nt) {
       la.load(ab, K, 1, tc.m0, (t + 1) * BK, M, K, vec_a, nan_f());
       lb.load(bb, 1, N, tc.n0, (t + 1) * BK, N, K, vec_b, 0.f);
     }
 #pragma unroll
-    for (int kp = 0; kp < BK / 2; ++kp) {
-      const float* xs = sx[cur] + (kp * LDX + mt.ty * 4) * 2;
-      const float* ys = sy[cur] + (kp * LDY + mt.tx * 4) * 2;
+    for (int kp2 = 0; kp2 < BK / 2; ++kp2) {
+      const float* xs = sx[cur] + (kp2 * LDX + mt.ty * 4) * 2;
+      const float* ys = sy[cur] + (kp2 * LDY + mt.tx * 4) * 2;
       const ulonglong2 x01 = *reinterpret_cast<const ulonglong2*>(xs);
       const ulonglong2 x23 = *reinterpret_cast<const ulonglong2*>(xs + 4);
       const ulonglong2 x45 = *reinterpret_cast<const ulonglong2*>(xs + 128);
@@ -141,25 +149,47 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
         for (int j = 0; j < 4; ++j) {
           float v0, v1;
           unpack2(MUL ? mul2(xp[i], yp[j]) : add2(xp[i], yp[j]), v0, v1);
-          cm[i][j] = max3(cm[i][j], v0, v1);
+          acc[i][j] = max3(kp2 == 0 ? prev[i][j] : acc[i][j], v0, v1);
         }
     }
+    // strict `>`: an equal maximum in a later tile does not move the index
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 8; ++i) {
+      if (PACK) {
+        if (acc[i][0] > prev[i][0]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3214);
+        if (acc[i][1] > prev[i][1]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3240);
+        if (acc[i][2] > prev[i][2]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3410);
+        if (acc[i][3] > prev[i][3]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x4210);
+      } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (cm[i][j] > best[i][j]) {
-          best[i][j] = cm[i][j];
-          cid[i][j] = t;
-        }
-        cm[i][j] = ninf_f();
+        for (int j = 0; j < 4; ++j)
+          if (acc[i][j] > prev[i][j]) cid[i][j] = t;
       }
+    }
     if (t + 1 < nt) {
       store_pairs_a(sx[cur ^ 1], la);
       store_pairs_b(sy[cur ^ 1], lb);
     }
     __syncthreads();
+  };
+  int t = 0;
+  for (; t + 1 < nt; t += 2) {
+    tile_step(t, X, Y);
+    tile_step(t + 1, Y, X);
   }
+  if (t < nt) {
+    tile_step(t, X, Y);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) Y[i][j] = X[i][j];
+  }
+  // from here on Y holds the maxima
+  auto tile_of = [&](int i, int j) -> int {
+    if (!PACK) return cid[PACK ? 0 : i][j];
+    const unsigned c = (cidp[PACK ? i : 0] >> (8 * j)) & 0xffu;
+    return c == 0xffu ? -1 : (int)c;
+  };
 
   // Rescan the winning tile of every result for the first k that attains the maximum; the
   // stored value is that term itself, so a zero keeps the sign the reference would keep.
@@ -175,14 +205,15 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = tc.n0 + mt.col(j);
-      val[j] = best[i][j];
+      val[j] = Y[i][j];
       ind[j] = -1;
-      if (n < N && cid[i][j] >= 0) {
+      const int ct = tile_of(i, j);
+      if (n < N && ct >= 0) {
         // all loads of the tile are issued before any is used; the scan runs from the last k
         // down, so the lowest matching k is the assignment that sticks.  With a transposed copy
         // of b (b_t: (batch, N, kp), kp a multiple of 16) both 16-term segments are contiguous:
         // 8 128-bit loads and 4 sectors per result instead of 32 loads and 18 sectors.
-        const int k0 = cid[i][j] * BK;
+        const int k0 = ct * BK;
         const float* ap = ab + (int64_t)m * K + k0;
         float xv[BK], yv[BK], v[BK];
         if (vec_a && k0 + BK <= K) {
@@ -214,7 +245,7 @@ __global__ void __launch_bounds__(NT) dense_max_fwd_kernel(const float* __restri
         }
 #pragma unroll
         for (int kk = BK - 1; kk >= 0; --kk)
-          if (v[kk] == best[i][j]) {
+          if (v[kk] == Y[i][j]) {
             val[j] = v[kk];
             ind[j] = k0 + kk;
           }
@@ -523,12 +554,19 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
         transpose_b_kernel<<<(unsigned)tb, 256, 0, st>>>(b, b_t, k, n, kp, (int)tk, (int)tnn);
         if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
       }
-      if (mode == GBMM_MODE_MAX)
-        dense_max_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, static_cast<int*>(aux), m, k, n, tm, tn, b_t,
-                                                            kp);
-      else
-        dense_max_fwd_kernel<true><<<grid, block, 0, st>>>(a, b, out, static_cast<int*>(aux), m, k, n, tm, tn, b_t,
-                                                           kp);
+      const bool pack = ceil_div(K, BK) <= 255;
+      int* ix = static_cast<int*>(aux);
+      if (mode == GBMM_MODE_MAX) {
+        if (pack)
+          dense_max_fwd_kernel<false, true><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
+        else
+          dense_max_fwd_kernel<false, false><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
+      } else {
+        if (pack)
+          dense_max_fwd_kernel<true, true><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
+        else
+          dense_max_fwd_kernel<true, false><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
+      }
       break;
     }
     case GBMM_MODE_SAMPLE:
