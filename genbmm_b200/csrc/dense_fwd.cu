@@ -198,59 +198,136 @@ __global__ void __launch_bounds__(NT, PACK ? 2 : 1) dense_max_fwd_kernel(const f
   const bool vec_o = aligned16(ob) && aligned16(ib) && (N % 4 == 0);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int m = tc.m0 + mt.row(i);
-    if (m >= M) continue;
+    const int m = tc.m0 + mt.row(i);  // the same row for the four lanes of a quad
     float val[4];
     int ind[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int n = tc.n0 + mt.col(j);
       val[j] = Y[i][j];
       ind[j] = -1;
-      const int ct = tile_of(i, j);
-      if (n < N && ct >= 0) {
-        // all loads of the tile are issued before any is used; the scan runs from the last k
-        // down, so the lowest matching k is the assignment that sticks.  With a transposed copy
-        // of b (b_t: (batch, N, kp), kp a multiple of 16) both 16-term segments are contiguous:
-        // 8 128-bit loads and 4 sectors per result instead of 32 loads and 18 sectors.
-        const int k0 = ct * BK;
-        const float* ap = ab + (int64_t)m * K + k0;
-        float xv[BK], yv[BK], v[BK];
-        if (vec_a && k0 + BK <= K) {
+    }
+    if (b_t) {
+      // Quad-cooperative scan: the four lanes of a quad take the quad's results one owner at a
+      // time; each lane loads a quarter (16 bytes of a, 16 of b_t) of the winning tile's two
+      // 64-byte segments, so one warp-wide load touches 8 segments instead of 32, and the lowest
+      // matching k is found by a minimum over the quad.
+      const unsigned full = 0xffffffffu;
+      const int lane = threadIdx.x & 31, q = lane & 3;
+      const int tx_quad = mt.tx & ~3;
 #pragma unroll
-          for (int q = 0; q < BK / 4; ++q) {
-            const float4 t4 = __ldg(reinterpret_cast<const float4*>(ap) + q);
-            xv[4 * q] = t4.x; xv[4 * q + 1] = t4.y; xv[4 * q + 2] = t4.z; xv[4 * q + 3] = t4.w;
-          }
-        } else {
+      for (int o = 0; o < 4; ++o) {
+        const int src = (lane & ~3) | o;
+        float bo[4], av[4][4], bv[4][4];
+        int ct[4];
 #pragma unroll
-          for (int kk = 0; kk < BK; ++kk) xv[kk] = (k0 + kk < K) ? __ldg(ap + kk) : nan_f();
-        }
-        if (b_t) {
-          const float4* bp = reinterpret_cast<const float4*>(b_t + ((int64_t)tc.bt * N + n) * kp + k0);
-#pragma unroll
-          for (int q = 0; q < BK / 4; ++q) {
-            const float4 t4 = __ldg(bp + q);
-            yv[4 * q] = t4.x; yv[4 * q + 1] = t4.y; yv[4 * q + 2] = t4.z; yv[4 * q + 3] = t4.w;
-          }
-        } else {
-          const float* bp = bb + (int64_t)k0 * N + n;
-#pragma unroll
-          for (int kk = 0; kk < BK; ++kk) yv[kk] = (k0 + kk < K) ? __ldg(bp + (int64_t)kk * N) : 0.f;
+        for (int j = 0; j < 4; ++j) {
+          bo[j] = __shfl_sync(full, Y[i][j], src);
+          ct[j] = __shfl_sync(full, tile_of(i, j), src);
         }
 #pragma unroll
-        for (int kk = 0; kk < BK; ++kk) {
-          const float t = MUL ? __fmul_rn(xv[kk], yv[kk]) : __fadd_rn(xv[kk], yv[kk]);
-          v[kk] = (k0 + kk < K) ? t : nan_f();
+        for (int j = 0; j < 4; ++j) {
+          const int n = tc.n0 + (tx_quad + o) * 4 + j;
+          const int k0 = ct[j] * BK + 4 * q;
+          const bool ok = ct[j] >= 0 && m < M && n < N;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            av[j][kk] = nan_f();
+            bv[j][kk] = 0.f;
+          }
+          if (ok) {
+            const float* ap = ab + (int64_t)m * K + k0;
+            if (vec_a && k0 + 3 < K) {
+              const float4 t4 = __ldg(reinterpret_cast<const float4*>(ap));
+              av[j][0] = t4.x; av[j][1] = t4.y; av[j][2] = t4.z; av[j][3] = t4.w;
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                if (k0 + kk < K) av[j][kk] = __ldg(ap + kk);
+            }
+            const float4 u4 = __ldg(reinterpret_cast<const float4*>(b_t + ((int64_t)tc.bt * N + n) * kp + k0));
+            bv[j][0] = u4.x; bv[j][1] = u4.y; bv[j][2] = u4.z; bv[j][3] = u4.w;
+          }
         }
 #pragma unroll
-        for (int kk = BK - 1; kk >= 0; --kk)
-          if (v[kk] == Y[i][j]) {
-            val[j] = v[kk];
-            ind[j] = k0 + kk;
+        for (int j = 0; j < 4; ++j) {
+          int loc = 99;
+          float vm = 0.f;
+#pragma unroll
+          for (int kk = 3; kk >= 0; --kk) {
+            // a NaN (padding beyond K, or no winner) never equals the maximum
+            const float t = MUL ? __fmul_rn(av[j][kk], bv[j][kk]) : __fadd_rn(av[j][kk], bv[j][kk]);
+            if (t == bo[j]) {
+              loc = 4 * q + kk;
+              vm = t;
+            }
           }
+#pragma unroll
+          for (int d = 1; d <= 2; d <<= 1) {
+            const int oloc = __shfl_xor_sync(full, loc, d);
+            const float ovm = __shfl_xor_sync(full, vm, d);
+            if (oloc < loc) {
+              loc = oloc;
+              vm = ovm;
+            }
+          }
+          if (q == o && loc != 99) {
+            ind[j] = ct[j] * BK + loc;
+            val[j] = vm;
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = tc.n0 + mt.col(j);
+        val[j] = Y[i][j];
+        ind[j] = -1;
+        const int ct = tile_of(i, j);
+        if (m < M && n < N && ct >= 0) {
+          // all loads of the tile are issued before any is used; the scan runs from the last k
+          // down, so the lowest matching k is the assignment that sticks.  With a transposed copy
+          // of b (b_t: (batch, N, kp), kp a multiple of 16) both 16-term segments are contiguous:
+          // 8 128-bit loads and 4 sectors per result instead of 32 loads and 18 sectors.
+          const int k0 = ct * BK;
+          const float* ap = ab + (int64_t)m * K + k0;
+          float xv[BK], yv[BK], v[BK];
+          if (vec_a && k0 + BK <= K) {
+  #pragma unroll
+            for (int q = 0; q < BK / 4; ++q) {
+              const float4 t4 = __ldg(reinterpret_cast<const float4*>(ap) + q);
+              xv[4 * q] = t4.x; xv[4 * q + 1] = t4.y; xv[4 * q + 2] = t4.z; xv[4 * q + 3] = t4.w;
+            }
+          } else {
+  #pragma unroll
+            for (int kk = 0; kk < BK; ++kk) xv[kk] = (k0 + kk < K) ? __ldg(ap + kk) : nan_f();
+          }
+          if (b_t) {
+            const float4* bp = reinterpret_cast<const float4*>(b_t + ((int64_t)tc.bt * N + n) * kp + k0);
+  #pragma unroll
+            for (int q = 0; q < BK / 4; ++q) {
+              const float4 t4 = __ldg(bp + q);
+              yv[4 * q] = t4.x; yv[4 * q + 1] = t4.y; yv[4 * q + 2] = t4.z; yv[4 * q + 3] = t4.w;
+            }
+          } else {
+            const float* bp = bb + (int64_t)k0 * N + n;
+  #pragma unroll
+            for (int kk = 0; kk < BK; ++kk) yv[kk] = (k0 + kk < K) ? __ldg(bp + (int64_t)kk * N) : 0.f;
+          }
+  #pragma unroll
+          for (int kk = 0; kk < BK; ++kk) {
+            const float t = MUL ? __fmul_rn(xv[kk], yv[kk]) : __fadd_rn(xv[kk], yv[kk]);
+            v[kk] = (k0 + kk < K) ? t : nan_f();
+          }
+  #pragma unroll
+          for (int kk = BK - 1; kk >= 0; --kk)
+            if (v[kk] == Y[i][j]) {
+              val[j] = v[kk];
+              ind[j] = k0 + kk;
+            }
+        }
       }
     }
+    if (m >= M) continue;
     const int nb = tc.n0 + mt.col(0);
     if (vec_o && nb + 3 < N) {
       *reinterpret_cast<float4*>(ob + (int64_t)m * N + nb) = make_float4(val[0], val[1], val[2], val[3]);
