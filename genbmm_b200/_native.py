@@ -29,6 +29,11 @@ _SIGNATURES = {
     "gbmm_band_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L, _P, _L, _P], _I),
     "gbmm_band_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P, _L, _P], _I),
     "gbmm_band_backbackward_f32": ([_P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _P], _I),
+    "gbmm_band_tc_eligible": ([_I, _L, _I, _I, _I, _I], _I),
+    "gbmm_band_tc_workspace_bytes": ([_I, _L, _L, _I, _I, _I, _I], _L),
+    "gbmm_band_tc_workspace_init": ([_P, _L, _P], _I),
+    "gbmm_band_tc_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _L, _L, _P, _L, _P], _I),
+    "gbmm_band_tc_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P, _L, _P], _I),
     "gbmm_logbmm_workspace_bytes": ([_I, _L, _L, _L, _L], _L),
     "gbmm_logbmm_flag_count": ([_L, _L, _L], _L),
     "gbmm_logbmm_forward_f32": ([_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
@@ -212,6 +217,37 @@ def _check_band(a, a_lu, a_lb, b, b_lu, b_lb):
         raise RuntimeError("a and b must be on the same device")
 
 
+# Workspaces of the banded tensor-core path, kept between calls: their zero padding is written once, when
+# a workspace is created (the library never rewrites it).  One entry per device, replaced when the shape
+# changes; a backward-sized workspace also serves the forward.
+_band_tc_cache = {}
+
+
+def _band_tc_workspace(mode, backward, B, n, bands, device):
+    """The cached workspace for these dimensions on this device, or None when the tensor-core path is not
+    taken.  By default the log semiring goes through it and the ordinary (sum) semiring stays on the FP32
+    block kernels: 3xTF32 sums of signed terms are within 1e-6 of the sum of the terms' magnitudes, but
+    several times further off than an FP32 sum where terms cancel.  GENBMM_B200_BAND=tensor sends the sum
+    semiring through it as well, =block neither; GENBMM_B200_BANDLOG=exact keeps the direct kernels."""
+    choice = os.environ.get("GENBMM_B200_BAND", "auto")
+    if choice == "block" or os.environ.get("GENBMM_B200_BANDLOG") == "exact":
+        return None
+    if mode == BAND_MUL and choice != "tensor":
+        return None
+    lib = load()
+    key = (B, n) + tuple(bands)
+    dev = device.index if device.index is not None else torch.cuda.current_device()
+    hit = _band_tc_cache.get(dev)
+    need = lib.gbmm_band_tc_workspace_bytes(1 if backward else 0, B, n, *bands)
+    if hit is not None and hit[0] == key and hit[1].numel() >= need:
+        return hit[1]
+    _band_tc_cache.pop(dev, None)
+    ws = torch.empty((need,), dtype=torch.uint8, device=device)
+    _check(lib.gbmm_band_tc_workspace_init(_ptr(ws), ws.numel(), _stream(device)), "gbmm_band_tc_workspace_init")
+    _band_tc_cache[dev] = (key, ws)
+    return ws
+
+
 def _band_workspace(B, n, device):
     if os.environ.get("GENBMM_B200_BANDLOG", "auto") == "exact":
         return None
@@ -234,6 +270,15 @@ def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode, want_maxes=False):
         out = torch.empty((B, n, Wo), dtype=a.dtype, device=a.device)
         idx = torch.empty((B, n, Wo), dtype=torch.int32, device=a.device) if mode == BAND_MAX else None
         maxes = torch.empty_like(out) if (mode == BAND_LOG and want_maxes) else None
+        bands = (a_lu, a_lb, b_lu, b_lb)
+        tc_ws = None
+        if maxes is None and load().gbmm_band_tc_eligible(mode, n, *bands):
+            tc_ws = _band_tc_workspace(mode, False, B, n, bands, a.device)
+        if tc_ws is not None:
+            st = load().gbmm_band_tc_forward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), B, n,
+                                                 _ptr(tc_ws), tc_ws.numel(), _stream(a.device))
+            _check(st, "gbmm_band_tc_forward_f32")
+            return [out, idx, maxes]
         ws = _band_workspace(B, n, a.device) if mode == BAND_LOG else None
         st = load().gbmm_band_forward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), _ptr(idx),
                                           _ptr(maxes), B, n, _ptr(ws), 0 if ws is None else ws.numel(),
@@ -268,6 +313,16 @@ def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=Fa
             raise RuntimeError("part must have shape %s" % ((B, n, Wo),))
         grad_a = torch.empty_like(a)
         grad_b = torch.empty_like(b) if both else None
+        bands = (a_lu, a_lb, b_lu, b_lb)
+        tc_ws = None
+        if load().gbmm_band_tc_eligible(mode, n, *bands):
+            tc_ws = _band_tc_workspace(mode, True, B, n, bands, a.device)
+        if tc_ws is not None:
+            st = load().gbmm_band_tc_backward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(grad_output),
+                                                  _ptr(part), _ptr(grad_a), _ptr(grad_b), B, n, _ptr(tc_ws),
+                                                  tc_ws.numel(), _stream(a.device))
+            _check(st, "gbmm_band_tc_backward_f32")
+            return [grad_a, grad_b] if both else [grad_a]
         ws = _band_workspace(B, n, a.device) if mode == BAND_LOG else None
         st = load().gbmm_band_backward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(grad_output),
                                            _ptr(part), _ptr(grad_a), _ptr(grad_b), B, n, _ptr(ws),

@@ -643,6 +643,62 @@ extern "C" int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_
   return exact_backward(mode, a, b, grad_out, part, grad_a, grad_b, d, B, flags, st);
 }
 
+extern "C" int gbmm_band_tc_eligible(int mode, int64_t n, int a_lu, int a_ld, int b_lu, int b_ld) {
+  if (a_lu < 0 || a_ld < 0 || b_lu < 0 || b_ld < 0 || n < 0) return 0;
+  return band_tc_eligible(mode, BandDims{n, a_lu, a_ld, b_lu, b_ld}) ? 1 : 0;
+}
+
+extern "C" int64_t gbmm_band_tc_workspace_bytes(int backward, int64_t B, int64_t n, int a_lu, int a_ld, int b_lu,
+                                                int b_ld) {
+  if (B < 0 || n < 0 || a_lu < 0 || a_ld < 0 || b_lu < 0 || b_ld < 0) return -1;
+  return band_tc_workspace_bytes(backward, B, BandDims{n, a_lu, a_ld, b_lu, b_ld});
+}
+
+extern "C" int gbmm_band_tc_workspace_init(void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!workspace || workspace_bytes < 0) return GBMM_ERR_INVALID_ARG;
+  return cudaMemsetAsync(workspace, 0, (size_t)workspace_bytes, static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? GBMM_OK
+             : GBMM_ERR_LAUNCH;
+}
+
+extern "C" int gbmm_band_tc_forward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu,
+                                        int b_ld, float* out, int64_t B, int64_t n, void* workspace,
+                                        int64_t workspace_bytes, void* stream) {
+  const int st0 = check_band(mode, B, n, a_lu, a_ld, b_lu, b_ld);
+  if (st0 != GBMM_OK) return st0;
+  if (B == 0 || n == 0) return GBMM_OK;
+  if (!a || !b || !out || !workspace) return GBMM_ERR_INVALID_ARG;
+  const BandDims d{n, a_lu, a_ld, b_lu, b_ld};
+  if (!band_tc_eligible(mode, d)) return GBMM_ERR_UNSUPPORTED;
+  if (workspace_bytes < band_tc_workspace_bytes(0, B, d) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return GBMM_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int* flags = nullptr;
+  const int rc = band_tc_forward(mode, a, b, out, d, B, workspace, &flags, st);
+  if (rc != GBMM_OK || mode != GBMM_BAND_LOG) return rc;
+  return exact_forward(mode, a, b, out, nullptr, nullptr, d, B, flags, st);
+}
+
+extern "C" int gbmm_band_tc_backward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu,
+                                         int b_ld, const float* grad_out, const float* part, float* grad_a,
+                                         float* grad_b, int64_t B, int64_t n, void* workspace,
+                                         int64_t workspace_bytes, void* stream) {
+  const int st0 = check_band(mode, B, n, a_lu, a_ld, b_lu, b_ld);
+  if (st0 != GBMM_OK) return st0;
+  if (B == 0 || n == 0) return GBMM_OK;
+  if (!a || !b || !grad_out || !workspace) return GBMM_ERR_INVALID_ARG;
+  if (mode == GBMM_BAND_LOG && !part) return GBMM_ERR_INVALID_ARG;
+  const BandDims d{n, a_lu, a_ld, b_lu, b_ld};
+  if (!band_tc_eligible(mode, d)) return GBMM_ERR_UNSUPPORTED;
+  if (workspace_bytes < band_tc_workspace_bytes(1, B, d) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return GBMM_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int* flags = nullptr;
+  const int rc = band_tc_backward(mode, a, b, grad_out, part, grad_a, grad_b, d, B, workspace, &flags, st);
+  if (rc != GBMM_OK || mode != GBMM_BAND_LOG) return rc;
+  return exact_backward(mode, a, b, grad_out, part, grad_a, grad_b, d, B, flags, st);
+}
+
 extern "C" int gbmm_band_backbackward_f32(const float* a, int a_lu, int a_ld, const float* b, int b_lu, int b_ld,
                                           const float* grad_out, const float* part, const float* h_a,
                                           const float* h_b, float* d_a, float* d_b, float* d_grad_out, int64_t B,

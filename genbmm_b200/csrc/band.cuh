@@ -23,4 +23,14 @@ int band_fast_forward(int mode, const float* a, const float* b, float* out, int*
 int band_fast_backward(int mode, const float* a, const float* b, const float* g, const float* part, float* grad_a,
                        float* grad_b, const BandDims& d, int64_t B, void* ws, int** flags_out, cudaStream_t st);
 
+// Tensor-core path (band_tc.cu) for the sum and log semirings with bands at least 32 wide.  `ws` holds at
+// least band_tc_workspace_bytes and was zero-filled once before its first use with these dimensions (the
+// zero padding between the rows of the skewed operand copies is never rewritten).
+bool band_tc_eligible(int mode, const BandDims& d);
+int64_t band_tc_workspace_bytes(int backward, int64_t B, const BandDims& d);
+int band_tc_forward(int mode, const float* a, const float* b, float* out, const BandDims& d, int64_t B, void* ws,
+                    int** flags_out, cudaStream_t st);
+int band_tc_backward(int mode, const float* a, const float* b, const float* g, const float* part, float* grad_a,
+                     float* grad_b, const BandDims& d, int64_t B, void* ws, int** flags_out, cudaStream_t st);
+
 }  // namespace gbmm

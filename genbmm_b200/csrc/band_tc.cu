@@ -1,0 +1,572 @@
+// Banded sum / log products on the tensor cores (3xTF32 on tcgen05), for bands at least 32 wide.
+//
+// In dense terms a band tensor data:(n,W) with `lu` is a matrix X[r,c] = data[r][c-r+lu], and the
+// forward product and both gradients are products between band matrices (see band_block.cu):
+//   forward  out[i,o] = sum_p Xa[i,p] Xb[o,p]
+//   grad_a   dXa[i,p] = sum_o G[i,o]  Xb[o,p]
+//   grad_b   dXb[o,p] = sum_i G[i,o]  Xa[i,p]
+// A dense tile of X is a *strided view* of band storage: X[r,c] sits r*(W-1) + c + lu elements
+// after the start, i.e. rows W-1 elements apart and columns contiguous — except that cells outside
+// the band alias the neighbouring rows.  So every operand is first copied (exponentiated for the
+// log semiring, split into tf32 hi + lo) into a "skewed" layout with zero padding after each row:
+// pitch = off + W + 192 (pitch % 4 == 1, off zero columns in front so that lu + off is a multiple
+// of 32).  With 192 zeros between consecutive rows' bands, any 128 x 32 box of the view (pitch - 1
+// elements between rows) that touches the band reads the band cells where they are and zeros
+// elsewhere, and TMA can fetch it: as a K-major tile (reduction index contiguous) through a 3-D map,
+// or as an MN-major tile (result index contiguous) through a 4-D map, exactly the two operand forms
+// of the dense kernel (dense_tc.cu).  The padding is written once (gbmm_band_tc_workspace_init) and
+// never again: the per-call copy only rewrites the W band columns.
+//
+// band_tc_kernel is the persistent single-CTA tcgen05 kernel of dense_tc.cu with three changes:
+// tiles are enumerated over the 128x128 blocks that meet the result band, each with its own
+// reduction range (where both operand bands are populated); the two operands take separate TMA
+// coordinates; and the epilogue scatters a tile's band cells into band storage (each tile row is a
+// contiguous run of a band row).  Log semiring: factorised like the dense path (row maxima, guard
+// flags per 64-row block, flagged blocks redone by the exact kernels of band.cu).
+#include "band.cuh"
+#include "tc.cuh"
+
+namespace gbmm {
+namespace {
+
+constexpr int SKEW_PAD = 192;  // >= 127 (tile rows) + 2 * 31 (reduction range rounded to boxes of 32)
+
+struct Skew {
+  int off, pitch, kofs;   // zero columns in front, floats per row, lu + off
+  int64_t bstride;        // floats per batch element (a multiple of 4)
+};
+Skew make_skew(int lu, int W, int64_t n) {
+  Skew s;
+  s.off = (32 - lu % 32) % 32;
+  s.pitch = s.off + W + SKEW_PAD;
+  s.pitch += (1 - s.pitch % 4 + 4) % 4;
+  s.kofs = lu + s.off;
+  s.bstride = (n * s.pitch + 3) & ~int64_t(3);
+  return s;
+}
+int64_t skew_floats(const Skew& s, int64_t B) { return pad64(B * s.bstride + 64); }
+
+// One warp per band row.  KIND 0: v = x.  KIND 1: v = exp(x - m), m = the row's maximum over its in-matrix
+// cells (0 when there is none), also written to ra_out[row].  KIND 2: v = g * exp(ra[row] + rb[col] - x), x
+// the saved output, 0 in flagged 64-row blocks.  Cells outside the matrix become 0.
+template <int KIND>
+__global__ void __launch_bounds__(256) band_skew_kernel(const float* __restrict__ x, const float* __restrict__ g,
+                                                        const float* __restrict__ ra, const float* __restrict__ rb,
+                                                        const int* __restrict__ flags, float* __restrict__ ra_out,
+                                                        float* __restrict__ hi, float* __restrict__ lo, int64_t rows,
+                                                        int n, int lu, int W, int off, int pitch, int64_t bstride) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const int i = (int)(row % n);
+  const int64_t bt = row / n;
+  const float* xr = x + row * W;
+  // in-matrix cells of this row: j in [jlo, jhi)
+  const int jlo = max(0, lu - i), jhi = min(W, n - i + lu);
+  float shift = 0.f;
+  bool dead = false;
+  if (KIND == 1) {
+    float m = __int_as_float(0xff800000);
+    for (int j = jlo + lane; j < jhi; j += 32) m = fmaxf(m, __ldg(xr + j));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    shift = (m == __int_as_float(0xff800000)) ? 0.f : m;
+    if (lane == 0) ra_out[row] = shift;
+  }
+  if (KIND == 2) {
+    shift = __ldg(ra + row);
+    dead = __ldg(flags + bt * ((n + 63) / 64) + i / 64) != 0;
+  }
+  float* hr = hi + bt * bstride + (int64_t)i * pitch + off;
+  float* lr = lo + bt * bstride + (int64_t)i * pitch + off;
+  const float* gr = KIND == 2 ? g + row * W : nullptr;
+  const float* rbb = KIND == 2 ? rb + bt * n + (i - lu) : nullptr;  // rbb[j] = rb of column i + j - lu
+  for (int j = lane; j < W; j += 32) {
+    float v = 0.f;
+    if (j >= jlo && j < jhi) {
+      const float xv = __ldg(xr + j);
+      if (KIND == 0) v = xv;
+      if (KIND == 1) v = exp_sfu(xv - shift);
+      if (KIND == 2) v = dead ? 0.f : __ldg(gr + j) * exp_sfu((shift + __ldg(rbb + j)) - xv);
+    }
+    const float h = tf32_round(v);
+    hr[j] = h;
+    lr[j] = v - h;
+  }
+}
+
+template <int KIND>
+int launch_skew(const float* x, const float* g, const float* ra, const float* rb, const int* flags, float* ra_out,
+                float* hi, float* lo, int64_t B, int64_t n, int lu, int W, const Skew& s, cudaStream_t st) {
+  const int64_t rows = B * n, blocks = ceil_div(rows, 8);
+  if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  band_skew_kernel<KIND><<<(unsigned)blocks, 256, 0, st>>>(x, g, ra, rb, flags, ra_out, hi, lo, rows, (int)n, lu, W,
+                                                          s.off, s.pitch, s.bstride);
+  return launch_status();
+}
+
+// Tensor maps over a skewed copy.  !MN: contiguous index = reduction (coordinate s + kofs), rows = result
+// index.  MN: contiguous index = result (32-blocks (r + kofs) / 32), rows = reduction.
+template <bool MN>
+bool make_skew_map(CUtensorMap* map, const float* base, int64_t B, int64_t n, const Skew& s) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  if (reinterpret_cast<uintptr_t>(base) & 15) return false;
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const cuuint64_t rstride = (cuuint64_t)(s.pitch - 1) * sizeof(float), bstride = (cuuint64_t)s.bstride * sizeof(float);
+  if (MN) {
+    const cuuint64_t dims[4] = {32, (cuuint64_t)n, (cuuint64_t)(n + s.kofs + 128 + 31) / 32, (cuuint64_t)B};
+    const cuuint64_t strides[3] = {rstride, 32 * sizeof(float), bstride};
+    const cuuint32_t box[4] = {32, TK, TM / 32, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
+  const cuuint64_t dims[3] = {(cuuint64_t)(n + s.kofs + 32), (cuuint64_t)n, (cuuint64_t)B};
+  const cuuint64_t strides[2] = {rstride, bstride};
+  const cuuint32_t box[3] = {TK, TM, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+enum { E_SUM = 0, E_LOG = 1 };
+
+struct BandTcArgs {
+  int n, lu_out, w_out;      // result band
+  int xl, xu, yl, yu;        // operand supports: s - r in [-xl, xu], s - c in [-yl, yu]
+  int kofs_x, kofs_y;        // lu + off of the two skewed operands
+  int nrb, ncb;              // 128-row blocks, candidate column tiles per row block
+  int64_t total;             // batch * nrb * ncb
+  float* out;                // (batch, n, w_out)
+  const float* ra;           // E_LOG: row maxima of a
+  const float* rb;           // E_LOG: row maxima of b
+  int* flags;                // E_LOG: (batch, ceil(n / 64))
+  int* error;
+};
+
+// Tile `tile` -> batch element, first row / column, first reduction index (a multiple of 32) and number of
+// 32-step stages.  false: the tile lies beyond the result band and owns no cell.  nt == 0: the tile owns band
+// cells but no term reaches them (outside the matrix, or no common support): zeros are written.
+__device__ __forceinline__ bool band_tile(const BandTcArgs& g, int64_t tile, int& bt, int& r0, int& c0, int& s0,
+                                          int& nt) {
+  const int cbi = (int)(tile % g.ncb);
+  const int rbk = (int)((tile / g.ncb) % g.nrb);
+  bt = (int)(tile / ((int64_t)g.ncb * g.nrb));
+  r0 = rbk * TM;
+  const int lo = r0 - g.lu_out;
+  const int cfirst = lo >= 0 ? lo / TN : -((-lo + TN - 1) / TN);
+  c0 = (cfirst + cbi) * TN;
+  if (c0 > r0 + TM - 1 + (g.w_out - 1 - g.lu_out)) return false;
+  const int s_lo = max(max(r0 - g.xl, c0 - g.yl), 0);
+  int s_hi = min(min(r0 + TM - 1 + g.xu, c0 + TN - 1 + g.yu), g.n - 1);
+  if (c0 >= g.n || c0 + TN - 1 < 0) s_hi = s_lo - 1;
+  s0 = s_lo & ~31;
+  nt = s_hi >= s_lo ? (s_hi - s0) / TK + 1 : 0;
+  return true;
+}
+
+// One warp's 32 rows x TEC columns of a tile: band cells (col - row + lu_out in [0, w_out)) go to band
+// storage; lanes run along columns, so a tile row is written as one contiguous run.  The epilogue reads
+// nothing large from global memory: while the products stream the padded operands, every load of an SM
+// queues behind its TMA traffic for microseconds (the log gradients' factor exp(a - ra) is therefore
+// applied by a separate pass, band_scale_kernel).
+template <int EPI>
+__device__ __forceinline__ void store_band(const float (&sum)[TEC], float* blk, const BandTcArgs& g, int bt, int row0,
+                                           int col0, int lane, bool& bad) {
+  float* ob = g.out + (int64_t)bt * g.n * g.w_out;
+  // shift of row row0 + lane, handed round by shuffles
+  float rshift = 0.f;
+  if (EPI == E_LOG && row0 + lane < g.n) rshift = __ldg(g.ra + (int64_t)bt * g.n + row0 + lane);
+  const int rows = min(32, g.n - row0);
+#pragma unroll
+  for (int pass = 0; pass < TEC / 32; ++pass) {
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < 32; ++q) blk[lane * 33 + q] = sum[pass * 32 + q];
+    __syncwarp();
+    const int c = col0 + pass * 32 + lane;
+    const bool inside = c >= 0 && c < g.n;
+    float cshift = 0.f;
+    if (EPI == E_LOG && inside) cshift = __ldg(g.rb + (int64_t)bt * g.n + c);
+    // cell of (row0 + rr, c) = c - row0 - rr + lu_out: valid rr in [rr_lo, rr_hi)
+    const int top = c - row0 + g.lu_out;  // cell at rr = 0
+    const int rr_lo = max(0, top - (g.w_out - 1)), rr_hi = min(rows, top + 1);
+#pragma unroll
+    for (int rr = 0; rr < 32; ++rr) {
+      const float rs = EPI == E_LOG ? __shfl_sync(0xffffffffu, rshift, rr) : 0.f;
+      if (rr < rr_lo || rr >= rr_hi) continue;
+      const float v = blk[rr * 33 + lane];
+      float o = 0.f;
+      if (inside) {
+        if (EPI == E_SUM) o = v;
+        if (EPI == E_LOG) {
+          const float sh = rs + cshift;
+          bad |= !(v >= kTiny) || !(v <= 3.0e38f) || (sh < kFloor);
+          o = __logf(v) + sh;
+        }
+      }
+      ob[(int64_t)(row0 + rr) * g.w_out + (top - rr)] = o;  // cells outside the matrix stay zero
+    }
+  }
+}
+
+// grad[row][j] *= exp(src[row][j] - shift[row]) over the in-matrix cells of a band tensor (the others hold 0).
+__global__ void __launch_bounds__(256) band_scale_kernel(float* __restrict__ grad, const float* __restrict__ src,
+                                                         const float* __restrict__ shift, int64_t rows, int n, int lu,
+                                                         int W) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const int i = (int)(row % n);
+  const int jlo = max(0, lu - i), jhi = min(W, n - i + lu);
+  const float sh = __ldg(shift + row);
+  for (int j = jlo + lane; j < jhi; j += 32)
+    grad[row * W + j] *= exp_sfu(__ldg(src + row * W + j) - sh);
+}
+
+template <int EPI, bool X_MN, bool Y_MN>
+__global__ void __launch_bounds__(TNT, 1) band_tc_kernel(const __grid_constant__ CUtensorMap mx_hi,
+                                                         const __grid_constant__ CUtensorMap mx_lo,
+                                                         const __grid_constant__ CUtensorMap my_hi,
+                                                         const __grid_constant__ CUtensorMap my_lo, BandTcArgs g) {
+  extern __shared__ unsigned char smem_raw[];
+  TcSmem& sm = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < TST; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+#pragma unroll
+    for (int q = 0; q < TNB; ++q) {
+      mbar_init(&sm.chunk_full[q], 1);
+      mbar_init(&sm.chunk_empty[q], TEW);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  bool fail = false;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int64_t tile = blockIdx.x; tile < g.total && !fail; tile += gridDim.x) {
+        int bt, r0, c0, s0, nt;
+        if (!band_tile(g, tile, bt, r0, c0, s0, nt)) continue;
+        for (int t = 0; t < nt; ++t, ++it) {
+          const int s = it % TST, sr = s0 + t * TK;
+          if (it >= TST && !mbar_wait_bounded(&sm.empty[s], ((it / TST) - 1) & 1)) {
+            fail = true;
+            break;
+          }
+          mbar_arrive_expect_tx(&sm.full[s], 4 * kTileBytes);
+          if (X_MN) {
+            tma_load_4d(sm.a_hi[s], &mx_hi, &sm.full[s], 0, sr, (r0 + g.kofs_x) / 32, bt);
+            tma_load_4d(sm.a_lo[s], &mx_lo, &sm.full[s], 0, sr, (r0 + g.kofs_x) / 32, bt);
+          } else {
+            tma_load_3d(sm.a_hi[s], &mx_hi, &sm.full[s], sr + g.kofs_x, r0, bt);
+            tma_load_3d(sm.a_lo[s], &mx_lo, &sm.full[s], sr + g.kofs_x, r0, bt);
+          }
+          if (Y_MN) {
+            tma_load_4d(sm.b_hi[s], &my_hi, &sm.full[s], 0, sr, (c0 + g.kofs_y) / 32, bt);
+            tma_load_4d(sm.b_lo[s], &my_lo, &sm.full[s], 0, sr, (c0 + g.kofs_y) / 32, bt);
+          } else {
+            tma_load_3d(sm.b_hi[s], &my_hi, &sm.full[s], sr + g.kofs_y, c0, bt);
+            tma_load_3d(sm.b_lo[s], &my_lo, &sm.full[s], sr + g.kofs_y, c0, bt);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = kIdesc | (X_MN ? 1u << 15 : 0u) | (Y_MN ? 1u << 16 : 0u);
+      uint32_t it = 0, gc = 0;
+      for (int64_t tile = blockIdx.x; tile < g.total && !fail; tile += gridDim.x) {
+        int bt, r0, c0, s0, nt;
+        if (!band_tile(g, tile, bt, r0, c0, s0, nt)) continue;
+        for (int t = 0; t < nt; ++t, ++it) {
+          const int s = it % TST, buf = gc % TNB;
+          const bool chunk_start = (t % TCH) == 0;
+          if (chunk_start && gc >= TNB && !mbar_wait_bounded(&sm.chunk_empty[buf], ((gc / TNB) - 1) & 1)) {
+            fail = true;
+            break;
+          }
+          if (!mbar_wait_bounded(&sm.full[s], (it / TST) & 1)) {
+            fail = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t acc = tmem + (uint32_t)(buf * TN);
+#pragma unroll
+          for (int kk = 0; kk < TK / 8; ++kk) {
+            const int ko = kk * 8 * (int)sizeof(float);
+            const uint64_t ah = X_MN ? umma_desc_mn(sm.a_hi[s], kk) : umma_desc(sm.a_hi[s], ko);
+            const uint64_t al = X_MN ? umma_desc_mn(sm.a_lo[s], kk) : umma_desc(sm.a_lo[s], ko);
+            const uint64_t bh = Y_MN ? umma_desc_mn(sm.b_hi[s], kk) : umma_desc(sm.b_hi[s], ko);
+            const uint64_t bl = Y_MN ? umma_desc_mn(sm.b_lo[s], kk) : umma_desc(sm.b_lo[s], ko);
+            umma_tf32(acc, al, bh, idesc, (!chunk_start || kk > 0) ? 1u : 0u);
+            umma_tf32(acc, ah, bl, idesc, 1u);
+            umma_tf32(acc, ah, bh, idesc, 1u);
+          }
+          umma_commit(&sm.empty[s]);
+          if ((t % TCH) == TCH - 1 || t == nt - 1) {
+            umma_commit(&sm.chunk_full[buf]);
+            ++gc;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp % 4;
+    const int cbase = ((warp - 2) / 4) * TEC;
+    float* blk = sm.epi[warp - 2];
+    uint32_t gc = 0;
+    for (int64_t tile = blockIdx.x; tile < g.total && !fail; tile += gridDim.x) {
+      int bt, r0, c0, s0, nt;
+      if (!band_tile(g, tile, bt, r0, c0, s0, nt)) continue;
+      const int nchunks = (nt + TCH - 1) / TCH;
+      float sum[TEC];
+#pragma unroll
+      for (int q = 0; q < TEC; ++q) sum[q] = 0.f;
+      for (int chunk = 0; chunk < nchunks; ++chunk, ++gc) {
+        const int buf = gc % TNB;
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.chunk_full[buf], (gc / TNB) & 1))) {
+          fail = true;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < TEC / 32; ++c) {
+          float v[32];
+          tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * TN + cbase + c * 32), v);
+#pragma unroll
+          for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.chunk_empty[buf])) : "memory");
+      }
+      if (fail) break;
+      bool bad = false;
+      store_band<EPI>(sum, blk, g, bt, r0 + quad * 32, c0 + cbase, lane, bad);
+      if (EPI == E_LOG) {
+        const int row0 = r0 + quad * 32;
+        if (__any_sync(0xffffffffu, bad) && lane == 0 && row0 < g.n)
+          atomicExch(g.flags + (int64_t)bt * ((g.n + 63) / 64) + row0 / 64, 1);
+      }
+    }
+  }
+  if (__any_sync(0xffffffffu, fail) && lane == 0) atomicExch(g.error, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+struct SkewOperand {
+  const float* hi;
+  const float* lo;
+  Skew s;
+};
+
+template <int EPI, bool X_MN, bool Y_MN>
+int launch_band_tc(const SkewOperand& X, const SkewOperand& Y, BandTcArgs args, int64_t B, cudaStream_t st) {
+  CUtensorMap m0, m1, m2, m3;
+  if (!make_skew_map<X_MN>(&m0, X.hi, B, args.n, X.s) || !make_skew_map<X_MN>(&m1, X.lo, B, args.n, X.s) ||
+      !make_skew_map<Y_MN>(&m2, Y.hi, B, args.n, Y.s) || !make_skew_map<Y_MN>(&m3, Y.lo, B, args.n, Y.s))
+    return GBMM_ERR_LAUNCH;
+  args.kofs_x = X.s.kofs;
+  args.kofs_y = Y.s.kofs;
+  args.nrb = (int)ceil_div((int64_t)args.n, TM);
+  args.ncb = (args.w_out + 2 * TN - 2) / TN + 1;
+  args.total = B * args.nrb * args.ncb;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    return GBMM_ERR_DEVICE;
+  const unsigned blocks = (unsigned)(args.total < sms ? args.total : sms);
+  const size_t smem = sizeof(TcSmem) + 1024;
+  if (cudaFuncSetAttribute(band_tc_kernel<EPI, X_MN, Y_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return GBMM_ERR_LAUNCH;
+  band_tc_kernel<EPI, X_MN, Y_MN><<<blocks, TNT, smem, st>>>(m0, m1, m2, m3, args);
+  return launch_status();
+}
+
+struct BandWs {
+  int* error;
+  float *ra, *rb;
+  int* flags;
+  SkewOperand A, Bm, G;
+};
+
+BandWs carve_ws(void* ws, int64_t B, const BandDims& d, bool backward) {
+  BandWs w;
+  float* p = static_cast<float*>(ws);
+  auto take = [&](int64_t floats) {
+    float* q = p;
+    p += pad64(floats);
+    return q;
+  };
+  w.error = reinterpret_cast<int*>(take(64));
+  w.ra = take(B * d.n);
+  w.rb = take(B * d.n);
+  w.flags = reinterpret_cast<int*>(take(B * ceil_div(d.n, 64)));
+  w.A.s = make_skew(d.a_lu, d.Wa(), d.n);
+  w.Bm.s = make_skew(d.b_lu, d.Wb(), d.n);
+  w.G.s = make_skew(d.r_lu(), d.Wo(), d.n);
+  w.A.hi = take(skew_floats(w.A.s, B));
+  w.A.lo = take(skew_floats(w.A.s, B));
+  w.Bm.hi = take(skew_floats(w.Bm.s, B));
+  w.Bm.lo = take(skew_floats(w.Bm.s, B));
+  w.G.hi = w.G.lo = nullptr;
+  if (backward) {
+    w.G.hi = take(skew_floats(w.G.s, B));
+    w.G.lo = take(skew_floats(w.G.s, B));
+  }
+  return w;
+}
+
+}  // namespace
+
+// declared in band.cuh
+bool band_tc_eligible(int mode, const BandDims& d) {
+  if (mode != GBMM_BAND_MUL && mode != GBMM_BAND_LOG) return false;
+  return d.Wa() >= 32 && d.Wb() >= 32 && d.n >= 128 && d.n < (1LL << 30);
+}
+
+int64_t band_tc_workspace_bytes(int backward, int64_t B, const BandDims& d) {
+  const Skew sa = make_skew(d.a_lu, d.Wa(), d.n), sb = make_skew(d.b_lu, d.Wb(), d.n),
+             sg = make_skew(d.r_lu(), d.Wo(), d.n);
+  int64_t floats = 64 + 2 * pad64(B * d.n) + pad64(B * ceil_div(d.n, 64)) + 2 * skew_floats(sa, B) +
+                   2 * skew_floats(sb, B);
+  if (backward) floats += 2 * skew_floats(sg, B);
+  return floats * (int64_t)sizeof(float);
+}
+
+// the guard flags of a saved output come from band_block.cu
+int band_saved_flags(const float* out, const float* ra, const float* rb, int* flags, int64_t B, int64_t n, int r_lu,
+                     int Wo, cudaStream_t st);
+
+int band_tc_forward(int mode, const float* a, const float* b, float* out, const BandDims& d, int64_t B, void* ws,
+                    int** flags_out, cudaStream_t st) {
+  const BandWs w = carve_ws(ws, B, d, false);
+  const bool lg = mode == GBMM_BAND_LOG;
+  if (cudaMemsetAsync(w.error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
+  int rc = GBMM_OK;
+  if (lg) {
+    if (cudaMemsetAsync(w.flags, 0, sizeof(int) * B * ceil_div(d.n, 64), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
+    // the row maxima come out of the same pass that exponentiates and splits the operands
+    rc = launch_skew<1>(a, nullptr, nullptr, nullptr, nullptr, w.ra, const_cast<float*>(w.A.hi),
+                        const_cast<float*>(w.A.lo), B, d.n, d.a_lu, d.Wa(), w.A.s, st);
+    if (rc != GBMM_OK) return rc;
+    rc = launch_skew<1>(b, nullptr, nullptr, nullptr, nullptr, w.rb, const_cast<float*>(w.Bm.hi),
+                        const_cast<float*>(w.Bm.lo), B, d.n, d.b_lu, d.Wb(), w.Bm.s, st);
+  } else {
+    rc = launch_skew<0>(a, nullptr, nullptr, nullptr, nullptr, nullptr, const_cast<float*>(w.A.hi),
+                        const_cast<float*>(w.A.lo), B, d.n, d.a_lu, d.Wa(), w.A.s, st);
+    if (rc != GBMM_OK) return rc;
+    rc = launch_skew<0>(b, nullptr, nullptr, nullptr, nullptr, nullptr, const_cast<float*>(w.Bm.hi),
+                        const_cast<float*>(w.Bm.lo), B, d.n, d.b_lu, d.Wb(), w.Bm.s, st);
+  }
+  if (rc != GBMM_OK) return rc;
+  // out[i,o] = sum_p Xa[i,p] Xb[o,p]: both operands K-major
+  BandTcArgs args{};
+  args.n = (int)d.n;
+  args.lu_out = d.r_lu();
+  args.w_out = d.Wo();
+  args.xl = d.a_lu; args.xu = d.a_ld; args.yl = d.b_lu; args.yu = d.b_ld;
+  args.out = out;
+  args.ra = w.ra;
+  args.rb = w.rb;
+  args.flags = w.flags;
+  args.error = w.error;
+  *flags_out = lg ? w.flags : nullptr;
+  return lg ? launch_band_tc<E_LOG, false, false>(w.A, w.Bm, args, B, st)
+            : launch_band_tc<E_SUM, false, false>(w.A, w.Bm, args, B, st);
+}
+
+int band_tc_backward(int mode, const float* a, const float* b, const float* g, const float* part, float* grad_a,
+                     float* grad_b, const BandDims& d, int64_t B, void* ws, int** flags_out, cudaStream_t st) {
+  const BandWs w = carve_ws(ws, B, d, true);
+  const bool lg = mode == GBMM_BAND_LOG;
+  if (cudaMemsetAsync(w.error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
+  int rc = GBMM_OK;
+  float *ah = const_cast<float*>(w.A.hi), *al = const_cast<float*>(w.A.lo), *bh = const_cast<float*>(w.Bm.hi),
+        *bl = const_cast<float*>(w.Bm.lo), *gh = const_cast<float*>(w.G.hi), *gl = const_cast<float*>(w.G.lo);
+  if (lg) {
+    if (cudaMemsetAsync(w.flags, 0, sizeof(int) * B * ceil_div(d.n, 64), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
+    // both row maxima are needed whichever gradient is asked for (G' uses ra and rb)
+    rc = launch_skew<1>(a, nullptr, nullptr, nullptr, nullptr, w.ra, ah, al, B, d.n, d.a_lu, d.Wa(), w.A.s, st);
+    if (rc != GBMM_OK) return rc;
+    rc = launch_skew<1>(b, nullptr, nullptr, nullptr, nullptr, w.rb, bh, bl, B, d.n, d.b_lu, d.Wb(), w.Bm.s, st);
+    if (rc != GBMM_OK) return rc;
+    rc = band_saved_flags(part, w.ra, w.rb, w.flags, B, d.n, d.r_lu(), d.Wo(), st);
+    if (rc != GBMM_OK) return rc;
+    rc = launch_skew<2>(part, g, w.ra, w.rb, w.flags, nullptr, gh, gl, B, d.n, d.r_lu(), d.Wo(), w.G.s, st);
+  } else {
+    if (grad_b)
+      rc = launch_skew<0>(a, nullptr, nullptr, nullptr, nullptr, nullptr, ah, al, B, d.n, d.a_lu, d.Wa(), w.A.s, st);
+    if (rc != GBMM_OK) return rc;
+    if (grad_a)
+      rc = launch_skew<0>(b, nullptr, nullptr, nullptr, nullptr, nullptr, bh, bl, B, d.n, d.b_lu, d.Wb(), w.Bm.s, st);
+    if (rc != GBMM_OK) return rc;
+    rc = launch_skew<0>(g, nullptr, nullptr, nullptr, nullptr, nullptr, gh, gl, B, d.n, d.r_lu(), d.Wo(), w.G.s, st);
+  }
+  if (rc != GBMM_OK) return rc;
+  *flags_out = lg ? w.flags : nullptr;
+  const int r_lu = d.r_lu(), r_ld = d.Wo() - 1 - r_lu;
+  if (grad_a) {
+    // dXa[i,p] = sum_o G[i,o] Xb[o,p]: X = G K-major (o contiguous), Y = Xb MN-major (p contiguous)
+    BandTcArgs args{};
+    args.n = (int)d.n;
+    args.lu_out = d.a_lu;
+    args.w_out = d.Wa();
+    args.xl = r_lu; args.xu = r_ld; args.yl = d.b_ld; args.yu = d.b_lu;
+    args.out = grad_a;
+    args.error = w.error;
+    rc = launch_band_tc<E_SUM, false, true>(w.G, w.Bm, args, B, st);
+    if (rc != GBMM_OK) return rc;
+    if (lg) {  // log: dXa = EA (.) sum
+      band_scale_kernel<<<(unsigned)ceil_div(B * d.n, 8), 256, 0, st>>>(grad_a, a, w.ra, B * d.n, (int)d.n, d.a_lu,
+                                                                      d.Wa());
+      if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+    }
+  }
+  if (grad_b) {
+    // dXb[o,p] = sum_i G[i,o] Xa[i,p]: X = G MN-major (o contiguous), Y = Xa MN-major (p contiguous)
+    BandTcArgs args{};
+    args.n = (int)d.n;
+    args.lu_out = d.b_lu;
+    args.w_out = d.Wb();
+    args.xl = r_ld; args.xu = r_lu; args.yl = d.a_ld; args.yu = d.a_lu;
+    args.out = grad_b;
+    args.error = w.error;
+    rc = launch_band_tc<E_SUM, true, true>(w.G, w.A, args, B, st);
+    if (rc != GBMM_OK) return rc;
+    if (lg) {
+      band_scale_kernel<<<(unsigned)ceil_div(B * d.n, 8), 256, 0, st>>>(grad_b, b, w.rb, B * d.n, (int)d.n, d.b_lu,
+                                                                      d.Wb());
+      rc = launch_status();
+    }
+  }
+  return rc;
+}
+
+}  // namespace gbmm

@@ -135,6 +135,27 @@ int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_ld,
                            int64_t B, int64_t n, void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * Tensor-core variants of gbmm_band_forward_f32 / gbmm_band_backward_f32 for modes 3 (sum) and 0 (log)
+ * when both bands are at least 32 wide and n >= 128 (gbmm_band_tc_eligible): the three banded products run
+ * as 3xTF32 on tcgen05 over zero-padded, skewed copies of the operands kept in the workspace.  Same
+ * results as the plain entry points (log mode: same guard, flagged 64-row blocks are redone exactly).
+ * Workspace contract: at least gbmm_band_tc_workspace_bytes bytes, 256-byte aligned, zero-filled ONCE with
+ * gbmm_band_tc_workspace_init before its first use and afterwards only passed to these two functions with
+ * the same B, n and band widths (they rewrite the band cells of the copies, never the zero padding).  A
+ * backward workspace may also serve the forward.  Calls sharing a workspace must not overlap on the GPU.
+ * `maxes` and `idx` are not produced (mode 0 needs neither for its backward).
+ */
+int gbmm_band_tc_eligible(int mode, int64_t n, int a_lu, int a_ld, int b_lu, int b_ld);
+int64_t gbmm_band_tc_workspace_bytes(int backward, int64_t B, int64_t n, int a_lu, int a_ld, int b_lu, int b_ld);
+int gbmm_band_tc_workspace_init(void* workspace, int64_t workspace_bytes, void* stream);
+int gbmm_band_tc_forward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu, int b_ld,
+                             float* out, int64_t B, int64_t n, void* workspace, int64_t workspace_bytes,
+                             void* stream);
+int gbmm_band_tc_backward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu, int b_ld,
+                              const float* grad_out, const float* part, float* grad_a, float* grad_b,
+                              int64_t B, int64_t n, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * Banded log-semiring second-order terms.  Replaces `_genbmm.backbackward_band(a, a_lu, a_lb, b,
  * b_lu, b_lb, grad_output, part, maxes, grad_out_a, 0)` — banded_backbackward,
  * matmul_cuda.cpp:145-161 -> banded_cuda_backbackward, banded_cuda_kernel.cu:453-546 — extended to

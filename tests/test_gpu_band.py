@@ -11,7 +11,10 @@ pytestmark = pytest.mark.gpu
 # (B, n, a_lu, a_ld, b_lu, b_ld)
 CASES = [(2, 5, 2, 1, 1, 2), (3, 8, 0, 3, 2, 0), (2, 6, 3, 3, 3, 3), (1, 4, 5, 4, 0, 0), (2, 9, 1, 1, 2, 2),
          (1, 1, 0, 0, 0, 0), (2, 70, 4, 7, 9, 2), (2, 300, 20, 13, 5, 31), (1, 40, 64, 64, 64, 64),
-         (3, 33, 0, 0, 3, 1)]
+         (3, 33, 0, 0, 3, 1),
+         # bands >= 32 wide and n >= 128: the tensor-core path (sum, log), with odd sizes and offsets
+         (2, 300, 20, 15, 18, 17), (1, 128, 40, 3, 5, 40), (2, 517, 64, 64, 64, 64), (1, 257, 0, 40, 35, 0),
+         (1, 1000, 31, 1, 0, 33), (2, 130, 100, 90, 70, 120)]
 MODES = [("multiply", 3), ("multiply_log", 0), ("multiply_max", 1)]
 
 
@@ -51,9 +54,34 @@ def test_band_products_match_oracle(gb, case, method, mode):
         assert_equal_bits(gb_, dB, "max grad_b")
     else:
         out, _, _, dA, dB = oracle.band_fwd_bwd(mode, a, alu, ald, b, blu, bld, g, dtype=np.float64)
-        assert_close(r.data, out, what=method)
-        assert_close(ga, dA, what=method + " grad_a")
-        assert_close(gb_, dB, what=method + " grad_b")
+        bound = (None, None, None)
+        if mode == 3:  # signed terms: the same sums over absolute values bound the rounding error
+            t_out, _, _, t_dA, t_dB = oracle.band_fwd_bwd(mode, a.abs(), alu, ald, b.abs(), blu, bld, g.abs(),
+                                                          dtype=np.float64)
+            bound = (t_out, t_dA, t_dB)
+        assert_close(r.data, out, what=method, term_sum=bound[0])
+        assert_close(ga, dA, what=method + " grad_a", term_sum=bound[1])
+        assert_close(gb_, dB, what=method + " grad_b", term_sum=bound[2])
+    inside = band_inside(B, n, alu + bld, ald + blu)
+    assert (r.data.cpu().numpy()[~inside] == 0).all()
+
+
+@pytest.mark.parametrize("case", [c for c in CASES if c[1] >= 128 and min(c[2] + c[3], c[4] + c[5]) >= 31])
+def test_sum_semiring_on_tensor_cores(gb, case, monkeypatch):
+    """GENBMM_B200_BAND=tensor: the ordinary product and its gradients as 3xTF32 (opt-in; the default for the
+    sum semiring is the FP32 block kernel).  Bound: 1e-6 of the sum of the terms' magnitudes."""
+    monkeypatch.setenv("GENBMM_B200_BAND", "tensor")
+    B, n, alu, ald, blu, bld = case
+    gen = torch.Generator().manual_seed(sum(case))
+    a = torch.randn(B, n, alu + ald + 1, generator=gen)
+    b = torch.randn(B, n, blu + bld + 1, generator=gen)
+    g = torch.randn(B, n, alu + ald + blu + bld + 1, generator=gen)
+    r, ga, gb_ = run(gb, "multiply", a, alu, ald, b, blu, bld, g)
+    out, _, _, dA, dB = oracle.band_fwd_bwd(3, a, alu, ald, b, blu, bld, g, dtype=np.float64)
+    t_out, _, _, t_dA, t_dB = oracle.band_fwd_bwd(3, a.abs(), alu, ald, b.abs(), blu, bld, g.abs(), dtype=np.float64)
+    assert_close(r.data, out, what="multiply", term_sum=t_out)
+    assert_close(ga, dA, what="grad_a", term_sum=t_dA)
+    assert_close(gb_, dB, what="grad_b", term_sum=t_dB)
     inside = band_inside(B, n, alu + bld, ald + blu)
     assert (r.data.cpu().numpy()[~inside] == 0).all()
 
@@ -132,9 +160,13 @@ def test_wide_band_falls_back_to_global_reads(gb):
     for method, mode in MODES:
         r, ga, gb_ = run(gb, method, a, lu, ld, b, lu, ld, g)
         out, idx, _, dA, dB = oracle.band_fwd_bwd(mode, a, lu, ld, b, lu, ld, g, dtype=np.float64)
-        assert_close(r.data, out, 1e-5, 2e-5, what=method)
-        assert_close(ga, dA, 1e-5, 2e-5, what=method + " grad_a")
-        assert_close(gb_, dB, 1e-5, 2e-5, what=method + " grad_b")
+        bound = (None, None, None)
+        if mode == 3:
+            t_out, _, _, t_dA, t_dB = oracle.band_fwd_bwd(3, a.abs(), lu, ld, b.abs(), lu, ld, g.abs(), dtype=np.float64)
+            bound = (t_out, t_dA, t_dB)
+        assert_close(r.data, out, 1e-5, 2e-5, what=method, term_sum=bound[0])
+        assert_close(ga, dA, 1e-5, 2e-5, what=method + " grad_a", term_sum=bound[1])
+        assert_close(gb_, dB, 1e-5, 2e-5, what=method + " grad_b", term_sum=bound[2])
 
 
 def test_band_rejects_bad_inputs(gb):
@@ -145,16 +177,18 @@ def test_band_rejects_bad_inputs(gb):
         gb.BandedMatrix(a.cuda(), 2, 2)
 
 
-def test_band_log_guard_recomputes_flagged_row_blocks(gb, monkeypatch):
+@pytest.mark.parametrize("lu,ld", [(9, 8), (20, 20)], ids=["block", "tensor"])
+def test_band_log_guard_recomputes_flagged_row_blocks(gb, monkeypatch, lu, ld):
     """Operand rows whose supports miss each other make the factorised sum underflow: the row
-    block is flagged and goes through the exact kernels, forward and backward."""
+    block is flagged and goes through the exact kernels, forward and backward (17-wide bands: the
+    FP32 block kernels; 41-wide: the tensor-core kernels)."""
     from genbmm_b200 import _native
-    B, n, lu, ld = 2, 200, 9, 8
+    B, n = 2, 200
     gen = torch.Generator().manual_seed(5)
     a, b = torch.randn(B, n, lu + ld + 1, generator=gen), torch.randn(B, n, lu + ld + 1, generator=gen)
     g = torch.rand(B, n, 2 * (lu + ld) + 1, generator=gen)
-    a[:, 70:90, :9] -= 300.0     # rows 70..89 of a live on the upper half of the band ...
-    b[:, 60:100, 9:] -= 300.0    # ... the b rows they meet live on the lower half
+    a[:, 70:90, :lu] -= 300.0       # rows 70..89 of a live on the upper half of the band ...
+    b[:, 40:120, lu:] -= 300.0      # ... the b rows they meet live on the lower half
     out, ga, gb_ = run(gb, "multiply_log", a, lu, ld, b, lu, ld, g)
     want, _, _, dA, dB = oracle.band_fwd_bwd(0, a, lu, ld, b, lu, ld, g, dtype=np.float64)
     assert_close(out.data, want, 1e-5, 2e-5, "fwd")

@@ -7,11 +7,16 @@ import torch
 RTOL, ATOL = 1e-5, 2e-6
 
 
-def assert_close(got, want, rtol=RTOL, atol=ATOL, what=""):
+def assert_close(got, want, rtol=RTOL, atol=ATOL, what="", term_sum=None):
+    """|got - want| <= atol + rtol |want|.  For sums of signed terms (the ordinary semiring) a result may be
+    the small difference of large terms; `term_sum` = the same sum over the terms' absolute values then also
+    admits 1e-6 of it, the componentwise bound of a float32 sum (a few ulp of the terms' total)."""
     got = got.detach().cpu().numpy() if hasattr(got, "detach") else np.asarray(got)
     want = np.asarray(want)
     assert got.shape == want.shape, (what, got.shape, want.shape)
     bad = ~np.isclose(got, want, rtol=rtol, atol=atol, equal_nan=True)
+    if term_sum is not None:
+        bad &= ~(np.abs(got - want) <= 1e-6 * np.asarray(term_sum))
     if bad.any():
         i = np.argwhere(bad)[0]
         raise AssertionError("%s: %d of %d differ; first at %s: got %r want %r" % (
