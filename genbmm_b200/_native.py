@@ -33,7 +33,7 @@ _SIGNATURES = {
     "gbmm_band_tc_workspace_bytes": ([_I, _L, _L, _I, _I, _I, _I], _L),
     "gbmm_band_tc_workspace_init": ([_P, _L, _P], _I),
     "gbmm_band_tc_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _L, _L, _P, _L, _P], _I),
-    "gbmm_band_tc_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P, _L, _P], _I),
+    "gbmm_band_tc_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P, _L, _I, _P], _I),
     "gbmm_logbmm_workspace_bytes": ([_I, _L, _L, _L, _L], _L),
     "gbmm_logbmm_flag_count": ([_L, _L, _L], _L),
     "gbmm_logbmm_forward_f32": ([_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P], _I),
@@ -244,8 +244,22 @@ def _band_tc_workspace(mode, backward, B, n, bands, device):
     _band_tc_cache.pop(dev, None)
     ws = torch.empty((need,), dtype=torch.uint8, device=device)
     _check(lib.gbmm_band_tc_workspace_init(_ptr(ws), ws.numel(), _stream(device)), "gbmm_band_tc_workspace_init")
-    _band_tc_cache[dev] = (key, ws)
+    _band_tc_cache[dev] = [key, ws, None]
     return ws
+
+
+def _band_tc_tag(mode, a, b):
+    """Identifies the operand contents a workspace holds: storage address and version counter of both."""
+    return (mode, a.data_ptr(), a._version, b.data_ptr(), b._version, torch.cuda.current_stream(a.device).cuda_stream)
+
+
+def _band_tc_holds(ws, tag, store=False):
+    for entry in _band_tc_cache.values():
+        if entry[1] is ws:
+            if store:
+                entry[2] = tag
+            return entry[2] == tag
+    return False
 
 
 def _band_workspace(B, n, device):
@@ -278,6 +292,7 @@ def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode, want_maxes=False):
             st = load().gbmm_band_tc_forward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), B, n,
                                                  _ptr(tc_ws), tc_ws.numel(), _stream(a.device))
             _check(st, "gbmm_band_tc_forward_f32")
+            _band_tc_holds(tc_ws, _band_tc_tag(mode, a, b), store=True)
             return [out, idx, maxes]
         ws = _band_workspace(B, n, a.device) if mode == BAND_LOG else None
         st = load().gbmm_band_forward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), _ptr(idx),
@@ -287,12 +302,15 @@ def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode, want_maxes=False):
     return [out, idx, maxes]
 
 
-def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=False):
+def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=False, reuse_forward=False):
     """`_genbmm.backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode)` -> [grad_a].
 
     With both=True returns [grad_a, grad_b], grad_b computed directly by a second kernel rather
     than by the reference's swap-and-transpose route (sparse.py:436-446).  `part` is the forward
     output (mode 0), the int32 or float indices in a's band coordinate (mode 1), ignored (mode 3).
+    reuse_forward=True (for callers that kept a and b alive and unmodified since `forward_band`, as autograd
+    does): when that forward was the last banded tensor-core call on this device and stream, its converted
+    operands, row maxima and guard flags are reused.
     """
     _check_band(a, a_lu, a_lb, b, b_lu, b_lb)
     _check_input(grad_output, "grad_output")
@@ -318,10 +336,17 @@ def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=Fa
         if load().gbmm_band_tc_eligible(mode, n, *bands):
             tc_ws = _band_tc_workspace(mode, True, B, n, bands, a.device)
         if tc_ws is not None:
+            # the forward of these very operands (same storage, unmodified, same stream) may have been the last
+            # banded call on this device: its converted operands, row maxima and flags are still in place
+            ready = 1 if reuse_forward and _band_tc_holds(tc_ws, _band_tc_tag(mode, a, b)) else 0
             st = load().gbmm_band_tc_backward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(grad_output),
                                                   _ptr(part), _ptr(grad_a), _ptr(grad_b), B, n, _ptr(tc_ws),
-                                                  tc_ws.numel(), _stream(a.device))
+                                                  tc_ws.numel(), ready, _stream(a.device))
             _check(st, "gbmm_band_tc_backward_f32")
+            if not both:  # only b's copy is rebuilt when grad_b is not wanted (sum semiring)
+                _band_tc_holds(tc_ws, None, store=True)
+            else:
+                _band_tc_holds(tc_ws, _band_tc_tag(mode, a, b), store=True)
             return [grad_a, grad_b] if both else [grad_a]
         ws = _band_workspace(B, n, a.device) if mode == BAND_LOG else None
         st = load().gbmm_band_backward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(grad_output),

@@ -682,7 +682,7 @@ extern "C" int gbmm_band_tc_forward_f32(int mode, const float* a, int a_lu, int 
 extern "C" int gbmm_band_tc_backward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu,
                                          int b_ld, const float* grad_out, const float* part, float* grad_a,
                                          float* grad_b, int64_t B, int64_t n, void* workspace,
-                                         int64_t workspace_bytes, void* stream) {
+                                         int64_t workspace_bytes, int operands_ready, void* stream) {
   const int st0 = check_band(mode, B, n, a_lu, a_ld, b_lu, b_ld);
   if (st0 != GBMM_OK) return st0;
   if (B == 0 || n == 0) return GBMM_OK;
@@ -694,7 +694,8 @@ extern "C" int gbmm_band_tc_backward_f32(int mode, const float* a, int a_lu, int
     return GBMM_ERR_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int* flags = nullptr;
-  const int rc = band_tc_backward(mode, a, b, grad_out, part, grad_a, grad_b, d, B, workspace, &flags, st);
+  const int rc = band_tc_backward(mode, a, b, grad_out, part, grad_a, grad_b, d, B, workspace, operands_ready, &flags,
+                                  st);
   if (rc != GBMM_OK || mode != GBMM_BAND_LOG) return rc;
   return exact_backward(mode, a, b, grad_out, part, grad_a, grad_b, d, B, flags, st);
 }

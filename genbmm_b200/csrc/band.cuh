@@ -31,6 +31,7 @@ int64_t band_tc_workspace_bytes(int backward, int64_t B, const BandDims& d);
 int band_tc_forward(int mode, const float* a, const float* b, float* out, const BandDims& d, int64_t B, void* ws,
                     int** flags_out, cudaStream_t st);
 int band_tc_backward(int mode, const float* a, const float* b, const float* g, const float* part, float* grad_a,
-                     float* grad_b, const BandDims& d, int64_t B, void* ws, int** flags_out, cudaStream_t st);
+                     float* grad_b, const BandDims& d, int64_t B, void* ws, int operands_ready, int** flags_out,
+                     cudaStream_t st);
 
 }  // namespace gbmm

@@ -48,7 +48,8 @@ int64_t skew_floats(const Skew& s, int64_t B) { return pad64(B * s.bstride + 64)
 
 // One warp per band row.  KIND 0: v = x.  KIND 1: v = exp(x - m), m = the row's maximum over its in-matrix
 // cells (0 when there is none), also written to ra_out[row].  KIND 2: v = g * exp(ra[row] + rb[col] - x), x
-// the saved output, 0 in flagged 64-row blocks.  Cells outside the matrix become 0.
+// the saved output, 0 in flagged 64-row blocks.  Cells outside the matrix become 0.  Rows of up to 256
+// cells are held in registers (all loads of a row in flight at once); wider rows are walked twice.
 template <int KIND>
 __global__ void __launch_bounds__(256) band_skew_kernel(const float* __restrict__ x, const float* __restrict__ g,
                                                         const float* __restrict__ ra, const float* __restrict__ rb,
@@ -63,8 +64,52 @@ __global__ void __launch_bounds__(256) band_skew_kernel(const float* __restrict_
   const float* xr = x + row * W;
   // in-matrix cells of this row: j in [jlo, jhi)
   const int jlo = max(0, lu - i), jhi = min(W, n - i + lu);
+  float* hr = hi + bt * bstride + (int64_t)i * pitch + off;
+  float* lr = lo + bt * bstride + (int64_t)i * pitch + off;
+  const float* gr = KIND == 2 ? g + row * W : nullptr;
+  const float* rbb = KIND == 2 ? rb + bt * n + (i - lu) : nullptr;  // rbb[j] = rb of column i + j - lu
   float shift = 0.f;
   bool dead = false;
+  if (KIND == 2) {
+    shift = __ldg(ra + row);
+    dead = __ldg(flags + bt * ((n + 63) / 64) + i / 64) != 0;
+  }
+  constexpr int NV = 8;
+  if (W <= 32 * NV) {
+    float xv[NV], gv[NV], cv[NV];
+#pragma unroll
+    for (int q = 0; q < NV; ++q) {
+      const int j = lane + 32 * q;
+      const bool in = j >= jlo && j < jhi;
+      xv[q] = in ? __ldg(xr + j) : __int_as_float(0xff800000);
+      gv[q] = (KIND == 2 && in) ? __ldg(gr + j) : 0.f;
+      cv[q] = (KIND == 2 && in) ? __ldg(rbb + j) : 0.f;
+    }
+    if (KIND == 1) {
+      float m = xv[0];
+#pragma unroll
+      for (int q = 1; q < NV; ++q) m = fmaxf(m, xv[q]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      shift = (m == __int_as_float(0xff800000)) ? 0.f : m;
+      if (lane == 0) ra_out[row] = shift;
+    }
+#pragma unroll
+    for (int q = 0; q < NV; ++q) {
+      const int j = lane + 32 * q;
+      if (j >= W) break;
+      float v = 0.f;
+      if (j >= jlo && j < jhi) {
+        if (KIND == 0) v = xv[q];
+        if (KIND == 1) v = exp_sfu(xv[q] - shift);
+        if (KIND == 2) v = dead ? 0.f : gv[q] * exp_sfu((shift + cv[q]) - xv[q]);
+      }
+      const float h = tf32_round(v);
+      hr[j] = h;
+      lr[j] = v - h;
+    }
+    return;
+  }
   if (KIND == 1) {
     float m = __int_as_float(0xff800000);
     for (int j = jlo + lane; j < jhi; j += 32) m = fmaxf(m, __ldg(xr + j));
@@ -73,14 +118,6 @@ __global__ void __launch_bounds__(256) band_skew_kernel(const float* __restrict_
     shift = (m == __int_as_float(0xff800000)) ? 0.f : m;
     if (lane == 0) ra_out[row] = shift;
   }
-  if (KIND == 2) {
-    shift = __ldg(ra + row);
-    dead = __ldg(flags + bt * ((n + 63) / 64) + i / 64) != 0;
-  }
-  float* hr = hi + bt * bstride + (int64_t)i * pitch + off;
-  float* lr = lo + bt * bstride + (int64_t)i * pitch + off;
-  const float* gr = KIND == 2 ? g + row * W : nullptr;
-  const float* rbb = KIND == 2 ? rb + bt * n + (i - lu) : nullptr;  // rbb[j] = rb of column i + j - lu
   for (int j = lane; j < W; j += 32) {
     float v = 0.f;
     if (j >= jlo && j < jhi) {
@@ -503,7 +540,8 @@ int band_tc_forward(int mode, const float* a, const float* b, float* out, const 
 }
 
 int band_tc_backward(int mode, const float* a, const float* b, const float* g, const float* part, float* grad_a,
-                     float* grad_b, const BandDims& d, int64_t B, void* ws, int** flags_out, cudaStream_t st) {
+                     float* grad_b, const BandDims& d, int64_t B, void* ws, int operands_ready, int** flags_out,
+                     cudaStream_t st) {
   const BandWs w = carve_ws(ws, B, d, true);
   const bool lg = mode == GBMM_BAND_LOG;
   if (cudaMemsetAsync(w.error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
@@ -511,20 +549,22 @@ int band_tc_backward(int mode, const float* a, const float* b, const float* g, c
   float *ah = const_cast<float*>(w.A.hi), *al = const_cast<float*>(w.A.lo), *bh = const_cast<float*>(w.Bm.hi),
         *bl = const_cast<float*>(w.Bm.lo), *gh = const_cast<float*>(w.G.hi), *gl = const_cast<float*>(w.G.lo);
   if (lg) {
-    if (cudaMemsetAsync(w.flags, 0, sizeof(int) * B * ceil_div(d.n, 64), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
-    // both row maxima are needed whichever gradient is asked for (G' uses ra and rb)
-    rc = launch_skew<1>(a, nullptr, nullptr, nullptr, nullptr, w.ra, ah, al, B, d.n, d.a_lu, d.Wa(), w.A.s, st);
-    if (rc != GBMM_OK) return rc;
-    rc = launch_skew<1>(b, nullptr, nullptr, nullptr, nullptr, w.rb, bh, bl, B, d.n, d.b_lu, d.Wb(), w.Bm.s, st);
-    if (rc != GBMM_OK) return rc;
-    rc = band_saved_flags(part, w.ra, w.rb, w.flags, B, d.n, d.r_lu(), d.Wo(), st);
-    if (rc != GBMM_OK) return rc;
+    if (!operands_ready) {
+      if (cudaMemsetAsync(w.flags, 0, sizeof(int) * B * ceil_div(d.n, 64), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
+      // both row maxima are needed whichever gradient is asked for (G' uses ra and rb)
+      rc = launch_skew<1>(a, nullptr, nullptr, nullptr, nullptr, w.ra, ah, al, B, d.n, d.a_lu, d.Wa(), w.A.s, st);
+      if (rc != GBMM_OK) return rc;
+      rc = launch_skew<1>(b, nullptr, nullptr, nullptr, nullptr, w.rb, bh, bl, B, d.n, d.b_lu, d.Wb(), w.Bm.s, st);
+      if (rc != GBMM_OK) return rc;
+      rc = band_saved_flags(part, w.ra, w.rb, w.flags, B, d.n, d.r_lu(), d.Wo(), st);
+      if (rc != GBMM_OK) return rc;
+    }
     rc = launch_skew<2>(part, g, w.ra, w.rb, w.flags, nullptr, gh, gl, B, d.n, d.r_lu(), d.Wo(), w.G.s, st);
   } else {
-    if (grad_b)
+    if (grad_b && !operands_ready)
       rc = launch_skew<0>(a, nullptr, nullptr, nullptr, nullptr, nullptr, ah, al, B, d.n, d.a_lu, d.Wa(), w.A.s, st);
     if (rc != GBMM_OK) return rc;
-    if (grad_a)
+    if (grad_a && !operands_ready)
       rc = launch_skew<0>(b, nullptr, nullptr, nullptr, nullptr, nullptr, bh, bl, B, d.n, d.b_lu, d.Wb(), w.Bm.s, st);
     if (rc != GBMM_OK) return rc;
     rc = launch_skew<0>(g, nullptr, nullptr, nullptr, nullptr, nullptr, gh, gl, B, d.n, d.r_lu(), d.Wo(), w.G.s, st);

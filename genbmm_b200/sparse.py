@@ -203,7 +203,7 @@ class _BandedProduct(torch.autograd.Function):
         a, b = saved[0], saved[1]
         part = saved[2].detach() if len(saved) > 2 else None
         grad_a, grad_b = _native.backward_band(a, a_lu, a_ld, b, b_lu, b_ld, grad_output.contiguous(), part,
-                                               cls.MODE, both=True)
+                                               cls.MODE, both=True, reuse_forward=True)
         return grad_a, None, None, grad_b, None, None, None, None
 
 
@@ -229,7 +229,7 @@ class BandedLogMulBack(torch.autograd.Function):
         ctx.bands = bands
         a_lu, a_ld, b_lu, b_ld = bands
         grad_a, grad_b = _native.backward_band(a, a_lu, a_ld, b, b_lu, b_ld, grad_out, part, _native.BAND_LOG,
-                                               both=True)
+                                               both=True, reuse_forward=True)
         return grad_a, grad_b
 
     @staticmethod

@@ -144,6 +144,9 @@ int gbmm_band_backward_f32(int mode, const float* a, int a_lu, int a_ld,
  * the same B, n and band widths (they rewrite the band cells of the copies, never the zero padding).  A
  * backward workspace may also serve the forward.  Calls sharing a workspace must not overlap on the GPU.
  * `maxes` and `idx` are not produced (mode 0 needs neither for its backward).
+ * operands_ready != 0 tells the backward that the workspace still holds what the last
+ * gbmm_band_tc_forward_f32 call of the same mode left for exactly these a and b (unchanged since): their
+ * skewed copies, row maxima and guard flags are then reused instead of rebuilt.
  */
 int gbmm_band_tc_eligible(int mode, int64_t n, int a_lu, int a_ld, int b_lu, int b_ld);
 int64_t gbmm_band_tc_workspace_bytes(int backward, int64_t B, int64_t n, int a_lu, int a_ld, int b_lu, int b_ld);
@@ -153,7 +156,8 @@ int gbmm_band_tc_forward_f32(int mode, const float* a, int a_lu, int a_ld, const
                              void* stream);
 int gbmm_band_tc_backward_f32(int mode, const float* a, int a_lu, int a_ld, const float* b, int b_lu, int b_ld,
                               const float* grad_out, const float* part, float* grad_a, float* grad_b,
-                              int64_t B, int64_t n, void* workspace, int64_t workspace_bytes, void* stream);
+                              int64_t B, int64_t n, void* workspace, int64_t workspace_bytes,
+                              int operands_ready, void* stream);
 
 /*
  * Banded log-semiring second-order terms.  Replaces `_genbmm.backbackward_band(a, a_lu, a_lb, b,
