@@ -25,6 +25,10 @@ _SIGNATURES = {
     "gbmm_dense_forward_f32": ([_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _L, _P], _I),
     "gbmm_dense_backward_f32": ([_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
     "gbmm_dense_backbackward_f32": ([_P] * 9 + [_L] * 4 + [_P], _I),
+    "gbmm_dense_forward_f64": ([_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
+    "gbmm_dense_backward_f64": ([_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
+    "gbmm_band_forward_f64": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L, _P], _I),
+    "gbmm_band_backward_f64": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P], _I),
     "gbmm_band_workspace_bytes": ([_L, _L], _L),
     "gbmm_band_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L, _P, _L, _P], _I),
     "gbmm_band_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P, _L, _P], _I),
@@ -99,6 +103,11 @@ def _check_input(x, name, dtype=torch.float32):
         raise RuntimeError("%s must be %s (got %s)" % (name, dtype, x.dtype))
 
 
+def _compute_dtype(x):
+    """float32 or float64 kernels; anything else is an error here (the operators widen half / bfloat16)."""
+    return torch.float64 if x.dtype == torch.float64 else torch.float32
+
+
 def _stream(dev):
     return torch.cuda.current_stream(dev).cuda_stream
 
@@ -117,8 +126,9 @@ def forward(a, b, mode, u=None, want_maxes=True):
     Mode 2 (sample) takes the uniforms `u`:(B,M,N); when None they are drawn with torch.rand
     on the device, as the reference does inside its dispatcher (matmul_cuda_kernel.cu:517).
     """
-    _check_input(a, "a")
-    _check_input(b, "b")
+    dt = _compute_dtype(a)
+    _check_input(a, "a", dt)
+    _check_input(b, "b", dt)
     if a.dim() != 3 or b.dim() != 3 or a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1]:
         raise RuntimeError("expected a:(B,M,K) and b:(B,K,N), got %s and %s" % (tuple(a.shape), tuple(b.shape)))
     if b.device != a.device:
@@ -136,9 +146,14 @@ def forward(a, b, mode, u=None, want_maxes=True):
         if mode == MODE_SAMPLE:
             if u is None:
                 u = torch.rand((B, M, N), dtype=a.dtype, device=a.device)
-            _check_input(u, "u")
+            _check_input(u, "u", dt)
             if tuple(u.shape) != (B, M, N):
                 raise RuntimeError("u must have shape %s" % ((B, M, N),))
+        if dt == torch.float64:
+            st = load().gbmm_dense_forward_f64(mode, _ptr(a), _ptr(b), _ptr(u) if mode == MODE_SAMPLE else None,
+                                               _ptr(out), _ptr(aux), B, M, K, N, _stream(a.device))
+            _check(st, "gbmm_dense_forward_f64")
+            return [out, aux]
         nbytes = load().gbmm_dense_forward_workspace_bytes(mode, B, M, K, N)
         ws = torch.empty((nbytes,), dtype=torch.uint8, device=a.device) if nbytes > 0 else None
         st = load().gbmm_dense_forward_f32(mode, _ptr(a), _ptr(b), _ptr(u) if mode == MODE_SAMPLE else None,
@@ -154,16 +169,17 @@ def backward(a, b, grad_output, part, maxes, mode):
     not read.  Modes 1-3: `part` holds the saved indices (int32, or the float copy the
     reference's Python passes, genmul.py:63).  Unlike the reference, mode 0 fills grad_b too.
     """
-    _check_input(a, "a")
-    _check_input(b, "b")
-    _check_input(grad_output, "grad_output")
+    dt = _compute_dtype(a)
+    _check_input(a, "a", dt)
+    _check_input(b, "b", dt)
+    _check_input(grad_output, "grad_output", dt)
     B, M, K = a.shape
     N = b.shape[2]
     if tuple(grad_output.shape) != (B, M, N):
         raise RuntimeError("grad_output must have shape %s" % ((B, M, N),))
     with torch.cuda.device(a.device):
         if mode == MODE_LOG:
-            _check_input(part, "part")
+            _check_input(part, "part", dt)
             pf, aux = part, None
         else:
             if part.dtype != torch.int32:
@@ -174,6 +190,11 @@ def backward(a, b, grad_output, part, maxes, mode):
             raise RuntimeError("part must have shape %s" % ((B, M, N),))
         grad_a = torch.empty_like(a)
         grad_b = torch.empty_like(b)
+        if dt == torch.float64:
+            st = load().gbmm_dense_backward_f64(mode, _ptr(a), _ptr(b), _ptr(grad_output), _ptr(pf), _ptr(aux),
+                                                _ptr(grad_a), _ptr(grad_b), B, M, K, N, _stream(a.device))
+            _check(st, "gbmm_dense_backward_f64")
+            return [grad_a, grad_b]
         st = load().gbmm_dense_backward_f32(mode, _ptr(a), _ptr(b), _ptr(grad_output), _ptr(pf), _ptr(aux),
                                             _ptr(grad_a), _ptr(grad_b), B, M, K, N, _stream(a.device))
     _check(st, "gbmm_dense_backward_f32")
@@ -207,8 +228,8 @@ def backbackward(a, b, grad_output, part, maxes, grad_out_a, mode=0, grad_out_b=
 
 
 def _check_band(a, a_lu, a_lb, b, b_lu, b_lb):
-    _check_input(a, "a")
-    _check_input(b, "b")
+    _check_input(a, "a", _compute_dtype(a))
+    _check_input(b, "b", _compute_dtype(a))
     if a.dim() != 3 or b.dim() != 3 or a.shape[:2] != b.shape[:2]:
         raise RuntimeError("expected a:(B,n,Wa) and b:(B,n,Wb), got %s and %s" % (tuple(a.shape), tuple(b.shape)))
     if a.shape[2] != a_lu + a_lb + 1 or b.shape[2] != b_lu + b_lb + 1:
@@ -285,6 +306,11 @@ def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode, want_maxes=False):
         idx = torch.empty((B, n, Wo), dtype=torch.int32, device=a.device) if mode == BAND_MAX else None
         maxes = torch.empty_like(out) if (mode == BAND_LOG and want_maxes) else None
         bands = (a_lu, a_lb, b_lu, b_lb)
+        if a.dtype == torch.float64:
+            st = load().gbmm_band_forward_f64(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), _ptr(idx),
+                                              _ptr(maxes), B, n, _stream(a.device))
+            _check(st, "gbmm_band_forward_f64")
+            return [out, idx, maxes]
         tc_ws = None
         if maxes is None and load().gbmm_band_tc_eligible(mode, n, *bands):
             tc_ws = _band_tc_workspace(mode, False, B, n, bands, a.device)
@@ -313,7 +339,7 @@ def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=Fa
     operands, row maxima and guard flags are reused.
     """
     _check_band(a, a_lu, a_lb, b, b_lu, b_lb)
-    _check_input(grad_output, "grad_output")
+    _check_input(grad_output, "grad_output", _compute_dtype(a))
     B, n, Wa = a.shape
     Wo = Wa + b.shape[2] - 1
     if tuple(grad_output.shape) != (B, n, Wo):
@@ -324,13 +350,18 @@ def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=Fa
                 part = part.to(torch.int32)
             _check_input(part, "part", torch.int32)
         elif mode == BAND_LOG:
-            _check_input(part, "part")
+            _check_input(part, "part", _compute_dtype(a))
         else:
             part = None
         if part is not None and tuple(part.shape) != (B, n, Wo):
             raise RuntimeError("part must have shape %s" % ((B, n, Wo),))
         grad_a = torch.empty_like(a)
         grad_b = torch.empty_like(b) if both else None
+        if a.dtype == torch.float64:
+            st = load().gbmm_band_backward_f64(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(grad_output),
+                                               _ptr(part), _ptr(grad_a), _ptr(grad_b), B, n, _stream(a.device))
+            _check(st, "gbmm_band_backward_f64")
+            return [grad_a, grad_b] if both else [grad_a]
         bands = (a_lu, a_lb, b_lu, b_lb)
         tc_ws = None
         if load().gbmm_band_tc_eligible(mode, n, *bands):

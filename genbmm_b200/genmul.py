@@ -23,11 +23,13 @@ def trans(s):
 
 
 def _as_f32(x, name):
-    if x.dtype == torch.float32:
+    """The tensor the kernels compute on: float32 and float64 as they are, half and bfloat16 widened to
+    float32 (results are cast back to the input's dtype)."""
+    if x.dtype in (torch.float32, torch.float64):
         return x
     if x.dtype in (torch.float16, torch.bfloat16):
         return x.float()
-    raise RuntimeError("%s: dtype %s is not supported by the fp32 kernels" % (name, x.dtype))
+    raise RuntimeError("%s: dtype %s is not supported" % (name, x.dtype))
 
 
 def _log_path(M, K, N):
@@ -65,6 +67,8 @@ class LogMatMulBack(torch.autograd.Function):
     @staticmethod
     def backward(ctx, h_a, h_b):
         a, b, grad_out, part = ctx.saved_tensors
+        if a.dtype == torch.float64:
+            raise RuntimeError("logbmm: second-order gradients are implemented for float32 inputs only")
         d_a, d_b, d_g = _native.backbackward(a, b, grad_out, part, None,
                                              None if h_a is None else h_a.float(), 0,
                                              None if h_b is None else h_b.float())
@@ -77,6 +81,8 @@ class LogMatMul(torch.autograd.Function):
         a32, b32 = _as_f32(a, "a"), _as_f32(b, "b")
         ctx.aux = None
         path = _log_path(a32.shape[1], a32.shape[2], b32.shape[-1]) if a32.dim() == 3 and b32.dim() == 3 else "exact"
+        if a32.dtype == torch.float64:
+            path = "exact"  # the factorised paths are float32 kernels
         if path != "exact":
             tc = path == "tensor"
             # the split exponentiated operands (4x the size of a and b) stay alive until the backward
@@ -94,7 +100,7 @@ class LogMatMul(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         a, b, out = ctx.saved_tensors
-        grad_a, grad_b = LogMatMulBack.apply(a, b, grad_output.contiguous().float(), out, ctx.aux)
+        grad_a, grad_b = LogMatMulBack.apply(a, b, grad_output.contiguous().to(a.dtype), out, ctx.aux)
         return grad_a.to(ctx.dtypes[0]), grad_b.to(ctx.dtypes[1])
 
 
@@ -114,7 +120,7 @@ class _IndexRouted(torch.autograd.Function):
     @classmethod
     def _backward(cls, ctx, grad_output):
         a, b, switches = ctx.saved_tensors
-        grad_a, grad_b = _native.backward(a, b, grad_output.contiguous().float(), switches, switches, cls.MODE)
+        grad_a, grad_b = _native.backward(a, b, grad_output.contiguous().to(a.dtype), switches, switches, cls.MODE)
         return grad_a.to(ctx.dtypes[0]), grad_b.to(ctx.dtypes[1])
 
 

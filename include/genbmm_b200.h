@@ -173,6 +173,24 @@ int gbmm_band_backbackward_f32(const float* a, int a_lu, int a_ld, const float* 
                                int64_t B, int64_t n, void* stream);
 
 /*
+ * Double-precision entry points: the reference dispatches every kernel over float, double and half
+ * (AT_DISPATCH_FLOATING_TYPES_AND_HALF, matmul_cuda_kernel.cu:489; AT_DISPATCH_FLOATING_TYPES,
+ * banded_cuda_kernel.cu:389).  Same arguments and semantics as the _f32 functions with double data (indices stay
+ * int32); no workspace.  Half and bfloat16 inputs are widened to float by the Python layer, as nothing in the
+ * path is bound by their storage.
+ */
+int gbmm_dense_forward_f64(int mode, const double* a, const double* b, const double* u, double* out, void* aux,
+                           int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+int gbmm_dense_backward_f64(int mode, const double* a, const double* b, const double* grad_out, const double* part,
+                            const void* aux, double* grad_a, double* grad_b,
+                            int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+int gbmm_band_forward_f64(int mode, const double* a, int a_lu, int a_ld, const double* b, int b_lu, int b_ld,
+                          double* out, int32_t* idx, double* maxes, int64_t B, int64_t n, void* stream);
+int gbmm_band_backward_f64(int mode, const double* a, int a_lu, int a_ld, const double* b, int b_lu, int b_ld,
+                           const double* grad_out, const void* part, double* grad_a, double* grad_b,
+                           int64_t B, int64_t n, void* stream);
+
+/*
  * Factorised log-semiring product (fast path of logbmm).  Same result as
  * gbmm_dense_forward_f32(GBMM_MODE_LOG, ...) / gbmm_dense_backward_f32 within fp32 rounding,
  * computed as ordinary fp32 matrix products of exponentiated operands

@@ -52,8 +52,10 @@ def test_host_mirror_rejects_cpu_and_strided_tensors():
             fn(a, b)
     with pytest.raises(RuntimeError, match="a must be a CUDA tensor"):
         gb.BandedMatrix(torch.rand(2, 5, 3), 1, 1).multiply_log(gb.BandedMatrix(torch.rand(2, 5, 3), 1, 1))
+    with pytest.raises(RuntimeError, match="a must be a CUDA tensor"):
+        gb.logbmm(a.double(), b.double())   # float64 has kernels of its own, and the same checks
     with pytest.raises(RuntimeError, match="not supported"):
-        gb.logbmm(a.double(), b.double())
+        gb.logbmm(a.long(), b.long())
 
 
 def test_public_names_match_the_reference():
