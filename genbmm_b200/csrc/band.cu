@@ -340,36 +340,58 @@ __global__ void __launch_bounds__(256) band_route_a_kernel(const int* __restrict
   for (int k = lane; k < Wa; k += 32) grad_a[row * Wa + k] = hist[k];
 }
 
-// grad_b: one warp per 32 consecutive rows o of b; lane = one o, walking the contributing rows
-// i = o-jo+r_lu in ascending order into its private column of the [Wb][33] histogram.
-__global__ void __launch_bounds__(32) band_route_b_kernel(const int* __restrict__ idx, const float* __restrict__ g,
-                                                          float* __restrict__ grad_b, BandDims d, int tiles_o) {
-  extern __shared__ float hist[];
-  const int lane = threadIdx.x;
+// grad_b: one CTA of 32 warps per 32 consecutive rows o of b.  The cells (i, jo = o - i + r_lu) that feed
+// row o lie on an anti-diagonal of idx / g, so rows i are taken 32 at a time as coalesced 32 x 63 tiles and
+// turned through shared memory: warp w then owns o = o0 + w, its lanes 32 consecutive i, and lanes that
+// target the same bucket k2 add one after another in lane (= i) order — the ascending-i sum a sequential
+// walk would give.  hist: [32 rows o][Wb + 1].
+__global__ void __launch_bounds__(1024) band_route_b_kernel(const int* __restrict__ idx, const float* __restrict__ g,
+                                                            float* __restrict__ grad_b, BandDims d, int tiles_o) {
+  extern __shared__ float hist_all[];
+  __shared__ int si[32][66];
+  __shared__ float sg[32][66];
+  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu(), r_ld = Wo - 1 - r_lu;
   const int64_t n = d.n;
   const int64_t bt = blockIdx.x / tiles_o;
-  const int64_t o0 = (int64_t)(blockIdx.x % tiles_o) * 32, o = o0 + lane;
+  const int64_t o0 = (int64_t)(blockIdx.x % tiles_o) * 32, o = o0 + warp;
   const int* ib = idx + bt * n * Wo;
   const float* gb = g + bt * n * Wo;
-  for (int k = 0; k < Wb; ++k) hist[k * 33 + lane] = 0.f;
+  float* hist = hist_all + warp * (Wb + 1);
+  for (int k = lane; k < Wb; k += 32) hist[k] = 0.f;
   const int64_t i_lo = max((int64_t)0, o0 - r_ld), i_hi = min(n - 1, o0 + 31 + r_lu);
-  if (o < n) {
-#pragma unroll 4
-    for (int64_t i = i_lo; i <= i_hi; ++i) {
-      const int64_t jo = o - i + r_lu;
-      if (jo < 0 || jo >= Wo) continue;
-      const int ja = __ldg(ib + i * Wo + jo);
-      const int k2 = ja - (int)jo + Wb - 1;
-      const int64_t p = i + ja - d.a_lu;
-      if (ja >= 0 && ja < Wa && k2 >= 0 && k2 < Wb && p >= 0 && p < n)
-        hist[k2 * 33 + lane] = __fadd_rn(hist[k2 * 33 + lane], __ldg(gb + i * Wo + jo));
+  for (int64_t i0 = i_lo; i0 <= i_hi; i0 += 32) {
+    // tile row = warp (i = i0 + warp), tile column c <-> jo = jbase + c, c in [0, 63)
+    const int64_t jbase = o0 - i0 - 31 + r_lu, ii = i0 + warp;
+    __syncthreads();  // the previous tile has been consumed
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c = lane + 32 * h;
+      const int64_t jo = jbase + c;
+      const bool ok = c < 63 && ii <= i_hi && jo >= 0 && jo < Wo;
+      si[warp][c] = ok ? __ldg(ib + ii * Wo + jo) : -1;
+      sg[warp][c] = ok ? __ldg(gb + ii * Wo + jo) : 0.f;
+    }
+    __syncthreads();
+    // lane = row of the tile; this warp's o meets it at column warp + 31 - lane
+    const int ja = si[lane][warp + 31 - lane];
+    const float gv = sg[lane][warp + 31 - lane];
+    const int64_t i = i0 + lane, jo = o - i + r_lu;
+    const int k2 = ja - (int)jo + Wb - 1;
+    const int64_t p = i + ja - d.a_lu;
+    const bool hit = o < n && ja >= 0 && ja < Wa && k2 >= 0 && k2 < Wb && p >= 0 && p < n;
+    // lanes without a target get distinct negative keys so they group with nobody
+    const unsigned peers = __match_any_sync(0xffffffffu, hit ? k2 : -1 - lane);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
+    for (int r = 0; r <= last; ++r) {
+      if (hit && rank == r) hist[k2] = __fadd_rn(hist[k2], gv);
+      __syncwarp();
     }
   }
   __syncwarp();
-  float* ob = grad_b + bt * n * Wb;
-  for (int ol = 0; ol < 32 && o0 + ol < n; ++ol)
-    for (int k = lane; k < Wb; k += 32) ob[(o0 + ol) * Wb + k] = hist[k * 33 + ol];
+  if (o < n)
+    for (int k = lane; k < Wb; k += 32) grad_b[(bt * n + o) * Wb + k] = hist[k];
 }
 
 // ------------------------------------------------------------------ log semiring, second order
@@ -515,8 +537,8 @@ static int exact_forward(int mode, const float* a, const float* b, float* out, i
 
 static int route_max_backward(const float* grad_out, const int* idx, float* grad_a, float* grad_b,
                               const BandDims& d, int64_t B, cudaStream_t st, bool* handled) {
-  const size_t smem_a = sizeof(float) * 8 * d.Wa(), smem_b = sizeof(float) * 33 * d.Wb();
-  *handled = smem_a <= (size_t)kSmemBudget && smem_b <= (size_t)kSmemBudget;
+  const size_t smem_a = sizeof(float) * 8 * d.Wa(), smem_b = sizeof(float) * 32 * (d.Wb() + 1);
+  *handled = smem_a <= (size_t)kSmemBudget && smem_b + 17 * 1024 <= (size_t)kSmemBudget;
   if (!*handled) return GBMM_OK;  // bands too wide for the histograms: the scanning kernels take over
   if (grad_a) {
     const int64_t rows = B * d.n, blocks = ceil_div(rows, 8);
@@ -528,8 +550,9 @@ static int route_max_backward(const float* grad_out, const int* idx, float* grad
   if (grad_b) {
     const int64_t tiles = ceil_div(d.n, 32), blocks = B * tiles;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
-    if (smem_b > 48 * 1024 && !allow_smem(band_route_b_kernel, smem_b)) return GBMM_ERR_LAUNCH;
-    band_route_b_kernel<<<(unsigned)blocks, 32, smem_b, st>>>(idx, grad_out, grad_b, d, (int)tiles);
+    // the kernel also holds 16.5 KB of static tiles; together they may pass the 48 KB default
+    if (smem_b + 17 * 1024 > 48 * 1024 && !allow_smem(band_route_b_kernel, smem_b)) return GBMM_ERR_LAUNCH;
+    band_route_b_kernel<<<(unsigned)blocks, 1024, smem_b, st>>>(idx, grad_out, grad_b, d, (int)tiles);
   }
   return launch_status();
 }
