@@ -33,6 +33,10 @@ _SIGNATURES = {
     "gbmm_band_forward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _L, _L, _P, _L, _P], _I),
     "gbmm_band_backward_f32": ([_I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _P, _L, _P], _I),
     "gbmm_band_backbackward_f32": ([_P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _P], _I),
+    "gbmm_band_max_eligible": ([_L, _I, _I, _I, _I], _I),
+    "gbmm_band_max_workspace_bytes": ([_L, _L, _I, _I, _I, _I], _L),
+    "gbmm_band_max_workspace_init": ([_P, _L, _P], _I),
+    "gbmm_band_max_forward_f32": ([_P, _I, _I, _P, _I, _I, _P, _P, _L, _L, _P, _L, _P], _I),
     "gbmm_band_tc_eligible": ([_I, _L, _I, _I, _I, _I], _I),
     "gbmm_band_tc_workspace_bytes": ([_I, _L, _L, _I, _I, _I, _I], _L),
     "gbmm_band_tc_workspace_init": ([_P, _L, _P], _I),
@@ -269,6 +273,27 @@ def _band_tc_workspace(mode, backward, B, n, bands, device):
     return ws
 
 
+_band_max_cache = {}
+
+
+def _band_max_workspace(B, n, bands, device):
+    """Cached workspace of the fast max-plus forward (its -inf padding is written once), or None when
+    GENBMM_B200_BAND=block."""
+    if os.environ.get("GENBMM_B200_BAND", "auto") == "block":
+        return None
+    lib = load()
+    key = (B, n) + tuple(bands)
+    dev = device.index if device.index is not None else torch.cuda.current_device()
+    hit = _band_max_cache.get(dev)
+    if hit is not None and hit[0] == key:
+        return hit[1]
+    _band_max_cache.pop(dev, None)
+    ws = torch.empty((lib.gbmm_band_max_workspace_bytes(B, n, *bands),), dtype=torch.uint8, device=device)
+    _check(lib.gbmm_band_max_workspace_init(_ptr(ws), ws.numel(), _stream(device)), "gbmm_band_max_workspace_init")
+    _band_max_cache[dev] = (key, ws)
+    return ws
+
+
 def _band_tc_tag(mode, a, b):
     """Identifies the operand contents a workspace holds: storage address and version counter of both."""
     return (mode, a.data_ptr(), a._version, b.data_ptr(), b._version, torch.cuda.current_stream(a.device).cuda_stream)
@@ -311,6 +336,13 @@ def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode, want_maxes=False):
                                               _ptr(maxes), B, n, _stream(a.device))
             _check(st, "gbmm_band_forward_f64")
             return [out, idx, maxes]
+        if mode == BAND_MAX and load().gbmm_band_max_eligible(n, *bands):
+            mx_ws = _band_max_workspace(B, n, bands, a.device)
+            if mx_ws is not None:
+                st = load().gbmm_band_max_forward_f32(_ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), _ptr(idx),
+                                                      B, n, _ptr(mx_ws), mx_ws.numel(), _stream(a.device))
+                _check(st, "gbmm_band_max_forward_f32")
+                return [out, idx, maxes]
         tc_ws = None
         if maxes is None and load().gbmm_band_tc_eligible(mode, n, *bands):
             tc_ws = _band_tc_workspace(mode, False, B, n, bands, a.device)

@@ -6,8 +6,8 @@ C states": potentials pot:(B, T-1, C, C), the chain product
 
     P[b] = pot[b,0] (x) pot[b,1] (x) ... (x) pot[b,T-2],   (A (x) B)[i,j] = logsumexp_k A[i,k] + B[k,j]
 
-evaluated as a balanced pairwise tree (an unpaired last matrix is carried up a level), so level l
-is one logbmm call with batch B * (T-1) / 2^(l+1); logZ[b] = logsumexp_{i,j} P[b]; the edge
+evaluated as balanced pairwise trees over the power-of-two runs of the chain (level l of a run is one
+logbmm call with batch B * run / 2^(l+1)); logZ[b] = logsumexp_{i,j} P[b]; the edge
 marginals are d(sum_b logZ[b]) / d pot, obtained by autograd through the tree.
 
 `bmm` is the semiring product to use (default: genbmm_b200.logbmm); tests on CPU pass the
@@ -22,20 +22,104 @@ def _default_bmm():
     return logbmm
 
 
+def _bit_reversed(x, k):
+    """x:(2**k, ...) -> the same matrices in bit-reversed order of the first index, as one strided copy
+    (bit reversal = splitting the index into k binary digits and reversing their order).  Its own inverse."""
+    if k <= 1:
+        return x.contiguous()
+    rest = x.shape[1:]
+    y = x.reshape((2,) * k + tuple(rest))
+    y = y.permute(tuple(range(k - 1, -1, -1)) + tuple(range(k, k + len(rest))))
+    return y.reshape((2 ** k,) + tuple(rest)).contiguous()
+
+
+def _runs(L):
+    """(start, length, padded length) of the runs a chain of L matrices is cut into.  When the next power of
+    two is at most an eighth longer than L the chain is one run, padded with identity matrices (which
+    multiply away); otherwise one run per power of two of L's binary expansion, longest first."""
+    n = 1 << max(L - 1, 0).bit_length()
+    if n - L <= L // 8:
+        return [(0, L, n)]
+    out, s = [], 0
+    for bit in range(L.bit_length() - 1, -1, -1):
+        if L & (1 << bit):
+            out.append((s, 1 << bit, 1 << bit))
+            s += 1 << bit
+    return out
+
+
+class _ChainMajor(torch.autograd.Function):
+    """pot (B, L, C, C) -> one tensor per run of the chain (see _runs): (n, B, C, C), n a power of two, with the
+    run's chain positions in bit-reversed order.
+
+    In that order the matrices at even positions are the first half and the ones at odd positions the second
+    half, and the pairwise products come out in the bit-reversed order of their own index, so every level of
+    the tree multiplies the first half by the second half: contiguous views, no copies.  Padding matrices are
+    the semiring's identity (0 on the diagonal, -1e9 elsewhere).  The backward writes every run's gradient
+    into one buffer."""
+
+    @staticmethod
+    def forward(ctx, pot):
+        ctx.shape = pot.shape
+        B, L, C, D = pot.shape
+        out = []
+        for s, m, n in _runs(L):
+            src = pot[:, s:s + m].transpose(0, 1)
+            if n != m:
+                full = torch.empty((n, B, C, D), dtype=pot.dtype, device=pot.device)
+                full[:m].copy_(src)
+                full[m:] = -1e9
+                full[m:].diagonal(dim1=-2, dim2=-1).zero_()
+                src = full
+            out.append(_bit_reversed(src, n.bit_length() - 1))
+        return tuple(out)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        gp = None
+        for (s, m, n), g in zip(_runs(ctx.shape[1]), grads):
+            if gp is None:
+                gp = torch.empty(ctx.shape, dtype=g.dtype, device=g.device)
+            gp[:, s:s + m].copy_(_bit_reversed(g, n.bit_length() - 1)[:m].transpose(0, 1))
+        return gp
+
+
+class _Halves(torch.autograd.Function):
+    """(2p, B, C, C) -> the first and the second half as (p*B, C, C) views; the backward joins the two gradients
+    in one copy (autograd through two slices would zero-fill and add two full-size tensors)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        L, B, C, D = x.shape
+        p = L // 2
+        ctx.shape = (p, B, C, D)
+        return x[:p].view(p * B, C, D), x[p:].view(p * B, C, D)
+
+    @staticmethod
+    def backward(ctx, g_left, g_right):
+        p, B, C, D = ctx.shape
+        return torch.cat((g_left.reshape(p, B, C, D), g_right.reshape(p, B, C, D)), 0)
+
+
 def chain_product(pot, bmm=None):
-    """(B, L, C, C) -> (B, C, C): the log-semiring product of the L matrices of each chain."""
+    """(B, L, C, C) -> (B, C, C): the log-semiring product of the L matrices of each chain.
+
+    The chain is cut into power-of-two runs (_runs); each run is
+    reduced by a balanced pairwise tree (level l is one product with batch B * run / 2^(l+1)) on a
+    chain-major, bit-reversed copy (see _ChainMajor), and the few run products are multiplied in order."""
     bmm = bmm or _default_bmm()
-    x = pot
-    B, _, C, D = x.shape
+    B, L, C, D = pot.shape
     assert C == D, "transition matrices must be square"
-    while x.shape[1] > 1:
-        L = x.shape[1]
-        pairs = L // 2
-        left = x[:, 0:2 * pairs:2].reshape(B * pairs, C, C).contiguous()
-        right = x[:, 1:2 * pairs:2].reshape(B * pairs, C, C).contiguous()
-        y = bmm(left, right).view(B, pairs, C, C)
-        x = torch.cat([y, x[:, L - 1:]], 1) if L % 2 else y
-    return x[:, 0]
+    parts = []
+    for x in _ChainMajor.apply(pot):
+        while x.shape[0] > 1:
+            left, right = _Halves.apply(x)
+            x = bmm(left, right).view(x.shape[0] // 2, B, C, C)
+        parts.append(x[0])
+    out = parts[0]
+    for nxt in parts[1:]:
+        out = bmm(out.contiguous(), nxt.contiguous())
+    return out
 
 
 def log_partition(pot, bmm=None):

@@ -723,6 +723,35 @@ extern "C" int gbmm_band_tc_backward_f32(int mode, const float* a, int a_lu, int
   return exact_backward(mode, a, b, grad_out, part, grad_a, grad_b, d, B, flags, st);
 }
 
+extern "C" int gbmm_band_max_eligible(int64_t n, int a_lu, int a_ld, int b_lu, int b_ld) {
+  if (a_lu < 0 || a_ld < 0 || b_lu < 0 || b_ld < 0 || n < 0) return 0;
+  return band_max_fast_eligible(BandDims{n, a_lu, a_ld, b_lu, b_ld}) ? 1 : 0;
+}
+
+extern "C" int64_t gbmm_band_max_workspace_bytes(int64_t B, int64_t n, int a_lu, int a_ld, int b_lu, int b_ld) {
+  if (B < 0 || n < 0 || a_lu < 0 || a_ld < 0 || b_lu < 0 || b_ld < 0) return -1;
+  return band_max_workspace_bytes(B, BandDims{n, a_lu, a_ld, b_lu, b_ld});
+}
+
+extern "C" int gbmm_band_max_workspace_init(void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!workspace || workspace_bytes < 0 || (reinterpret_cast<uintptr_t>(workspace) & 15)) return GBMM_ERR_INVALID_ARG;
+  return band_max_workspace_init(workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int gbmm_band_max_forward_f32(const float* a, int a_lu, int a_ld, const float* b, int b_lu, int b_ld,
+                                         float* out, int32_t* idx, int64_t B, int64_t n, void* workspace,
+                                         int64_t workspace_bytes, void* stream) {
+  const int st0 = check_band(GBMM_BAND_MAX, B, n, a_lu, a_ld, b_lu, b_ld);
+  if (st0 != GBMM_OK) return st0;
+  if (B == 0 || n == 0) return GBMM_OK;
+  if (!a || !b || !out || !idx || !workspace) return GBMM_ERR_INVALID_ARG;
+  const BandDims d{n, a_lu, a_ld, b_lu, b_ld};
+  if (!band_max_fast_eligible(d)) return GBMM_ERR_UNSUPPORTED;
+  if (workspace_bytes < band_max_workspace_bytes(B, d) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return GBMM_ERR_INVALID_ARG;
+  return band_max_forward(a, b, out, idx, d, B, workspace, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int gbmm_band_backbackward_f32(const float* a, int a_lu, int a_ld, const float* b, int b_lu, int b_ld,
                                           const float* grad_out, const float* part, const float* h_a,
                                           const float* h_b, float* d_a, float* d_b, float* d_grad_out, int64_t B,

@@ -34,4 +34,13 @@ int band_tc_backward(int mode, const float* a, const float* b, const float* g, c
                      float* grad_b, const BandDims& d, int64_t B, void* ws, int operands_ready, int** flags_out,
                      cudaStream_t st);
 
+// Max-plus forward from skewed copies (band_max.cu), bands at least 32 wide.  `ws` holds at least
+// band_max_workspace_bytes and was filled with -inf once (band_max_workspace_init) before its first use with
+// these dimensions; the kernels rewrite the band cells of the copies, never the padding.
+bool band_max_fast_eligible(const BandDims& d);
+int64_t band_max_workspace_bytes(int64_t B, const BandDims& d);
+int band_max_workspace_init(void* ws, int64_t bytes, cudaStream_t st);
+int band_max_forward(const float* a, const float* b, float* out, int* idx, const BandDims& d, int64_t B, void* ws,
+                     cudaStream_t st);
+
 }  // namespace gbmm

@@ -1,0 +1,318 @@
+// Banded max-plus forward (multiply_max) for bands at least 32 wide: the dense max kernel's inner loop
+// (dense_fwd.cu) fed from skewed copies of the band tensors.
+//
+// As in band_tc.cu, X[r,c] = data[r][c-r+lu] is a strided view of band storage once every row is followed
+// by enough padding: rows pitch-1 apart, columns contiguous.  Here the padding (and every out-of-matrix
+// cell) holds -inf, so a term that involves a cell outside either band is -inf and never exceeds the
+// running maximum, which starts at -1e9 like the reference's (banded_cuda_kernel.cu:45-60).
+// A CTA owns a 128 x 64 block of the result that meets the result band and walks the reduction index over
+// the range where both operand bands are populated, 16 steps at a time: (k, k+1) pairs side by side in
+// shared memory, one packed add and one 3-input max per two terms, two alternating sets of running maxima,
+// the first 16-step tile that reached the maximum remembered in a byte.  A block's reduction range is short
+// (at most 63 + Wb or 127 + Wa steps), so all of it is loaded into shared memory up front (one CTA per SM,
+// up to 218 KB); the winning tile of each result is then searched there for the first p whose term equals
+// the maximum, with no second trip to global memory.  Ascending p is ascending index in a's band for a fixed
+// row, so this is the reference's lowest-index tie rule; the stored index is p - i + a_lu.
+#include <algorithm>
+
+#include "band.cuh"
+#include "tile.cuh"
+
+namespace gbmm {
+namespace {
+
+constexpr int BM = 128, BN = 64, BK = 16, NT = 256;
+constexpr int LDX = BM + 4, LDY = BN + 4;
+constexpr int MAX_PAD = 192;  // >= 127 (tile rows) + 2 * 15 (reduction range rounded to tiles of 16)
+
+__device__ __forceinline__ float nan_f() { return __int_as_float(0x7fc00000); }
+__device__ __forceinline__ float ninf_f() { return __int_as_float(0xff800000); }
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+struct MaxSkew {
+  int off, pitch, kofs;
+  int64_t bstride;
+};
+MaxSkew make_max_skew(int lu, int W, int64_t n) {
+  MaxSkew s;
+  s.off = (4 - lu % 4) % 4;  // 128-bit loads along the reduction index: lu + off a multiple of 4
+  s.pitch = s.off + W + MAX_PAD;
+  s.pitch += (1 - s.pitch % 4 + 4) % 4;
+  s.kofs = lu + s.off;
+  s.bstride = (n * s.pitch + 3) & ~int64_t(3);
+  return s;
+}
+int64_t max_skew_floats(const MaxSkew& s, int64_t B) { return (B * s.bstride + 64 + 63) & ~int64_t(63); }
+
+// band rows into the skewed layout; cells outside the matrix become -inf (one warp per row)
+__global__ void __launch_bounds__(256) band_max_skew_kernel(const float* __restrict__ x, float* __restrict__ dst,
+                                                            int64_t rows, int n, int lu, int W, int off, int pitch,
+                                                            int64_t bstride) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const int i = (int)(row % n);
+  const int64_t bt = row / n;
+  const int jlo = max(0, lu - i), jhi = min(W, n - i + lu);
+  float* dr = dst + bt * bstride + (int64_t)i * pitch + off;
+  for (int j = lane; j < W; j += 32) dr[j] = (j >= jlo && j < jhi) ? __ldg(x + row * W + j) : ninf_f();
+}
+
+__global__ void fill_ninf_kernel(float* p, int64_t count) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (int64_t)gridDim.x * blockDim.x)
+    p[e] = ninf_f();
+}
+
+struct MaxArgs {
+  const float* xs;  // skewed a
+  const float* ys;  // skewed b
+  int64_t x_bstride, y_bstride;
+  int x_rstride, y_rstride;  // pitch - 1
+  int x_kofs, y_kofs;
+  int n, a_lu, a_ld, b_lu, b_ld, r_lu, Wo;
+  int nrb, ncb;
+  float* out;
+  int* idx;
+};
+
+// Dynamic shared memory: the operand tiles of the block's whole reduction range (at most kMaxSteps tiles of
+// 16 steps), pair layout: x element (k, m) at ((k/2) * LDX + m) * 2 + (k & 1), y likewise with LDY.
+// Tiles are 4 floats further apart than their size: results of one warp search different tiles, and with a
+// stride that is a multiple of 32 banks all those reads would hit the same bank.
+constexpr int XS = (BK / 2) * LDX * 2 + 4, YS = (BK / 2) * LDY * 2 + 4;  // floats per x / y tile
+constexpr int kMaxSteps = 17;  // 272 reduction steps: 17 * (XS + YS) * 4 bytes = 213 KB
+__host__ __device__ constexpr size_t max_smem_bytes(int steps) { return (size_t)steps * (XS + YS) * sizeof(float); }
+
+__global__ void __launch_bounds__(NT, 1) band_max_kernel(MaxArgs g) {
+  extern __shared__ __align__(16) float smem_dyn[];
+  const Micro8x4 mt;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int64_t id = blockIdx.x;
+  const int cbi = (int)(id % g.ncb), rbk = (int)((id / g.ncb) % g.nrb);
+  const int64_t bt = id / ((int64_t)g.ncb * g.nrb);
+  const int r0 = rbk * BM;
+  const int lo = r0 - g.r_lu;
+  const int cfirst = lo >= 0 ? lo / BN : -((-lo + BN - 1) / BN);
+  const int c0 = (cfirst + cbi) * BN;
+  const int r_ld = g.Wo - 1 - g.r_lu;
+  if (c0 > r0 + BM - 1 + r_ld) return;  // beyond the band: owns no cell
+  const int s_lo = max(max(r0 - g.a_lu, c0 - g.b_lu), 0);
+  int s_hi = min(min(r0 + BM - 1 + g.a_ld, c0 + BN - 1 + g.b_ld), g.n - 1);
+  if (c0 >= g.n || c0 + BN - 1 < 0) s_hi = s_lo - 1;  // outside the matrix: only zeros to write
+  const int s0 = s_lo & ~(BK - 1);
+  const int nt = s_hi >= s_lo ? (s_hi - s0) / BK + 1 : 0;  // <= kMaxSteps by the eligibility rule
+  float* sx = smem_dyn;
+  float* sy = smem_dyn + (size_t)nt * XS;
+
+  const float* xb = g.xs + bt * g.x_bstride + g.x_kofs;
+  const float* yb = g.ys + bt * g.y_bstride + g.y_kofs;
+
+  // Tile loads: 4 consecutive reduction indices per 128-bit load (always aligned: row stride, kofs and the
+  // reduction start are multiples of 4); rows outside the matrix give NaN terms, which the maximum ignores.
+  // Tile t + 1 is fetched into registers while tile t is multiplied and stored behind it; every tile stays
+  // in shared memory for the index search at the end.
+  float4 xa[2], ya;
+  auto fetch = [&](int t) {
+    const int s = s0 + t * BK;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int f = tid + q * NT, o = f / (BK / 4), r = (f % (BK / 4)) * 4;
+      const int i = r0 + o;
+      xa[q] = (i < g.n) ? __ldg(reinterpret_cast<const float4*>(xb + (int64_t)i * g.x_rstride + s + r))
+                        : make_float4(nan_f(), nan_f(), nan_f(), nan_f());
+    }
+    const int o = tid / (BK / 4), r = (tid % (BK / 4)) * 4;
+    const int c = c0 + o;
+    ya = (c >= 0 && c < g.n) ? __ldg(reinterpret_cast<const float4*>(yb + (int64_t)c * g.y_rstride + s + r))
+                             : make_float4(nan_f(), nan_f(), nan_f(), nan_f());
+  };
+  auto stage = [&](int t) {
+    float* dx = sx + (size_t)t * XS;
+    float* dy = sy + (size_t)t * YS;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int f = tid + q * NT, o = f / (BK / 4), r = (f % (BK / 4)) * 4;
+      *reinterpret_cast<float2*>(dx + ((r / 2) * LDX + o) * 2) = make_float2(xa[q].x, xa[q].y);
+      *reinterpret_cast<float2*>(dx + ((r / 2 + 1) * LDX + o) * 2) = make_float2(xa[q].z, xa[q].w);
+    }
+    const int o = tid / (BK / 4), r = (tid % (BK / 4)) * 4;
+    *reinterpret_cast<float2*>(dy + ((r / 2) * LDY + o) * 2) = make_float2(ya.x, ya.y);
+    *reinterpret_cast<float2*>(dy + ((r / 2 + 1) * LDY + o) * 2) = make_float2(ya.z, ya.w);
+  };
+  if (nt > 0) {
+    fetch(0);
+    stage(0);
+  }
+  __syncthreads();
+
+  float X[8][4], Y[8][4];
+  unsigned cidp[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    cidp[i] = 0xffffffffu;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      X[i][j] = kFloor;
+      Y[i][j] = kFloor;
+    }
+  }
+
+  auto tile_step = [&](int t, float (&acc)[8][4], const float (&prev)[8][4]) {
+    const float* tx_ = sx + (size_t)t * XS;
+    const float* ty_ = sy + (size_t)t * YS;
+    if (t + 1 < nt) fetch(t + 1);
+#pragma unroll
+    for (int kp2 = 0; kp2 < BK / 2; ++kp2) {
+      const float* xs = tx_ + (kp2 * LDX + mt.ty * 4) * 2;
+      const float* ys = ty_ + (kp2 * LDY + mt.tx * 4) * 2;
+      const ulonglong2 x01 = *reinterpret_cast<const ulonglong2*>(xs);
+      const ulonglong2 x23 = *reinterpret_cast<const ulonglong2*>(xs + 4);
+      const ulonglong2 x45 = *reinterpret_cast<const ulonglong2*>(xs + 128);
+      const ulonglong2 x67 = *reinterpret_cast<const ulonglong2*>(xs + 132);
+      const ulonglong2 y01 = *reinterpret_cast<const ulonglong2*>(ys);
+      const ulonglong2 y23 = *reinterpret_cast<const ulonglong2*>(ys + 4);
+      const unsigned long long xp[8] = {x01.x, x01.y, x23.x, x23.y, x45.x, x45.y, x67.x, x67.y};
+      const unsigned long long yp[4] = {y01.x, y01.y, y23.x, y23.y};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float v0, v1;
+          unpack2(add2(xp[i], yp[j]), v0, v1);
+          acc[i][j] = max3(kp2 == 0 ? prev[i][j] : acc[i][j], v0, v1);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // strict `>`: an equal maximum in a later tile does not move the index
+      if (acc[i][0] > prev[i][0]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3214);
+      if (acc[i][1] > prev[i][1]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3240);
+      if (acc[i][2] > prev[i][2]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3410);
+      if (acc[i][3] > prev[i][3]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x4210);
+    }
+    if (t + 1 < nt) stage(t + 1);
+    __syncthreads();
+  };
+  int t = 0;
+  for (; t + 1 < nt; t += 2) {
+    tile_step(t, X, Y);
+    tile_step(t + 1, Y, X);
+  }
+  if (t < nt) {
+    tile_step(t, X, Y);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) Y[i][j] = X[i][j];
+  }
+  // from here on Y holds the maxima.  The winning tile of every result is still in shared memory: search it
+  // from the last step down, so the lowest matching p is the assignment that sticks; the stored value is that
+  // term itself (a zero keeps the sign the reference would keep).
+  float* ob = g.out + bt * g.n * (int64_t)g.Wo;
+  int* ib = g.idx + bt * g.n * (int64_t)g.Wo;
+  (void)lane;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int ml = mt.row(i), m = r0 + ml;
+    if (m >= g.n) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int cl = mt.col(j), c = c0 + cl;
+      const int cell = c - m + g.r_lu;
+      if (cell < 0 || cell >= g.Wo) continue;
+      const bool inside = c >= 0 && c < g.n;
+      const unsigned c8 = (cidp[i] >> (8 * j)) & 0xffu;
+      float val = Y[i][j];
+      int p = -1;
+      if (inside && c8 != 0xffu) {
+        const float* tx_ = sx + (size_t)c8 * XS + ml * 2;
+        const float* ty_ = sy + (size_t)c8 * YS + cl * 2;
+#pragma unroll
+        for (int kp2 = BK / 2 - 1; kp2 >= 0; --kp2) {
+          const float2 xv = *reinterpret_cast<const float2*>(tx_ + kp2 * LDX * 2);
+          const float2 yv = *reinterpret_cast<const float2*>(ty_ + kp2 * LDY * 2);
+          const float v1 = __fadd_rn(xv.y, yv.y), v0 = __fadd_rn(xv.x, yv.x);
+          if (v1 == Y[i][j]) {
+            val = v1;
+            p = s0 + (int)c8 * BK + 2 * kp2 + 1;
+          }
+          if (v0 == Y[i][j]) {
+            val = v0;
+            p = s0 + (int)c8 * BK + 2 * kp2;
+          }
+        }
+      }
+      const int64_t e = (int64_t)m * g.Wo + cell;
+      ob[e] = inside ? val : 0.f;  // cells outside the matrix stay zero (banded_cuda_kernel.cu:38)
+      ib[e] = inside ? (p >= 0 ? p - m + g.a_lu : -1) : 0;
+    }
+  }
+}
+
+}  // namespace
+
+// declared in band.cuh
+bool band_max_fast_eligible(const BandDims& d) {
+  // a block's whole reduction range stays in shared memory: at most kMaxSteps tiles of 16 steps
+  const int64_t range = std::min<int64_t>(BM - 1 + d.Wa(), BN - 1 + d.Wb()) + 2 * (BK - 1);
+  return d.Wa() >= 32 && d.Wb() >= 32 && d.n >= 128 && d.n < (1LL << 30) && range <= kMaxSteps * BK;
+}
+
+int64_t band_max_workspace_bytes(int64_t B, const BandDims& d) {
+  const MaxSkew sa = make_max_skew(d.a_lu, d.Wa(), d.n), sb = make_max_skew(d.b_lu, d.Wb(), d.n);
+  return (int64_t)sizeof(float) * (max_skew_floats(sa, B) + max_skew_floats(sb, B));
+}
+
+int band_max_workspace_init(void* ws, int64_t bytes, cudaStream_t st) {
+  fill_ninf_kernel<<<1184, 256, 0, st>>>(static_cast<float*>(ws), bytes / (int64_t)sizeof(float));
+  return launch_status();
+}
+
+int band_max_forward(const float* a, const float* b, float* out, int* idx, const BandDims& d, int64_t B, void* ws,
+                     cudaStream_t st) {
+  const MaxSkew sa = make_max_skew(d.a_lu, d.Wa(), d.n), sb = make_max_skew(d.b_lu, d.Wb(), d.n);
+  float* xs = static_cast<float*>(ws);
+  float* ys = xs + max_skew_floats(sa, B);
+  const int64_t rows = B * d.n, rblocks = ceil_div(rows, 8);
+  if (rblocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  band_max_skew_kernel<<<(unsigned)rblocks, 256, 0, st>>>(a, xs, rows, (int)d.n, d.a_lu, d.Wa(), sa.off, sa.pitch,
+                                                         sa.bstride);
+  band_max_skew_kernel<<<(unsigned)rblocks, 256, 0, st>>>(b, ys, rows, (int)d.n, d.b_lu, d.Wb(), sb.off, sb.pitch,
+                                                         sb.bstride);
+  if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+  MaxArgs g{};
+  g.xs = xs;
+  g.ys = ys;
+  g.x_bstride = sa.bstride;
+  g.y_bstride = sb.bstride;
+  g.x_rstride = sa.pitch - 1;
+  g.y_rstride = sb.pitch - 1;
+  g.x_kofs = sa.kofs;
+  g.y_kofs = sb.kofs;
+  g.n = (int)d.n;
+  g.a_lu = d.a_lu; g.a_ld = d.a_ld; g.b_lu = d.b_lu; g.b_ld = d.b_ld;
+  g.r_lu = d.r_lu();
+  g.Wo = d.Wo();
+  g.nrb = (int)ceil_div(d.n, BM);
+  g.ncb = (g.Wo + BM - 1 + BN - 1) / BN + 1;
+  g.out = out;
+  g.idx = idx;
+  const int64_t blocks = B * g.nrb * g.ncb;
+  if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  const size_t smem = max_smem_bytes(kMaxSteps);
+  if (cudaFuncSetAttribute(band_max_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return GBMM_ERR_LAUNCH;
+  // every block gets the size of the longest range (the sizes differ by block, the launch has one)
+  const int64_t range = std::min<int64_t>(BM - 1 + d.Wa(), BN - 1 + d.Wb()) + 2 * (BK - 1);
+  const int steps = (int)std::min<int64_t>(kMaxSteps, ceil_div(range, BK));
+  band_max_kernel<<<(unsigned)blocks, NT, max_smem_bytes(steps), st>>>(g);
+  return launch_status();
+}
+
+}  // namespace gbmm

@@ -160,6 +160,20 @@ int gbmm_band_tc_backward_f32(int mode, const float* a, int a_lu, int a_ld, cons
                               int operands_ready, void* stream);
 
 /*
+ * Fast max-plus forward (mode 1 of gbmm_band_forward_f32: values and int32 indices in a's band coordinate,
+ * bit-identical to it) for bands at least 32 wide and n >= 128 (gbmm_band_max_eligible).  It works from
+ * skewed copies of the operands kept in the workspace, whose padding holds -inf: fill the workspace ONCE
+ * with gbmm_band_max_workspace_init and afterwards pass it only to this function with the same B, n and
+ * band widths.  Calls sharing a workspace must not overlap on the GPU.
+ */
+int gbmm_band_max_eligible(int64_t n, int a_lu, int a_ld, int b_lu, int b_ld);
+int64_t gbmm_band_max_workspace_bytes(int64_t B, int64_t n, int a_lu, int a_ld, int b_lu, int b_ld);
+int gbmm_band_max_workspace_init(void* workspace, int64_t workspace_bytes, void* stream);
+int gbmm_band_max_forward_f32(const float* a, int a_lu, int a_ld, const float* b, int b_lu, int b_ld,
+                              float* out, int32_t* idx, int64_t B, int64_t n,
+                              void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * Banded log-semiring second-order terms.  Replaces `_genbmm.backbackward_band(a, a_lu, a_lb, b,
  * b_lu, b_lb, grad_output, part, maxes, grad_out_a, 0)` — banded_backbackward,
  * matmul_cuda.cpp:145-161 -> banded_cuda_backbackward, banded_cuda_kernel.cu:453-546 — extended to

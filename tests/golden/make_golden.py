@@ -20,7 +20,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/genbmm-checkout")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 from genbmm.sparse import BandedMatrix, banddiag  # noqa: E402
 

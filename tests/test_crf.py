@@ -15,7 +15,7 @@ def cpu_bmm(a, b):
     return oracle.expr_forward(0, a, b)
 
 
-@pytest.mark.parametrize("B,L,C", [(2, 1, 3), (2, 2, 4), (3, 7, 5), (2, 8, 3), (1, 13, 4)])
+@pytest.mark.parametrize("B,L,C", [(2, 1, 3), (2, 2, 4), (3, 7, 5), (2, 8, 3), (1, 13, 4), (2, 15, 3), (1, 31, 2)])
 def test_tree_equals_sequential_chain_on_cpu(B, L, C):
     from genbmm_b200 import crf
     gen = torch.Generator().manual_seed(B * 100 + L)
