@@ -235,18 +235,21 @@ __global__ void __launch_bounds__(NT, 1) band_max_kernel(MaxArgs g) {
         const float* ty_ = sy + (size_t)c8 * YS + cl * 2;
 #pragma unroll
         for (int kp2 = BK / 2 - 1; kp2 >= 0; --kp2) {
-          const float2 xv = *reinterpret_cast<const float2*>(tx_ + kp2 * LDX * 2);
-          const float2 yv = *reinterpret_cast<const float2*>(ty_ + kp2 * LDY * 2);
-          const float v1 = __fadd_rn(xv.y, yv.y), v0 = __fadd_rn(xv.x, yv.x);
-          if (v1 == Y[i][j]) {
-            val = v1;
-            p = s0 + (int)c8 * BK + 2 * kp2 + 1;
-          }
-          if (v0 == Y[i][j]) {
-            val = v0;
-            p = s0 + (int)c8 * BK + 2 * kp2;
-          }
+          float v0, v1;
+          unpack2(add2(*reinterpret_cast<const unsigned long long*>(tx_ + kp2 * LDX * 2),
+                       *reinterpret_cast<const unsigned long long*>(ty_ + kp2 * LDY * 2)),
+                  v0, v1);
+          if (v1 == Y[i][j]) p = 2 * kp2 + 1;
+          if (v0 == Y[i][j]) p = 2 * kp2;
         }
+        // the stored value is the matching term itself: only for a zero can it differ from the maximum
+        // (in sign), so that is the one case that reads the term again
+        if (val == 0.f && p >= 0) {
+          const float2 xv = *reinterpret_cast<const float2*>(tx_ + (p / 2) * LDX * 2);
+          const float2 yv = *reinterpret_cast<const float2*>(ty_ + (p / 2) * LDY * 2);
+          val = (p & 1) ? __fadd_rn(xv.y, yv.y) : __fadd_rn(xv.x, yv.x);
+        }
+        if (p >= 0) p += s0 + (int)c8 * BK;
       }
       const int64_t e = (int64_t)m * g.Wo + cell;
       ob[e] = inside ? val : 0.f;  // cells outside the matrix stay zero (banded_cuda_kernel.cu:38)
