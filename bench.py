@@ -252,6 +252,13 @@ def main():
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path"
     torch.cuda.set_device(local)
+    # pinned host buffers next to this rank's GPU: with several ranks on one box the end-to-end number is
+    # bound by host memory and PCIe roots, not by the kernels (at N = 1 all host cores stay available to the
+    # CPU baseline leg)
+    near = None
+    if world > 1:
+        from genbmm_b200.host import bind_host_near
+        near = bind_host_near(torch.device("cuda", local))
     dev = torch.device("cuda", local)
     dist = None
     if world > 1:
@@ -387,7 +394,8 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args), "clocks": clocks,
         "e2e": {"value": world * macs_log / t_e2e, "unit": "MAC/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e * 1e3},
+                "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e * 1e3,
+                "host_cores_bound": None if near is None else len(near)},
         "gpu_launches": 11 * args.steps,
         "roofline": {
             "bound": "tensor", "kernel": "tc_pair_gemm_kernel (%s)" % dominant, "achieved": achieved / 1e12,

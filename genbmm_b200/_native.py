@@ -23,6 +23,7 @@ _SIGNATURES = {
     "gbmm_abi_version": ([], _I),
     "gbmm_dense_forward_workspace_bytes": ([_I, _L, _L, _L, _L], _L),
     "gbmm_dense_forward_f32": ([_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _L, _P], _I),
+    "gbmm_dense_sample_pick_f32": ([_P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
     "gbmm_dense_backward_f32": ([_I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
     "gbmm_dense_backbackward_f32": ([_P] * 9 + [_L] * 4 + [_P], _I),
     "gbmm_dense_forward_f64": ([_I, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P], _I),
@@ -124,11 +125,12 @@ MODE_LOG, MODE_MAX, MODE_SAMPLE, MODE_PRODMAX = 0, 1, 2, 3
 BAND_LOG, BAND_MAX, BAND_MUL = 0, 1, 3
 
 
-def forward(a, b, mode, u=None, want_maxes=True):
+def forward(a, b, mode, u=None, want_maxes=True, fast_log=False):
     """`_genbmm.forward(a, b, mode)` -> [out, aux]; aux = maxes (mode 0) or int32 indices.
 
     Mode 2 (sample) takes the uniforms `u`:(B,M,N); when None they are drawn with torch.rand
-    on the device, as the reference does inside its dispatcher (matmul_cuda_kernel.cu:517).
+    on the device, as the reference does inside its dispatcher (matmul_cuda_kernel.cu:517);
+    fast_log=True takes its logsumexp from the factorised tensor-core forward (float32 only).
     """
     dt = _compute_dtype(a)
     _check_input(a, "a", dt)
@@ -157,6 +159,13 @@ def forward(a, b, mode, u=None, want_maxes=True):
             st = load().gbmm_dense_forward_f64(mode, _ptr(a), _ptr(b), _ptr(u) if mode == MODE_SAMPLE else None,
                                                _ptr(out), _ptr(aux), B, M, K, N, _stream(a.device))
             _check(st, "gbmm_dense_forward_f64")
+            return [out, aux]
+        if mode == MODE_SAMPLE and fast_log and K > 0:
+            # the logsumexp from the factorised tensor-core forward, then only the inverse-CDF pass
+            out = logbmm_fast_forward(a, b, tensor_cores=True)[0]
+            st = load().gbmm_dense_sample_pick_f32(_ptr(a), _ptr(b), _ptr(u), _ptr(out), _ptr(aux), B, M, K, N,
+                                                   _stream(a.device))
+            _check(st, "gbmm_dense_sample_pick_f32")
             return [out, aux]
         nbytes = load().gbmm_dense_forward_workspace_bytes(mode, B, M, K, N)
         ws = torch.empty((nbytes,), dtype=torch.uint8, device=a.device) if nbytes > 0 else None

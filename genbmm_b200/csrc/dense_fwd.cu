@@ -590,6 +590,19 @@ int launch_log_fwd_flagged(const float* a, const float* b, float* out, const int
 
 using namespace gbmm;
 
+extern "C" int gbmm_dense_sample_pick_f32(const float* a, const float* b, const float* u, const float* out,
+                                          int32_t* idx, int64_t B, int64_t M, int64_t K, int64_t N, void* stream) {
+  if (B < 0 || M < 0 || K < 0 || N < 0) return GBMM_ERR_INVALID_ARG;
+  if (B == 0 || M == 0 || N == 0) return GBMM_OK;
+  if ((K > 0 && (!a || !b)) || !u || !out || !idx) return GBMM_ERR_INVALID_ARG;
+  if (M >= (1LL << 31) - BM || K >= (1LL << 31) - BK || N >= (1LL << 31) - BN) return GBMM_ERR_UNSUPPORTED;
+  const int64_t tiles_m = ceil_div(M, BM), tiles_n = ceil_div(N, BN), blocks = B * tiles_m * tiles_n;
+  if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  dense_sample_pick_kernel<<<(unsigned)blocks, NT, 0, static_cast<cudaStream_t>(stream)>>>(
+      a, b, u, const_cast<float*>(out), idx, (int)M, (int)K, (int)N, (int)tiles_m, (int)tiles_n);
+  return launch_status();
+}
+
 extern "C" int64_t gbmm_dense_forward_workspace_bytes(int mode, int64_t B, int64_t M, int64_t K, int64_t N) {
   if (B < 0 || M < 0 || K < 0 || N < 0) return -1;
   if (mode != GBMM_MODE_MAX && mode != GBMM_MODE_PRODMAX) return 0;

@@ -112,7 +112,9 @@ class _IndexRouted(torch.autograd.Function):
     @classmethod
     def _forward(cls, ctx, a, b, u=None):
         a32, b32 = _as_f32(a, "a"), _as_f32(b, "b")
-        out, switches = _native.forward(a32, b32, cls.MODE, u)
+        fast = (cls.MODE == _native.MODE_SAMPLE and a32.dtype == torch.float32 and a32.dim() == 3 and b32.dim() == 3
+                and _log_path(a32.shape[1], a32.shape[2], b32.shape[-1]) == "tensor")
+        out, switches = _native.forward(a32, b32, cls.MODE, u, fast_log=fast)
         ctx.save_for_backward(a32, b32, switches)
         ctx.dtypes = (a.dtype, b.dtype)
         return out.to(a.dtype)

@@ -17,6 +17,32 @@ import torch
 from . import _native
 
 
+def bind_host_near(device):
+    """Restrict this process to the CPU cores NVML lists as local to `device` (its NUMA node), so that pinned
+    host buffers allocated afterwards — first touched by this process — sit next to the GPU's PCIe root and
+    ranks on different sockets do not all stream through one.  Reads GPU properties only; changes nothing but
+    this process's own CPU affinity.  Returns the cores chosen, or None when NVML or the affinity call is
+    unavailable, or none of the local cores is allowed to this process."""
+    import os
+    try:
+        import pynvml
+        dev = torch.device(device)
+        props = torch.cuda.get_device_properties(dev)
+        bus_id = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus_id.encode())
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        local = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1}
+        cores = sorted(local & os.sched_getaffinity(0))
+        if not cores:
+            return None
+        os.sched_setaffinity(0, cores)
+        return cores
+    except Exception:
+        return None
+
+
 class HostPipeline:
     def __init__(self, B, M, K, N, chunks=4, device=None, tensor_cores=True):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

@@ -71,6 +71,15 @@ int gbmm_dense_forward_f32(int mode, const float* a, const float* b, const float
                            void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * The second half of mode SAMPLE on its own: given out = logsumexp_k(a + b) from any of the log forward
+ * entry points, draws idx (matmul_cuda_kernel.cu:109-118: fp32 running sum of exp(a + b - out) in ascending
+ * k, strict double inequality against u, default 0).  Lets the caller take the logsumexp from the factorised
+ * / tensor-core forward instead of the exact kernel.
+ */
+int gbmm_dense_sample_pick_f32(const float* a, const float* b, const float* u, const float* out, int32_t* idx,
+                               int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+
+/*
  * Dense backward.  Replaces `_genbmm.backward(a, b, grad_output, part, maxes, mode)`
  * — matmul_backward, matmul_cuda.cpp:79-92 -> matmul_cuda_backward,
  * matmul_cuda_kernel.cu:625-720.  Fills grad_a:(B,M,K) and grad_b:(B,K,N); either
