@@ -288,10 +288,6 @@ int launch_block(const BlockArgs& args0, int64_t B, cudaStream_t st) {
 }  // namespace
 
 // shared with band_tc.cu
-int band_rowmax(const float* x, float* r, int64_t B, int64_t n, int lu, int W, cudaStream_t st) {
-  band_rowmax_kernel<<<(unsigned)ceil_div(B * n, 8), 256, 0, st>>>(x, r, B * n, n, lu, W);
-  return launch_status();
-}
 int band_saved_flags(const float* out, const float* ra, const float* rb, int* flags, int64_t B, int64_t n, int r_lu,
                      int Wo, cudaStream_t st) {
   band_flags_kernel<<<(unsigned)ceil_div(B * n, 8), 256, 0, st>>>(out, ra, rb, flags, B * n, n, r_lu, Wo);
