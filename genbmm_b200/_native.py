@@ -259,14 +259,10 @@ _band_tc_cache = {}
 
 def _band_tc_workspace(mode, backward, B, n, bands, device):
     """The cached workspace for these dimensions on this device, or None when the tensor-core path is not
-    taken.  By default the log semiring goes through it and the ordinary (sum) semiring stays on the FP32
-    block kernels: 3xTF32 sums of signed terms are within 1e-6 of the sum of the terms' magnitudes, but
-    several times further off than an FP32 sum where terms cancel.  GENBMM_B200_BAND=tensor sends the sum
-    semiring through it as well, =block neither; GENBMM_B200_BANDLOG=exact keeps the direct kernels."""
-    choice = os.environ.get("GENBMM_B200_BAND", "auto")
-    if choice == "block" or os.environ.get("GENBMM_B200_BANDLOG") == "exact":
-        return None
-    if mode == BAND_MUL and choice != "tensor":
+    taken (GENBMM_B200_BAND=block keeps the FP32 block kernels, GENBMM_B200_BANDLOG=exact the direct ones).
+    For the ordinary (sum) semiring the 3xTF32 result is about 1.7 times further from the exact sum than the
+    FP32 block kernel's, both a few units in the last place of the sum of the terms' magnitudes."""
+    if os.environ.get("GENBMM_B200_BAND", "auto") == "block" or os.environ.get("GENBMM_B200_BANDLOG") == "exact":
         return None
     lib = load()
     key = (B, n) + tuple(bands)

@@ -21,7 +21,8 @@
 // tiles are enumerated over the 128x128 blocks that meet the result band, each with its own
 // reduction range (where both operand bands are populated); the two operands take separate TMA
 // coordinates; and the epilogue scatters a tile's band cells into band storage (each tile row is a
-// contiguous run of a band row).  Log semiring: factorised like the dense path (row maxima, guard
+// contiguous run of a band row).  A chunk accumulates in a pair of TMEM buffers (hi*hi products in one, the
+// two correction products in the other).  Log semiring: factorised like the dense path (row maxima, guard
 // flags per 64-row block, flagged blocks redone by the exact kernels of band.cu).
 #include "band.cuh"
 #include "tc.cuh"
@@ -335,9 +336,13 @@ __global__ void __launch_bounds__(TNT, 1) band_tc_kernel(const __grid_constant__
         int bt, r0, c0, s0, nt;
         if (!band_tile(g, tile, bt, r0, c0, s0, nt)) continue;
         for (int t = 0; t < nt; ++t, ++it) {
-          const int s = it % TST, buf = gc % TNB;
+          // a chunk accumulates in a pair of TMEM buffers: the hi*hi products in one, the two correction
+          // products (2^-11 of their size) in the other, so the large sum is truncated once per reduction
+          // step of 8 instead of three times
+          const int s = it % TST, buf = gc % (TNB / 2);
           const bool chunk_start = (t % TCH) == 0;
-          if (chunk_start && gc >= TNB && !mbar_wait_bounded(&sm.chunk_empty[buf], ((gc / TNB) - 1) & 1)) {
+          if (chunk_start && gc >= TNB / 2 &&
+              !mbar_wait_bounded(&sm.chunk_empty[buf], ((gc / (TNB / 2)) - 1) & 1)) {
             fail = true;
             break;
           }
@@ -346,7 +351,7 @@ __global__ void __launch_bounds__(TNT, 1) band_tc_kernel(const __grid_constant__
             break;
           }
           tc_fence_after();
-          const uint32_t acc = tmem + (uint32_t)(buf * TN);
+          const uint32_t acc = tmem + (uint32_t)(2 * buf * TN), acc_c = acc + TN;
 #pragma unroll
           for (int kk = 0; kk < TK / 8; ++kk) {
             const int ko = kk * 8 * (int)sizeof(float);
@@ -354,9 +359,10 @@ __global__ void __launch_bounds__(TNT, 1) band_tc_kernel(const __grid_constant__
             const uint64_t al = X_MN ? umma_desc_mn(sm.a_lo[s], kk) : umma_desc(sm.a_lo[s], ko);
             const uint64_t bh = Y_MN ? umma_desc_mn(sm.b_hi[s], kk) : umma_desc(sm.b_hi[s], ko);
             const uint64_t bl = Y_MN ? umma_desc_mn(sm.b_lo[s], kk) : umma_desc(sm.b_lo[s], ko);
-            umma_tf32(acc, al, bh, idesc, (!chunk_start || kk > 0) ? 1u : 0u);
-            umma_tf32(acc, ah, bl, idesc, 1u);
-            umma_tf32(acc, ah, bh, idesc, 1u);
+            const uint32_t more = (!chunk_start || kk > 0) ? 1u : 0u;
+            umma_tf32(acc_c, al, bh, idesc, more);
+            umma_tf32(acc_c, ah, bl, idesc, 1u);
+            umma_tf32(acc, ah, bh, idesc, more);
           }
           umma_commit(&sm.empty[s]);
           if ((t % TCH) == TCH - 1 || t == nt - 1) {
@@ -380,18 +386,20 @@ __global__ void __launch_bounds__(TNT, 1) band_tc_kernel(const __grid_constant__
 #pragma unroll
       for (int q = 0; q < TEC; ++q) sum[q] = 0.f;
       for (int chunk = 0; chunk < nchunks; ++chunk, ++gc) {
-        const int buf = gc % TNB;
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.chunk_full[buf], (gc / TNB) & 1))) {
+        const int buf = gc % (TNB / 2);
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.chunk_full[buf], (gc / (TNB / 2)) & 1))) {
           fail = true;
           break;
         }
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < TEC / 32; ++c) {
-          float v[32];
-          tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * TN + cbase + c * 32), v);
+          float v[32], w[32];
+          const uint32_t col = (uint32_t)(2 * buf * TN + cbase + c * 32);
+          tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + col, v);
+          tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + col + TN, w);
 #pragma unroll
-          for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q];
+          for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q] + w[q];
         }
         tc_fence_before();
         __syncwarp();

@@ -67,10 +67,12 @@ def test_band_products_match_oracle(gb, case, method, mode):
 
 
 @pytest.mark.parametrize("case", [c for c in CASES if c[1] >= 128 and min(c[2] + c[3], c[4] + c[5]) >= 31])
-def test_sum_semiring_on_tensor_cores(gb, case, monkeypatch):
-    """GENBMM_B200_BAND=tensor: the ordinary product and its gradients as 3xTF32 (opt-in; the default for the
-    sum semiring is the FP32 block kernel).  Bound: 1e-6 of the sum of the terms' magnitudes."""
-    monkeypatch.setenv("GENBMM_B200_BAND", "tensor")
+@pytest.mark.parametrize("path", ["auto", "block"])
+def test_sum_semiring_both_paths(gb, case, monkeypatch, path):
+    """The ordinary product and its gradients as 3xTF32 on the tensor cores (default for wide bands) and on the
+    FP32 block kernels (GENBMM_B200_BAND=block), with signed cotangents.  Bound: 1e-6 of the sum of the terms'
+    magnitudes."""
+    monkeypatch.setenv("GENBMM_B200_BAND", path)
     B, n, alu, ald, blu, bld = case
     gen = torch.Generator().manual_seed(sum(case))
     a = torch.randn(B, n, alu + ald + 1, generator=gen)
@@ -132,9 +134,14 @@ def test_config5_full_size(gb):
             assert_equal_bits(ga[:1], dA)
             assert_equal_bits(gb_[:1], dB)
         else:
-            assert_close(out[:1], wout, 1e-5, 2e-5)
-            assert_close(ga[:1], dA, 1e-5, 2e-5)
-            assert_close(gb_[:1], dB, 1e-5, 2e-5)
+            bound = (None, None, None)
+            if mode == 3:  # signed terms: see assert_close
+                t_out, _, _, t_dA, t_dB = oracle.band_fwd_bwd(3, a[:1].abs(), lu, ld, b[:1].abs(), lu, ld, g[:1].abs(),
+                                                              dtype=np.float64)
+                bound = (t_out, t_dA, t_dB)
+            assert_close(out[:1], wout, 1e-5, 2e-5, term_sum=bound[0])
+            assert_close(ga[:1], dA, 1e-5, 2e-5, term_sum=bound[1])
+            assert_close(gb_[:1], dB, 1e-5, 2e-5, term_sum=bound[2])
     # linearity of the ordinary product at full size
     out1 = _native.forward_band(ad, lu, ld, bd, lu, ld, 3)[0]
     out2 = _native.forward_band(2 * ad, lu, ld, bd, lu, ld, 3)[0]
