@@ -227,24 +227,29 @@ __device__ __forceinline__ void store_band(const float (&sum)[TEC], float* blk, 
     const bool inside = c >= 0 && c < g.n;
     float cshift = 0.f;
     if (EPI == E_LOG && inside) cshift = __ldg(g.rb + (int64_t)bt * g.n + c);
-    // cell of (row0 + rr, c) = c - row0 - rr + lu_out: valid rr in [rr_lo, rr_hi)
+    // cell of (row0 + rr, c) = c - row0 - rr + lu_out: valid rr in [rr_lo, rr_hi); consecutive rows of this
+    // lane's column are w_out - 1 elements apart in band storage
     const int top = c - row0 + g.lu_out;  // cell at rr = 0
     const int rr_lo = max(0, top - (g.w_out - 1)), rr_hi = min(rows, top + 1);
-#pragma unroll
+    float* op = ob + (int64_t)row0 * g.w_out + top;
+    const int step = g.w_out - 1;
+    // (not fully unrolled: 64 copies of this body do not fit the instruction cache)
+#pragma unroll 4
     for (int rr = 0; rr < 32; ++rr) {
       const float rs = EPI == E_LOG ? __shfl_sync(0xffffffffu, rshift, rr) : 0.f;
-      if (rr < rr_lo || rr >= rr_hi) continue;
-      const float v = blk[rr * 33 + lane];
-      float o = 0.f;
-      if (inside) {
-        if (EPI == E_SUM) o = v;
-        if (EPI == E_LOG) {
-          const float sh = rs + cshift;
-          bad |= !(v >= kTiny) || !(v <= 3.0e38f) || (sh < kFloor);
-          o = __logf(v) + sh;
+      if (rr >= rr_lo && rr < rr_hi) {
+        const float v = blk[rr * 33 + lane];
+        float o = 0.f;
+        if (inside) {
+          if (EPI == E_SUM) o = v;
+          if (EPI == E_LOG) {
+            const float sh = rs + cshift;
+            bad |= !(v >= kTiny) || !(v <= 3.0e38f) || (sh < kFloor);
+            o = __logf(v) + sh;
+          }
         }
+        op[rr * step] = o;  // cells outside the matrix stay zero (banded_cuda_kernel.cu:38)
       }
-      ob[(int64_t)(row0 + rr) * g.w_out + (top - rr)] = o;  // cells outside the matrix stay zero
     }
   }
 }
