@@ -54,6 +54,7 @@ _SIGNATURES = {
     "gbmm_logbmm_forward_noalloc_max_bytes": ([], _L),
     "gbmm_logbmm_forward_noalloc_need_bytes": ([_L, _L, _L, _L], _L),
     "gbmm_logbmm_forward_noalloc_f32": ([_P, _P, _P, _L, _L, _L, _L, _P], _I),
+    "gbmm_gather_blocks_f32": ([_P, _P, _P, _L, _L, _I, _P], _I),
     "gbmm_profile_enable": ([_I], None),
     "gbmm_profile_last_ms": ([_I], ctypes.c_float),
 }
@@ -514,3 +515,18 @@ def backbackward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, maxes, gr
                                                B, n, _stream(a.device))
     _check(st, "gbmm_band_backbackward_f32")
     return [d_a, d_b, d_g]
+
+
+def gather_blocks(src, index, elems, side=0):
+    """dst block d <- src block index[d] (blocks of `elems` contiguous floats); index[d] < 0 gives the log
+    semiring's identity matrix of side `side`.  `src` float32 contiguous on the GPU, `index` int64 on it."""
+    _check_input(src, "src")
+    _check_input(index, "index", torch.int64)
+    if src.numel() % elems or elems % 4:
+        raise RuntimeError("src must consist of whole blocks of a multiple of 4 elements")
+    with torch.cuda.device(src.device):
+        dst = torch.empty((index.numel(), elems), dtype=src.dtype, device=src.device)
+        st = load().gbmm_gather_blocks_f32(_ptr(src), _ptr(dst), _ptr(index), index.numel(), elems, side,
+                                           _stream(src.device))
+    _check(st, "gbmm_gather_blocks_f32")
+    return dst

@@ -62,8 +62,17 @@ class _ChainMajor(torch.autograd.Function):
     def forward(ctx, pot):
         ctx.shape = pot.shape
         B, L, C, D = pot.shape
+        runs = _runs(L)
+        ctx.maps = None
+        if pot.is_cuda and pot.dtype == torch.float32 and pot.is_contiguous() and len(runs) == 1 and (C * D) % 4 == 0:
+            # one pass of the library's block gather instead of torch's strided copies
+            from . import _native
+            n = runs[0][2]
+            fwd, bwd = _chain_maps(B, L, n, pot.device)
+            ctx.maps = bwd
+            return (_native.gather_blocks(pot, fwd, C * D, side=C).view(n, B, C, D),)
         out = []
-        for s, m, n in _runs(L):
+        for s, m, n in runs:
             src = pot[:, s:s + m].transpose(0, 1)
             if n != m:
                 full = torch.empty((n, B, C, D), dtype=pot.dtype, device=pot.device)
@@ -76,12 +85,39 @@ class _ChainMajor(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
+        if ctx.maps is not None:
+            from . import _native
+            B, L, C, D = ctx.shape
+            return _native.gather_blocks(grads[0].contiguous(), ctx.maps, C * D).view(ctx.shape)
         gp = None
         for (s, m, n), g in zip(_runs(ctx.shape[1]), grads):
             if gp is None:
                 gp = torch.empty(ctx.shape, dtype=g.dtype, device=g.device)
             gp[:, s:s + m].copy_(_bit_reversed(g, n.bit_length() - 1)[:m].transpose(0, 1))
         return gp
+
+
+_map_cache = {}
+
+
+def _chain_maps(B, L, n, device):
+    """Block indices for the chain-major bit-reversed layout of one run of L matrices padded to n = 2**k:
+    forward[r * B + b] = b * L + bitrev(r), or -1 where bitrev(r) >= L (an identity pad);
+    backward[b * L + c] = bitrev(c) * B + b."""
+    key = (B, L, n, str(device))
+    if key not in _map_cache:
+        k = n.bit_length() - 1
+        r = torch.arange(n, device=device)
+        rev = torch.zeros_like(r)
+        for bit in range(k):
+            rev |= ((r >> bit) & 1) << (k - 1 - bit)
+        b = torch.arange(B, device=device)
+        fwd = torch.where(rev[:, None] < L, b[None, :] * L + rev[:, None], torch.full((), -1, device=device))
+        bwd = rev[None, :L] * B + b[:, None]
+        if len(_map_cache) > 8:
+            _map_cache.clear()
+        _map_cache[key] = (fwd.reshape(-1).contiguous(), bwd.reshape(-1).contiguous())
+    return _map_cache[key]
 
 
 class _Halves(torch.autograd.Function):

@@ -53,3 +53,48 @@ extern "C" float gbmm_profile_last_ms(int which) {
   if (cudaEventElapsedTime(&ms, g_events[which][0], g_events[which][1]) != cudaSuccess) return -1.f;
   return ms;
 }
+
+// ---- block gather: the chain driver's layout changes ---------------------------------------------
+namespace gbmm {
+namespace {
+// dst block d <- src block map[d] (a block = `elems` contiguous floats, elems % 4 == 0, both 16-byte
+// aligned); map[d] < 0 fills the block with the log semiring's identity matrix (0 on the diagonal of a
+// side x side block, -1e9 elsewhere).  One CTA per (block, 16 KB slice).
+__global__ void __launch_bounds__(256) gather_blocks_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                            const int64_t* __restrict__ map, int64_t elems, int side,
+                                                            int slices) {
+  const int64_t d = blockIdx.x / slices;
+  const int sl = blockIdx.x % slices;
+  const int64_t m = map[d];
+  const int64_t lo = (int64_t)sl * 4096, hi = min(elems, lo + 4096);
+  float4* dp = reinterpret_cast<float4*>(dst + d * elems);
+  if (m >= 0) {
+    const float4* sp = reinterpret_cast<const float4*>(src + m * elems);
+    for (int64_t e = lo / 4 + threadIdx.x; e < hi / 4; e += 256) dp[e] = __ldg(sp + e);
+  } else {
+    for (int64_t e = lo / 4 + threadIdx.x; e < hi / 4; e += 256) {
+      float v[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int64_t f = 4 * e + q;
+        v[q] = (side > 0 && f / side == f % side) ? 0.f : -1e9f;
+      }
+      dp[e] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  }
+}
+}  // namespace
+}  // namespace gbmm
+
+extern "C" int gbmm_gather_blocks_f32(const float* src, float* dst, const int64_t* map, int64_t blocks, int64_t elems,
+                                      int side, void* stream) {
+  if (blocks < 0 || elems < 0 || (elems & 3)) return GBMM_ERR_INVALID_ARG;
+  if (blocks == 0 || elems == 0) return GBMM_OK;
+  if (!src || !dst || !map || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
+    return GBMM_ERR_INVALID_ARG;
+  const int64_t slices = (elems + 4095) / 4096;
+  if (blocks * slices >= (1LL << 31) || slices >= (1LL << 30)) return GBMM_ERR_UNSUPPORTED;
+  gbmm::gather_blocks_kernel<<<(unsigned)(blocks * slices), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, dst, map, elems, side, (int)slices);
+  return gbmm::launch_status();
+}

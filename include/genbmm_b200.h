@@ -294,6 +294,16 @@ int64_t gbmm_logbmm_forward_noalloc_need_bytes(int64_t B, int64_t M, int64_t K, 
 int gbmm_logbmm_forward_noalloc_f32(const float* a, const float* b, float* out,
                                     int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
 
+/*
+ * Layout helper of the chain (CRF) driver, no counterpart in the reference: dst block d <- src block map[d],
+ * a block being `elems` contiguous floats (elems % 4 == 0, both pointers 16-byte aligned, map on the device);
+ * map[d] < 0 fills block d with the log semiring's identity matrix of side `side` (0 on the diagonal, -1e9
+ * elsewhere).  Used to put a chain of C x C matrices into the chain-major, bit-reversed order in which every
+ * level of the pairwise tree multiplies the first half of the buffer by the second, and to undo it.
+ */
+int gbmm_gather_blocks_f32(const float* src, float* dst, const int64_t* map, int64_t blocks, int64_t elems,
+                           int side, void* stream);
+
 /* Diagnostic timing of the fast path's product kernels (no counterpart in the reference).
  * While enabled, each gbmm_logbmm_* call brackets its product launch with CUDA events on its
  * stream; gbmm_profile_last_ms(which) waits for the latest bracket (which = 0 forward product,
