@@ -234,6 +234,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=32, help="1024^3 problems per GPU per step")
+    ap.add_argument("--e2e-chunks", type=int, default=16, help="batch chunks of the host pipeline (end-to-end leg)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the side measurements of configs 1-5")
     args = ap.parse_args()
@@ -319,7 +320,7 @@ def main():
     # genbmm_b200.host.HostPipeline: the package's call for host-resident operands; it overlaps the
     # two PCIe directions with the kernels by cutting the batch into chunks on three streams
     from genbmm_b200.host import HostPipeline
-    pipe = HostPipeline(B, SIZE, SIZE, SIZE, chunks=8, device=dev)
+    pipe = HostPipeline(B, SIZE, SIZE, SIZE, chunks=args.e2e_chunks, device=dev)
 
     def step_e2e():
         return pipe.step(a_h, b_h, ga_h, gb_h)
