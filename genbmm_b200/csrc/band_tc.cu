@@ -49,9 +49,9 @@ int64_t skew_floats(const Skew& s, int64_t B) { return pad64(B * s.bstride + 64)
 
 // One warp per band row.  KIND 0: v = x.  KIND 1: v = exp(x - m), m = the row's maximum over its in-matrix
 // cells (0 when there is none), also written to ra_out[row].  KIND 2: v = g * exp(ra[row] + rb[col] - x), x
-// the saved output, 0 in flagged 64-row blocks.  Cells outside the matrix become 0.  Rows of up to 256
+// the saved output, 0 in flagged 64-row blocks.  Cells outside the matrix become 0.  Rows of up to 32 * NV
 // cells are held in registers (all loads of a row in flight at once); wider rows are walked twice.
-template <int KIND>
+template <int KIND, int NV>
 __global__ void __launch_bounds__(256) band_skew_kernel(const float* __restrict__ x, const float* __restrict__ g,
                                                         const float* __restrict__ ra, const float* __restrict__ rb,
                                                         const int* __restrict__ flags, float* __restrict__ ra_out,
@@ -75,7 +75,6 @@ __global__ void __launch_bounds__(256) band_skew_kernel(const float* __restrict_
     shift = __ldg(ra + row);
     dead = __ldg(flags + bt * ((n + 63) / 64) + i / 64) != 0;
   }
-  constexpr int NV = 8;
   if (W <= 32 * NV) {
     float xv[NV], gv[NV], cv[NV];
 #pragma unroll
@@ -138,8 +137,12 @@ int launch_skew(const float* x, const float* g, const float* ra, const float* rb
                 float* hi, float* lo, int64_t B, int64_t n, int lu, int W, const Skew& s, cudaStream_t st) {
   const int64_t rows = B * n, blocks = ceil_div(rows, 8);
   if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
-  band_skew_kernel<KIND><<<(unsigned)blocks, 256, 0, st>>>(x, g, ra, rb, flags, ra_out, hi, lo, rows, (int)n, lu, W,
-                                                          s.off, s.pitch, s.bstride);
+  if (W <= 256)
+    band_skew_kernel<KIND, 8><<<(unsigned)blocks, 256, 0, st>>>(x, g, ra, rb, flags, ra_out, hi, lo, rows, (int)n, lu,
+                                                               W, s.off, s.pitch, s.bstride);
+  else
+    band_skew_kernel<KIND, 16><<<(unsigned)blocks, 256, 0, st>>>(x, g, ra, rb, flags, ra_out, hi, lo, rows, (int)n, lu,
+                                                                W, s.off, s.pitch, s.bstride);
   return launch_status();
 }
 
