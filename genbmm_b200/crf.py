@@ -137,20 +137,62 @@ class _Halves(torch.autograd.Function):
         return torch.cat((g_left.reshape(p, B, C, D), g_right.reshape(p, B, C, D)), 0)
 
 
+class _PairLevel(torch.autograd.Function):
+    """One level of the tree on the GPU: x (2p, B, C, C) -> (p, B, C, C), first half (x) second half, through the
+    factorised tensor-core logbmm.  The backward hands the two halves of one gradient buffer to the kernels as
+    their outputs, so nothing is joined or copied.  First-order only."""
+
+    @staticmethod
+    def forward(ctx, x):
+        from . import _native
+        L, B, C, D = x.shape
+        p = L // 2
+        left, right = x[:p].view(p * B, C, D), x[p:].view(p * B, C, D)
+        out, rowmax, colmax, flags, factors = _native.logbmm_fast_forward(left, right, tensor_cores=True,
+                                                                          keep_factors=True)
+        ctx.save_for_backward(x, out, rowmax, colmax, flags, factors)
+        return out.view(p, B, C, D)
+
+    @staticmethod
+    def backward(ctx, g):
+        from . import _native
+        x, out, rowmax, colmax, flags, factors = ctx.saved_tensors
+        L, B, C, D = x.shape
+        p = L // 2
+        gx = torch.empty_like(x)
+        _native.logbmm_fast_backward(x[:p].view(p * B, C, D), x[p:].view(p * B, C, D),
+                                     g.contiguous().view(p * B, C, D), out, rowmax, colmax, flags, tensor_cores=True,
+                                     out_grads=(gx[:p].view(p * B, C, D), gx[p:].view(p * B, C, D)), factors=factors)
+        return gx
+
+
+def _fused_levels(x, bmm):
+    """The GPU fast path applies to float32 CUDA chains reduced with the default product, at sizes the
+    tensor-core logbmm takes anyway."""
+    if bmm is not None or not x.is_cuda or x.dtype != torch.float32:
+        return False
+    from .genmul import _log_path
+    return _log_path(x.shape[2], x.shape[3], x.shape[3]) == "tensor"
+
+
 def chain_product(pot, bmm=None):
     """(B, L, C, C) -> (B, C, C): the log-semiring product of the L matrices of each chain.
 
     The chain is cut into power-of-two runs (_runs); each run is
     reduced by a balanced pairwise tree (level l is one product with batch B * run / 2^(l+1)) on a
     chain-major, bit-reversed copy (see _ChainMajor), and the few run products are multiplied in order."""
+    fused = _fused_levels(pot, bmm)
     bmm = bmm or _default_bmm()
     B, L, C, D = pot.shape
     assert C == D, "transition matrices must be square"
     parts = []
     for x in _ChainMajor.apply(pot):
         while x.shape[0] > 1:
-            left, right = _Halves.apply(x)
-            x = bmm(left, right).view(x.shape[0] // 2, B, C, C)
+            if fused:
+                x = _PairLevel.apply(x)
+            else:
+                left, right = _Halves.apply(x)
+                x = bmm(left, right).view(x.shape[0] // 2, B, C, C)
         parts.append(x[0])
     out = parts[0]
     for nxt in parts[1:]:
