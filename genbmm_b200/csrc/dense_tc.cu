@@ -631,13 +631,15 @@ int launch_tc(const TcOperand& A, const TcOperand& Bo, const TcEpi& ep, int64_t 
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
     return GBMM_ERR_DEVICE;
   const size_t smem = sizeof(TcSmem) + 1024;
-  // 256x256 tiles on CTA pairs once the result is larger than one 128-row or 128-column tile
-  // (GENBMM_B200_TC_PAIR=0 keeps the single-CTA kernel)
+  // 256x256 tiles on CTA pairs for long reductions over large results: a short reduction leaves a pair tile's
+  // epilogue (twice the columns per warp, two TMEM buffers) too little main loop to hide behind, and the
+  // single-CTA kernel with its four buffers is faster (measured crossover: 512 steps x 1024 rows).
+  // GENBMM_B200_TC_PAIR=0 keeps the single-CTA kernel everywhere.
   static const bool pair_ok = [] {
     const char* e = getenv("GENBMM_B200_TC_PAIR");
     return !(e && e[0] == '0');
   }();
-  if (pair_ok && I > TM && J > TN && sms >= 2) {
+  if (pair_ok && I > TM && J > TN && sms >= 2 && R * (I < J ? I : J) >= 512 * 1024) {
     const int64_t ti = ceil_div(I, 2 * TM), tj = ceil_div(J, PN), tiles = B * ti * tj;
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
     if (cudaFuncSetAttribute(tc_pair_gemm_kernel<EPI, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
