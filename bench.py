@@ -397,7 +397,7 @@ def main():
         "e2e": {"value": world * macs_log / t_e2e, "unit": "MAC/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": t_e2e * 1e3,
                 "host_cores_bound": None if near is None else len(near)},
-        "gpu_launches": 11 * args.steps,
+        "gpu_launches": 9 * args.steps,
         "roofline": {
             "bound": "tensor", "kernel": "tc_pair_gemm_kernel (%s)" % dominant, "achieved": achieved / 1e12,
             "peak": tf32_peak / 1e12, "unit": "TFLOP/s", "frac": achieved / tf32_peak, "traffic": traffic,

@@ -19,4 +19,6 @@ int launch_log_bwd_flagged(const float* a, const float* b, const float* c, const
 int launch_rowcol_max(const float* a, const float* b, float* rowmax, float* colmax, int64_t B, int64_t M, int64_t K,
                       int64_t N, cudaStream_t st);
 
+int rowmax_only(const float* a, float* rowmax, int64_t B, int64_t M, int64_t K, cudaStream_t st);
+
 }  // namespace gbmm

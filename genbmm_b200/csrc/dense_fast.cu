@@ -414,6 +414,11 @@ bool big_dims(int64_t M, int64_t K, int64_t N) {
 using namespace gbmm;
 
 namespace gbmm {
+int rowmax_only(const float* a, float* rowmax, int64_t B, int64_t M, int64_t K, cudaStream_t st) {
+  rowmax_kernel<<<(unsigned)ceil_div(B * M, 8), 256, 0, st>>>(a, rowmax, B * M, (int)K);
+  return launch_status();
+}
+
 // rowmax:(B,M) = max_k a, colmax:(B,N) = max_k b (0 for rows/columns without a finite entry)
 int launch_rowcol_max(const float* a, const float* b, float* rowmax, float* colmax, int64_t B, int64_t M, int64_t K,
                       int64_t N, cudaStream_t st) {

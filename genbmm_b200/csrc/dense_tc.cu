@@ -582,6 +582,85 @@ int launch_split(const float* src, const float* shift, const float* shift2, cons
   return launch_status();
 }
 
+// Fused operand preparation of the forward: the maximum and the exponentiated, split operand in one pass.
+// rowsplit: one warp per row of a (rows of up to 128 * NV floats held in registers): ra = row maximum (0 for
+// a row without a finite-or-+inf entry, like rowmax_kernel), EA = exp(a - ra) as hi + lo.
+template <int NV>
+__global__ void __launch_bounds__(256) rowsplit_kernel(const float* __restrict__ src, float* __restrict__ rowmax,
+                                                       float* __restrict__ hi_out, float* __restrict__ lo_out,
+                                                       int64_t rows, int C, int64_t pitch) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const float4* sp = reinterpret_cast<const float4*>(src + row * C);
+  const int groups = C / 4;  // C % 4 == 0 on this path
+  float4 x[NV];
+  float m = __int_as_float(0xff800000);
+#pragma unroll
+  for (int q = 0; q < NV; ++q) {
+    const int gq = lane + 32 * q;
+    if (gq < groups) {
+      x[q] = __ldg(sp + gq);
+      m = fmaxf(fmaxf(m, fmaxf(x[q].x, x[q].y)), fmaxf(x[q].z, x[q].w));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const float sh = (m == __int_as_float(0xff800000)) ? 0.f : m;
+  if (lane == 0) rowmax[row] = sh;
+  float4* hp = reinterpret_cast<float4*>(hi_out + row * pitch);
+  float4* lp = reinterpret_cast<float4*>(lo_out + row * pitch);
+#pragma unroll
+  for (int q = 0; q < NV; ++q) {
+    const int gq = lane + 32 * q;
+    if (gq < groups) {
+      const float v[4] = {exp_sfu(x[q].x - sh), exp_sfu(x[q].y - sh), exp_sfu(x[q].z - sh), exp_sfu(x[q].w - sh)};
+      float h[4], l[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        h[k] = tf32_round(v[k]);
+        l[k] = v[k] - h[k];
+      }
+      hp[gq] = make_float4(h[0], h[1], h[2], h[3]);
+      lp[gq] = make_float4(l[0], l[1], l[2], l[3]);
+    }
+  }
+}
+
+// colsplit: one CTA per (batch element, 32 columns of b), 32 columns x 8 row slices: first the column maxima
+// (rb, 0 for a column without a finite-or-+inf entry, like colmax_kernel), then the same elements again — from
+// L1 / L2 — as EB = exp(b - rb), hi + lo.
+__global__ void __launch_bounds__(256) colsplit_kernel(const float* __restrict__ src, float* __restrict__ colmax,
+                                                       float* __restrict__ hi_out, float* __restrict__ lo_out, int R,
+                                                       int C, int64_t pitch, int tiles_c) {
+  __shared__ float part[8][33];
+  const int lane = threadIdx.x % 32, slice = threadIdx.x / 32;
+  const int64_t bt = blockIdx.x / tiles_c;
+  const int c = (blockIdx.x % tiles_c) * 32 + lane;
+  const float* sp = src + bt * R * C + c;
+  float m = __int_as_float(0xff800000);
+  if (c < C) {
+#pragma unroll 4
+    for (int r = slice; r < R; r += 8) m = fmaxf(m, __ldg(sp + (int64_t)r * C));
+  }
+  part[slice][lane] = m;
+  __syncthreads();
+#pragma unroll
+  for (int s2 = 0; s2 < 8; ++s2) m = fmaxf(m, part[s2][lane]);
+  const float sh = (m == __int_as_float(0xff800000)) ? 0.f : m;
+  if (c >= C) return;
+  if (slice == 0) colmax[bt * C + c] = sh;
+  float* hp = hi_out + bt * R * pitch + c;
+  float* lp = lo_out + bt * R * pitch + c;
+#pragma unroll 4
+  for (int r = slice; r < R; r += 8) {
+    const float v = exp_sfu(__ldg(sp + (int64_t)r * C) - sh);
+    const float h = tf32_round(v);
+    hp[(int64_t)r * pitch] = h;
+    lp[(int64_t)r * pitch] = v - h;
+  }
+}
+
 // Tensor map over a (batch, rows, cols) fp32 array with rows `pitch` (a multiple of 32) apart, 128-byte
 // swizzle (16-byte atoms for !MN, 32-byte atoms for MN).  !MN: the columns are the reduction index; boxes of 128 rows x 32 columns.  MN: the rows are
 // the reduction index; dimensions (col % 32, row, col / 32, batch), boxes of 32 x 32 rows x 4 blocks.
@@ -685,6 +764,26 @@ Factors carve_factors(float*& cur, int64_t B, int64_t M, int64_t K, int64_t N) {
   f.eb_lo = carve(cur, B * K * pad32(N));
   return f;
 }
+// forward: maxima and split operands together (one read of a and of b from HBM each)
+int build_factors_with_maxima(const float* a, const float* b, float* rowmax, float* colmax, const Factors& f, int64_t B,
+                              int64_t M, int64_t K, int64_t N, cudaStream_t st) {
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  int rc = GBMM_OK;
+  const int64_t rblocks = ceil_div(B * M, 8);
+  if (K % 4 == 0 && K <= 1024 && al16(a) && rblocks < (1LL << 31)) {
+    rowsplit_kernel<8><<<(unsigned)rblocks, 256, 0, st>>>(a, rowmax, f.ea_hi, f.ea_lo, B * M, (int)K, pad32(K));
+    rc = launch_status();
+  } else {
+    rowmax_only(a, rowmax, B, M, K, st);
+    rc = launch_split<0>(a, rowmax, nullptr, nullptr, nullptr, f.ea_hi, f.ea_lo, B, M, K, st);
+  }
+  if (rc != GBMM_OK) return rc;
+  const int64_t tn = ceil_div(N, 32);
+  if (B * tn >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  colsplit_kernel<<<(unsigned)(B * tn), 256, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, (int)K, (int)N, pad32(N), (int)tn);
+  return launch_status();
+}
+
 int build_factors(const float* a, const float* b, const float* rowmax, const float* colmax, const Factors& f,
                   int64_t B, int64_t M, int64_t K, int64_t N, cudaStream_t st) {
   int rc = launch_split<0>(a, rowmax, nullptr, nullptr, nullptr, f.ea_hi, f.ea_lo, B, M, K, st);
@@ -720,9 +819,7 @@ extern "C" int gbmm_logbmm_tc_forward_f32(const float* a, const float* b, float*
   int* error = reinterpret_cast<int*>(carve(cur, 64));
   const Factors f = carve_factors(cur, B, M, K, N);
   if (cudaMemsetAsync(error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
-  int rc = launch_rowcol_max(a, b, rowmax, colmax, B, M, K, N, st);
-  if (rc != GBMM_OK) return rc;
-  rc = build_factors(a, b, rowmax, colmax, f, B, M, K, N, st);
+  int rc = build_factors_with_maxima(a, b, rowmax, colmax, f, B, M, K, N, st);
   if (rc != GBMM_OK) return rc;
   if (cudaMemsetAsync(flags, 0, sizeof(int) * B * ceil_div(M, TM) * ceil_div(N, TN), st) != cudaSuccess)
     return GBMM_ERR_LAUNCH;
