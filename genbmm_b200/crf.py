@@ -213,6 +213,46 @@ def marginals(pot, bmm=None):
     return logz.detach(), grad
 
 
+class GraphedMarginals:
+    """marginals() for one fixed shape, captured once into a CUDA graph and replayed.
+
+    The tree has log2(T) levels and each level is a handful of launches in either direction; at the upper
+    levels the products are tiny and the host cannot issue launches as fast as the GPU retires them.  The
+    capture records the whole forward and backward (layout conversion, every level, the final logsumexp and
+    its gradient) on static buffers, so a call is one copy into the input buffer and one graph launch.
+
+        run = GraphedMarginals((B, T - 1, C, C), device)
+        logz, marg = run(pot)        # views of the graph's own output buffers: copy them to keep them
+
+    Nothing in the captured region synchronises with the host: the guard flags of the factorised logbmm are
+    consumed on the device."""
+
+    def __init__(self, shape, device, dtype=torch.float32, warmup=3):
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise RuntimeError("GraphedMarginals needs a CUDA device")
+        self.pot = torch.zeros(shape, dtype=dtype, device=device)
+        with torch.cuda.device(device):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(max(warmup, 1)):      # loads every kernel and fills the driver-side caches
+                    marginals(self.pot)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.logz, self.grad = marginals(self.pot)
+
+    def __call__(self, pot):
+        if tuple(pot.shape) != tuple(self.pot.shape) or pot.dtype != self.pot.dtype:
+            raise RuntimeError("captured for %s %s, got %s %s" % (tuple(self.pot.shape), self.pot.dtype,
+                                                                  tuple(pot.shape), pot.dtype))
+        self.pot.copy_(pot)
+        self.graph.replay()
+        return self.logz, self.grad
+
+
 class _GatherKeepOwnGrad(torch.autograd.Function):
     """All-gather along a new leading rank axis.  Every rank goes on to compute the same
     replicated loss from the gathered tensor, so the gradient each rank needs is just the slice

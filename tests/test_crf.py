@@ -100,3 +100,20 @@ def test_config4_full_size_properties():
     right = marg[:, :-1].sum(2)     # state at the right end of edge t
     left = marg[:, 1:].sum(3)       # state at the left end of edge t+1
     assert torch.allclose(right, left, rtol=0, atol=2e-4)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,L,C", [(2, 15, 64), (2, 63, 256)])
+def test_graphed_marginals_replay_matches_eager(B, L, C):
+    """One capture, two replays on different potentials: each must reproduce the eager driver."""
+    from genbmm_b200 import crf
+    run = crf.GraphedMarginals((B, L, C, C), "cuda")
+    gen = torch.Generator().manual_seed(11)
+    for _ in range(2):
+        pot = torch.randn(B, L, C, C, generator=gen).cuda()
+        logz, marg = run(pot)
+        want_z, want_m = crf.marginals(pot)
+        assert torch.allclose(logz, want_z, rtol=1e-6, atol=0)
+        assert torch.allclose(marg, want_m, rtol=1e-5, atol=1e-9)
+    with pytest.raises(RuntimeError):
+        run(torch.zeros(B, L + 1, C, C, device="cuda"))
