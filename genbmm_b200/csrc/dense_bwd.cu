@@ -25,8 +25,7 @@ __device__ __forceinline__ float pinf_f() { return __int_as_float(0x7f800000); }
 
 struct TileCoord {
   int bt, r0, c0;
-  __device__ __forceinline__ TileCoord(int tiles_r, int tiles_c) {
-    const int64_t id = blockIdx.x;
+  __device__ __forceinline__ TileCoord(int64_t id, int tiles_r, int tiles_c) {
     c0 = (int)(id % tiles_c) * BC;
     r0 = (int)((id / tiles_c) % tiles_r) * BR;
     bt = (int)(id / ((int64_t)tiles_c * tiles_r));
@@ -68,17 +67,12 @@ __device__ __forceinline__ void store_tile(float* __restrict__ dst, int64_t pitc
 
 // grad_a tile: rows m, columns k, reduction over n.
 template <bool FLAGGED>
-__global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __restrict__ a,
-                                                             const float* __restrict__ b,
-                                                             const float* __restrict__ c,
-                                                             const float* __restrict__ g,
-                                                             float* __restrict__ grad_a, int M, int K, int N,
-                                                             int tiles_r, int tiles_c,
-                                                             const int* __restrict__ flags) {
-  __shared__ __align__(16) float sc[2][BK * LDR];
-  __shared__ __align__(16) float sg[2][BK * LDR];
-  __shared__ __align__(16) float sb[2][BK * LDC];
-  const TileCoord tc(tiles_r, tiles_c);
+__device__ __forceinline__ void log_bwd_a_tile(const TileCoord& tc, float (&sc)[2][BK * LDR],
+                                               float (&sg)[2][BK * LDR], float (&sb)[2][BK * LDC],
+                                               const float* __restrict__ a, const float* __restrict__ b,
+                                               const float* __restrict__ c, const float* __restrict__ g,
+                                               float* __restrict__ grad_a, int M, int K, int N, int tiles_r,
+                                               const int* __restrict__ flags) {
   const Micro8x4 mt;
   const float* ab = a + (int64_t)tc.bt * M * K;
   const float* bb = b + (int64_t)tc.bt * K * N;
@@ -90,11 +84,6 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __rest
   constexpr int GRP = 128 / BK;  // reduction tiles per 128-wide flag tile
   const int ngrp = FLAGGED ? (N + 127) / 128 : 1;
   const int* frow = FLAGGED ? flags + ((int64_t)tc.bt * tiles_r + tc.r0 / 128) * ngrp : nullptr;
-  if (FLAGGED) {
-    bool any = false;
-    for (int q = 0; q < ngrp; ++q) any |= (__ldg(frow + q) != 0);
-    if (!any) return;
-  }
 
   float acc[8][4], av[8][4];
 #pragma unroll
@@ -154,19 +143,52 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __rest
   store_tile<FLAGGED>(grad_a + (int64_t)tc.bt * M * K, K, M, K, tc, mt, acc);
 }
 
-// grad_b tile: rows k, columns n, reduction over m.
+// One tile per CTA (FLAGGED false: grid = `total` tiles), or a capped grid whose CTAs gather the tiles with a
+// marked flag in their strip and work through them.
 template <bool FLAGGED>
-__global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __restrict__ a,
+__global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __restrict__ a,
                                                              const float* __restrict__ b,
                                                              const float* __restrict__ c,
                                                              const float* __restrict__ g,
-                                                             float* __restrict__ grad_b, int M, int K, int N,
+                                                             float* __restrict__ grad_a, int M, int K, int N,
                                                              int tiles_r, int tiles_c,
-                                                             const int* __restrict__ flags) {
-  __shared__ __align__(16) float sa[2][BK * LDR];
-  __shared__ __align__(16) float sc[2][BK * LDC];
-  __shared__ __align__(16) float sg[2][BK * LDC];
-  const TileCoord tc(tiles_r, tiles_c);
+                                                             const int* __restrict__ flags, int64_t total) {
+  __shared__ __align__(16) float sc[2][BK * LDR];
+  __shared__ __align__(16) float sg[2][BK * LDR];
+  __shared__ __align__(16) float sb[2][BK * LDC];
+  if (!FLAGGED) {
+    log_bwd_a_tile<false>(TileCoord(blockIdx.x, tiles_r, tiles_c), sc, sg, sb, a, b, c, g, grad_a, M, K, N,
+                          tiles_r, flags);
+    return;
+  }
+  __shared__ int list[NT];
+  __shared__ int count;
+  const int ngrp = (N + 127) / 128;
+  auto flagged = [&](int64_t id) {
+    const TileCoord t(id, tiles_r, tiles_c);
+    const int* frow = flags + ((int64_t)t.bt * tiles_r + t.r0 / 128) * ngrp;
+    bool any = false;
+    for (int q = 0; q < ngrp; ++q) any |= (__ldg(frow + q) != 0);
+    return any;
+  };
+  for (int64_t base = 0; base < total; base += (int64_t)gridDim.x * NT) {
+    const int nw = collect_tiles(base, total, list, &count, flagged);
+    for (int w = 0; w < nw; ++w) {
+      log_bwd_a_tile<true>(TileCoord(list[w], tiles_r, tiles_c), sc, sg, sb, a, b, c, g, grad_a, M, K, N,
+                           tiles_r, flags);
+      __syncthreads();
+    }
+  }
+}
+
+// grad_b tile: rows k, columns n, reduction over m.
+template <bool FLAGGED>
+__device__ __forceinline__ void log_bwd_b_tile(const TileCoord& tc, float (&sa)[2][BK * LDR],
+                                               float (&sc)[2][BK * LDC], float (&sg)[2][BK * LDC],
+                                               const float* __restrict__ a, const float* __restrict__ b,
+                                               const float* __restrict__ c, const float* __restrict__ g,
+                                               float* __restrict__ grad_b, int M, int K, int N,
+                                               const int* __restrict__ flags) {
   const Micro8x4 mt;
   const float* ab = a + (int64_t)tc.bt * M * K;
   const float* bb = b + (int64_t)tc.bt * K * N;
@@ -179,11 +201,6 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __rest
   const int ngrp = FLAGGED ? (M + 127) / 128 : 1;
   const int fpitch = (N + 127) / 128;
   const int* fcol = FLAGGED ? flags + (int64_t)tc.bt * ngrp * fpitch + tc.c0 / 128 : nullptr;
-  if (FLAGGED) {
-    bool any = false;
-    for (int q = 0; q < ngrp; ++q) any |= (__ldg(fcol + (int64_t)q * fpitch) != 0);
-    if (!any) return;
-  }
 
   float acc[8][4], bv[8][4];
 #pragma unroll
@@ -238,6 +255,40 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __rest
     }
   }
   store_tile<FLAGGED>(grad_b + (int64_t)tc.bt * K * N, N, K, N, tc, mt, acc);
+}
+
+template <bool FLAGGED>
+__global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __restrict__ a,
+                                                             const float* __restrict__ b,
+                                                             const float* __restrict__ c,
+                                                             const float* __restrict__ g,
+                                                             float* __restrict__ grad_b, int M, int K, int N,
+                                                             int tiles_r, int tiles_c,
+                                                             const int* __restrict__ flags, int64_t total) {
+  __shared__ __align__(16) float sa[2][BK * LDR];
+  __shared__ __align__(16) float sc[2][BK * LDC];
+  __shared__ __align__(16) float sg[2][BK * LDC];
+  if (!FLAGGED) {
+    log_bwd_b_tile<false>(TileCoord(blockIdx.x, tiles_r, tiles_c), sa, sc, sg, a, b, c, g, grad_b, M, K, N, flags);
+    return;
+  }
+  __shared__ int list[NT];
+  __shared__ int count;
+  const int ngrp = (M + 127) / 128, fpitch = (N + 127) / 128;
+  auto flagged = [&](int64_t id) {
+    const TileCoord t(id, tiles_r, tiles_c);
+    const int* fcol = flags + (int64_t)t.bt * ngrp * fpitch + t.c0 / 128;
+    bool any = false;
+    for (int q = 0; q < ngrp; ++q) any |= (__ldg(fcol + (int64_t)q * fpitch) != 0);
+    return any;
+  };
+  for (int64_t base = 0; base < total; base += (int64_t)gridDim.x * NT) {
+    const int nw = collect_tiles(base, total, list, &count, flagged);
+    for (int w = 0; w < nw; ++w) {
+      log_bwd_b_tile<true>(TileCoord(list[w], tiles_r, tiles_c), sa, sc, sg, a, b, c, g, grad_b, M, K, N, flags);
+      __syncthreads();
+    }
+  }
 }
 
 // ------------------------------------------------------------------ index routing
@@ -374,15 +425,17 @@ int launch_log_bwd_flagged(const float* a, const float* b, const float* c, const
   if (grad_a) {
     const int64_t tr = ceil_div(M, BR), tcn = ceil_div(K, BC), blocks = B * tr * tcn;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
-    dense_log_bwd_a_kernel<true><<<(unsigned)blocks, NT, 0, st>>>(a, b, c, g, grad_a, m, k, n, (int)tr, (int)tcn,
-                                                                  flags);
+    unsigned grid = 0;
+    if (int rc = capped_grid(blocks, &grid)) return rc;
+    dense_log_bwd_a_kernel<true><<<grid, NT, 0, st>>>(a, b, c, g, grad_a, m, k, n, (int)tr, (int)tcn, flags, blocks);
     if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
   }
   if (grad_b) {
     const int64_t tr = ceil_div(K, BR), tcn = ceil_div(N, BC), blocks = B * tr * tcn;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
-    dense_log_bwd_b_kernel<true><<<(unsigned)blocks, NT, 0, st>>>(a, b, c, g, grad_b, m, k, n, (int)tr, (int)tcn,
-                                                                  flags);
+    unsigned grid = 0;
+    if (int rc = capped_grid(blocks, &grid)) return rc;
+    dense_log_bwd_b_kernel<true><<<grid, NT, 0, st>>>(a, b, c, g, grad_b, m, k, n, (int)tr, (int)tcn, flags, blocks);
   }
   return launch_status();
 }
@@ -414,14 +467,14 @@ extern "C" int gbmm_dense_backward_f32(int mode, const float* a, const float* b,
       const int64_t tr = ceil_div(M, BR), tcn = ceil_div(K, BC), blocks = B * tr * tcn;
       if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
       dense_log_bwd_a_kernel<false><<<(unsigned)blocks, NT, 0, st>>>(a, b, part, grad_out, grad_a, m, k, n,
-                                                                     (int)tr, (int)tcn, nullptr);
+                                                                     (int)tr, (int)tcn, nullptr, blocks);
       if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
     }
     if (grad_b) {
       const int64_t tr = ceil_div(K, BR), tcn = ceil_div(N, BC), blocks = B * tr * tcn;
       if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
       dense_log_bwd_b_kernel<false><<<(unsigned)blocks, NT, 0, st>>>(a, b, part, grad_out, grad_b, m, k, n,
-                                                                     (int)tr, (int)tcn, nullptr);
+                                                                     (int)tr, (int)tcn, nullptr, blocks);
     }
     return launch_status();
   }

@@ -27,8 +27,7 @@ constexpr int LDX = BM + 4, LDY = BN + 4;
 
 struct TileCoord {
   int bt, m0, n0;
-  __device__ __forceinline__ TileCoord(int tiles_m, int tiles_n) {
-    const int64_t id = blockIdx.x;
+  __device__ __forceinline__ TileCoord(int64_t id, int tiles_m, int tiles_n) {
     n0 = (int)(id % tiles_n) * BN;
     m0 = (int)((id / tiles_n) % tiles_m) * BM;
     bt = (int)(id / ((int64_t)tiles_n * tiles_m));
@@ -91,7 +90,7 @@ __global__ void __launch_bounds__(NT, PACK ? 2 : 1) dense_max_fwd_kernel(const f
                                                                          const float* __restrict__ b_t, int kp) {
   __shared__ __align__(16) float sx[2][BK * LDX];
   __shared__ __align__(16) float sy[2][BK * LDY];
-  const TileCoord tc(tiles_m, tiles_n);
+  const TileCoord tc(blockIdx.x, tiles_m, tiles_n);
   const Micro8x4 mt;
   const float* ab = a + (int64_t)tc.bt * M * K;
   const float* bb = b + (int64_t)tc.bt * K * N;
@@ -365,18 +364,10 @@ __global__ void __launch_bounds__(256) transpose_b_kernel(const float* __restric
 }
 
 // ------------------------------------------------------------------ log-sum-exp
-__global__ void __launch_bounds__(NT) dense_log_fwd_kernel(const float* __restrict__ a,
-                                                           const float* __restrict__ b,
-                                                           float* __restrict__ out,
-                                                           float* __restrict__ maxes, int M, int K, int N,
-                                                           int tiles_m, int tiles_n,
-                                                           const int* __restrict__ flags) {
-  __shared__ __align__(16) float sx[2][BK * LDX];
-  __shared__ __align__(16) float sy[2][BK * LDY];
-  const TileCoord tc(tiles_m, tiles_n);
-  // Behind the factorised fast path only the 128x128 result tiles it marked are recomputed.
-  if (flags && __ldg(flags + ((int64_t)tc.bt * tiles_m + tc.m0 / 128) * ((N + 127) / 128) + tc.n0 / 128) == 0)
-    return;
+__device__ __forceinline__ void log_fwd_tile(const TileCoord& tc, float (&sx)[2][BK * LDX],
+                                             float (&sy)[2][BK * LDY], const float* __restrict__ a,
+                                             const float* __restrict__ b, float* __restrict__ out,
+                                             float* __restrict__ maxes, int M, int K, int N) {
   const Micro8x4 mt;
   const float* ab = a + (int64_t)tc.bt * M * K;
   const float* bb = b + (int64_t)tc.bt * K * N;
@@ -487,6 +478,38 @@ __global__ void __launch_bounds__(NT) dense_log_fwd_kernel(const float* __restri
   }
 }
 
+// One tile per CTA (FLAGGED false: grid = all tiles).  Behind the factorised fast path (FLAGGED) only the
+// 128x128 result tiles it marked are recomputed: a capped grid whose CTAs gather the marked tiles among
+// their share of the `total` tiles and work through them.
+template <bool FLAGGED>
+__global__ void __launch_bounds__(NT) dense_log_fwd_kernel(const float* __restrict__ a,
+                                                           const float* __restrict__ b,
+                                                           float* __restrict__ out,
+                                                           float* __restrict__ maxes, int M, int K, int N,
+                                                           int tiles_m, int tiles_n,
+                                                           const int* __restrict__ flags, int64_t total) {
+  __shared__ __align__(16) float sx[2][BK * LDX];
+  __shared__ __align__(16) float sy[2][BK * LDY];
+  if (!FLAGGED) {
+    log_fwd_tile(TileCoord(blockIdx.x, tiles_m, tiles_n), sx, sy, a, b, out, maxes, M, K, N);
+    return;
+  }
+  __shared__ int list[NT];
+  __shared__ int count;
+  const int fm = (M + 127) / 128, fn = (N + 127) / 128;
+  auto flagged = [&](int64_t id) {
+    const TileCoord t(id, tiles_m, tiles_n);
+    return __ldg(flags + ((int64_t)t.bt * fm + t.m0 / 128) * fn + t.n0 / 128) != 0;
+  };
+  for (int64_t base = 0; base < total; base += (int64_t)gridDim.x * NT) {
+    const int nw = collect_tiles(base, total, list, &count, flagged);
+    for (int w = 0; w < nw; ++w) {
+      log_fwd_tile(TileCoord(list[w], tiles_m, tiles_n), sx, sy, a, b, out, maxes, M, K, N);
+      __syncthreads();
+    }
+  }
+}
+
 // ------------------------------------------------------------------ inverse-CDF sampling pass
 // Follows matmul_cuda_kernel.cu:109-118: with p_k = exp(a+b-out) and `total` the fp32 running
 // sum in ascending k, the sample is the first k with total < u and total + p_k > u; 0 if none.
@@ -499,7 +522,7 @@ __global__ void __launch_bounds__(NT) dense_sample_pick_kernel(const float* __re
                                                                int tiles_m, int tiles_n) {
   __shared__ __align__(16) float sx[2][BK * LDX];
   __shared__ __align__(16) float sy[2][BK * LDY];
-  const TileCoord tc(tiles_m, tiles_n);
+  const TileCoord tc(blockIdx.x, tiles_m, tiles_n);
   const Micro8x4 mt;
   const float* ab = a + (int64_t)tc.bt * M * K;
   const float* bb = b + (int64_t)tc.bt * K * N;
@@ -582,8 +605,15 @@ int launch_log_fwd_flagged(const float* a, const float* b, float* out, const int
                            int64_t K, int64_t N, cudaStream_t st) {
   const int64_t tiles_m = ceil_div(M, BM), tiles_n = ceil_div(N, BN), blocks = B * tiles_m * tiles_n;
   if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
-  dense_log_fwd_kernel<<<(unsigned)blocks, NT, 0, st>>>(a, b, out, nullptr, (int)M, (int)K, (int)N, (int)tiles_m,
-                                                        (int)tiles_n, flags);
+  if (!flags) {
+    dense_log_fwd_kernel<false><<<(unsigned)blocks, NT, 0, st>>>(a, b, out, nullptr, (int)M, (int)K, (int)N,
+                                                                 (int)tiles_m, (int)tiles_n, nullptr, blocks);
+    return launch_status();
+  }
+  unsigned grid = 0;
+  if (int rc = capped_grid(blocks, &grid)) return rc;
+  dense_log_fwd_kernel<true><<<grid, NT, 0, st>>>(a, b, out, nullptr, (int)M, (int)K, (int)N, (int)tiles_m,
+                                                  (int)tiles_n, flags, blocks);
   return launch_status();
 }
 }  // namespace gbmm
@@ -629,7 +659,8 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
   const int m = (int)M, k = (int)K, n = (int)N, tm = (int)tiles_m, tn = (int)tiles_n;
   switch (mode) {
     case GBMM_MODE_LOG:
-      dense_log_fwd_kernel<<<grid, block, 0, st>>>(a, b, out, static_cast<float*>(aux), m, k, n, tm, tn, nullptr);
+      dense_log_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, static_cast<float*>(aux), m, k, n, tm, tn, nullptr,
+                                                          blocks);
       break;
     case GBMM_MODE_MAX:
     case GBMM_MODE_PRODMAX: {
@@ -660,7 +691,7 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
       break;
     }
     case GBMM_MODE_SAMPLE:
-      dense_log_fwd_kernel<<<grid, block, 0, st>>>(a, b, out, nullptr, m, k, n, tm, tn, nullptr);
+      dense_log_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, nullptr, m, k, n, tm, tn, nullptr, blocks);
       if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
       dense_sample_pick_kernel<<<grid, block, 0, st>>>(a, b, u, out, static_cast<int*>(aux), m, k, n, tm, tn);
       break;
