@@ -661,6 +661,50 @@ __global__ void __launch_bounds__(256) colsplit_kernel(const float* __restrict__
   }
 }
 
+// colsplit for reductions of up to 32 * NV rows: one CTA of 32 warps per (batch element, 32 columns) holds the
+// whole strip in registers (thread = column lane x row slice, NV rows each), so b is read once and every
+// load of the strip is in flight together; measured 76 us against 92 us for the two-pass kernel at
+// 32 x 1024 x 1024.
+template <int NV>
+__global__ void __launch_bounds__(1024) colsplit_reg_kernel(const float* __restrict__ src, float* __restrict__ colmax,
+                                                       float* __restrict__ hi_out, float* __restrict__ lo_out, int R,
+                                                       int C, int64_t pitch, int tiles_c) {
+  __shared__ float part[32][33];
+  const int lane = threadIdx.x % 32, slice = threadIdx.x / 32;
+  const int64_t bt = blockIdx.x / tiles_c;
+  const int c = (blockIdx.x % tiles_c) * 32 + lane;
+  const float* sp = src + bt * R * C + c;
+  const float ninf = __int_as_float(0xff800000);
+  float v[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int r = slice + 32 * i;
+    v[i] = (c < C && r < R) ? __ldg(sp + (int64_t)r * C) : ninf;
+  }
+  float m = ninf;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) m = fmaxf(m, v[i]);
+  part[slice][lane] = m;
+  __syncthreads();
+#pragma unroll
+  for (int s2 = 0; s2 < 32; ++s2) m = fmaxf(m, part[s2][lane]);
+  const float sh = (m == ninf) ? 0.f : m;
+  if (c >= C) return;
+  if (slice == 0) colmax[bt * C + c] = sh;
+  float* hp = hi_out + bt * R * pitch + c;
+  float* lp = lo_out + bt * R * pitch + c;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int r = slice + 32 * i;
+    if (r < R) {
+      const float e = exp_sfu(v[i] - sh);
+      const float h = tf32_round(e);
+      hp[(int64_t)r * pitch] = h;
+      lp[(int64_t)r * pitch] = e - h;
+    }
+  }
+}
+
 // Tensor map over a (batch, rows, cols) fp32 array with rows `pitch` (a multiple of 32) apart, 128-byte
 // swizzle (16-byte atoms for !MN, 32-byte atoms for MN).  !MN: the columns are the reduction index; boxes of 128 rows x 32 columns.  MN: the rows are
 // the reduction index; dimensions (col % 32, row, col / 32, batch), boxes of 32 x 32 rows x 4 blocks.
@@ -780,7 +824,16 @@ int build_factors_with_maxima(const float* a, const float* b, float* rowmax, flo
   if (rc != GBMM_OK) return rc;
   const int64_t tn = ceil_div(N, 32);
   if (B * tn >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
-  colsplit_kernel<<<(unsigned)(B * tn), 256, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, (int)K, (int)N, pad32(N), (int)tn);
+  const unsigned cblocks = (unsigned)(B * tn);
+  const int k = (int)K, n = (int)N;
+  if (K <= 256)
+    colsplit_reg_kernel<8><<<cblocks, 1024, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
+  else if (K <= 512)
+    colsplit_reg_kernel<16><<<cblocks, 1024, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
+  else if (K <= 1024)
+    colsplit_reg_kernel<32><<<cblocks, 1024, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
+  else
+    colsplit_kernel<<<cblocks, 256, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
   return launch_status();
 }
 
