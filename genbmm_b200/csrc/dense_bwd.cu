@@ -297,6 +297,7 @@ constexpr int ROUTE_WARPS = 8;
 // grad_a: one warp per (batch, m) row.  hist holds KT buckets per warp; K larger than KT is
 // covered in passes.  Lanes take 32 consecutive n at a time; lanes that target the same bucket
 // add one after another in lane (= n) order so the sum is the reference's ascending-n sum.
+constexpr int RU = 8;
 template <bool MUL>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_grad_a_kernel(const float* __restrict__ b,
                                                                          const int* __restrict__ idx,
@@ -317,23 +318,40 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_grad_a_kernel(const fl
     const int kend = min(kbase + KT, K);
     for (int k = lane; k < kend - kbase; k += 32) hist[k] = 0.f;
     __syncwarp();
-    for (int n0 = 0; n0 < N; n0 += 32) {
-      const int n = n0 + lane;
-      int k = -1;
-      float gv = 0.f;
-      if (n < N) {
-        k = __ldg(irow + n);
-        gv = __ldg(grow + n);
+    // RU groups of 32 cells are fetched together: the walk is otherwise one global-load latency per group
+    for (int n0 = 0; n0 < N; n0 += 32 * RU) {
+      int kk[RU];
+      float gg[RU];
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+        const int n = n0 + u * 32 + lane;
+        kk[u] = -1;
+        gg[u] = 0.f;
+        if (n < N) {
+          kk[u] = __ldg(irow + n);
+          gg[u] = __ldg(grow + n);
+        }
       }
-      const bool hit = k >= kbase && k < kend;
-      if (MUL && hit) gv = __fmul_rn(__ldg(bb + (int64_t)k * N + n), gv);
-      // lanes without a target get distinct negative keys so they group with nobody
-      const unsigned peers = __match_any_sync(0xffffffffu, hit ? k : -1 - lane);
-      const int rank = __popc(peers & ((1u << lane) - 1u));
-      const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
-      for (int r = 0; r <= last; ++r) {
-        if (hit && rank == r) hist[k - kbase] = __fadd_rn(hist[k - kbase], gv);
-        __syncwarp();
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+        const int n = n0 + u * 32 + lane;
+        const bool hit = kk[u] >= kbase && kk[u] < kend;
+        if (MUL && hit) gg[u] = __fmul_rn(__ldg(bb + (int64_t)kk[u] * N + n), gg[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+        if (n0 + u * 32 >= N) break;
+        const int k = kk[u];
+        const float gv = gg[u];
+        const bool hit = k >= kbase && k < kend;
+        // lanes without a target get distinct negative keys so they group with nobody
+        const unsigned peers = __match_any_sync(0xffffffffu, hit ? k : -1 - lane);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
+        for (int r = 0; r <= last; ++r) {
+          if (hit && rank == r) hist[k - kbase] = __fadd_rn(hist[k - kbase], gv);
+          __syncwarp();
+        }
       }
     }
     for (int k = lane; k < kend - kbase; k += 32) grad_a[row * K + kbase + k] = hist[k];
@@ -345,7 +363,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_grad_a_kernel(const fl
 // as coalesced 32x32 tiles and turned through shared memory, after which warp w owns column n0 + w:
 // its lanes hold 32 consecutive m, and lanes that target the same bucket add one after another in
 // lane (= m) order, so every bucket is the reference's ascending-m sum.  hist: [32 columns][KB + 1].
-constexpr int RB_WARPS = 32;
+constexpr int RB_WARPS = 32, RD = 4;
 template <bool MUL>
 __global__ void __launch_bounds__(RB_WARPS * 32) route_grad_b_kernel(const float* __restrict__ a,
                                                                      const int* __restrict__ idx,
@@ -367,10 +385,10 @@ __global__ void __launch_bounds__(RB_WARPS * 32) route_grad_b_kernel(const float
   for (int kbase = 0; kbase < K; kbase += KB) {
     const int kend = min(kbase + KB, K);
     for (int k = lane; k < kend - kbase; k += 32) hist[k] = 0.f;
-    // tile 0 into buffer 0
-    int kn = -1;
-    float gn = 0.f;
-    auto fetch = [&](int m) {
+    // RD tiles are in flight in registers: the walk is otherwise one global-load latency per tile
+    int kq[RD];
+    float gq[RD];
+    auto fetch = [&](int m, int& kn, float& gn) {
       kn = -1;
       gn = 0.f;
       if (m < M && nl < N) {
@@ -380,30 +398,32 @@ __global__ void __launch_bounds__(RB_WARPS * 32) route_grad_b_kernel(const float
         if (MUL && kn >= 0) gn = __fmul_rn(__ldg(ab + (int64_t)m * K + kn), gn);
       }
     };
-    fetch(warp);
-    si[0][warp][lane] = kn;
-    sg[0][warp][lane] = gn;
-    __syncthreads();
-    for (int m0 = 0, cur = 0; m0 < M; m0 += 32, cur ^= 1) {
-      const bool more = m0 + 32 < M;
-      if (more) fetch(m0 + 32 + warp);
-      const int k = si[cur][lane][warp];  // lane = m offset, warp = column
-      const float gv = sg[cur][lane][warp];
-      const bool hit = k >= 0;
-      // lanes without a target get distinct negative keys so they group with nobody
-      const unsigned peers = __match_any_sync(0xffffffffu, hit ? k : -1 - lane);
-      const int rank = __popc(peers & ((1u << lane) - 1u));
-      const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
-      for (int r = 0; r <= last; ++r) {
-        if (hit && rank == r) hist[k - kbase] = __fadd_rn(hist[k - kbase], gv);
-        __syncwarp();
+#pragma unroll
+    for (int u = 0; u < RD; ++u) fetch(u * 32 + warp, kq[u], gq[u]);
+    for (int mb = 0; mb < M; mb += 32 * RD) {
+#pragma unroll
+      for (int u = 0; u < RD; ++u) {
+        const int m0 = mb + u * 32;
+        if (m0 >= M) break;
+        // buffer u & 1 was last read two tiles ago, before the previous tile's barrier
+        si[u & 1][warp][lane] = kq[u];
+        sg[u & 1][warp][lane] = gq[u];
+        fetch(m0 + 32 * RD + warp, kq[u], gq[u]);
+        __syncthreads();
+        const int k = si[u & 1][lane][warp];  // lane = m offset, warp = column
+        const float gv = sg[u & 1][lane][warp];
+        const bool hit = k >= 0;
+        // lanes without a target get distinct negative keys so they group with nobody
+        const unsigned peers = __match_any_sync(0xffffffffu, hit ? k : -1 - lane);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
+        for (int r = 0; r <= last; ++r) {
+          if (hit && rank == r) hist[k - kbase] = __fadd_rn(hist[k - kbase], gv);
+          __syncwarp();
+        }
       }
-      if (more) {
-        si[cur ^ 1][warp][lane] = kn;
-        sg[cur ^ 1][warp][lane] = gn;
-      }
-      __syncthreads();
     }
+    __syncthreads();
     // bucket k of all 32 columns is one 128-byte row of grad_b
     if (nl < N)
       for (int k = warp; k < kend - kbase; k += RB_WARPS)
