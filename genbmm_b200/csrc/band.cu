@@ -305,6 +305,7 @@ __global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict_
 // the same cells in ascending i).
 
 // grad_a: one warp per row i; lanes take 32 consecutive jo, same-target lanes add in lane order.
+constexpr int RUB = 9;
 __global__ void __launch_bounds__(256) band_route_a_kernel(const int* __restrict__ idx, const float* __restrict__ g,
                                                            float* __restrict__ grad_a, int64_t rows, BandDims d) {
   extern __shared__ float hist_all[];
@@ -316,25 +317,41 @@ __global__ void __launch_bounds__(256) band_route_a_kernel(const int* __restrict
   float* hist = hist_all + warp * Wa;
   for (int k = lane; k < Wa; k += 32) hist[k] = 0.f;
   __syncwarp();
-  for (int j0 = 0; j0 < Wo; j0 += 32) {
-    const int jo = j0 + lane;
-    int k = -1;
-    float gv = 0.f;
-    bool hit = false;
-    if (jo < Wo) {
-      const int64_t o = i + jo - r_lu;
-      k = __ldg(idx + row * Wo + jo);
-      gv = __ldg(g + row * Wo + jo);
-      const int k2 = k - jo + Wb - 1;
-      const int64_t p = i + k - d.a_lu;
-      hit = o >= 0 && o < n && k >= 0 && k < Wa && k2 >= 0 && k2 < Wb && p >= 0 && p < n;
+  // RUB groups of 32 cells are fetched together (a 257-wide result band is one batch): the walk is
+  // otherwise one global-load latency per group
+  for (int j0 = 0; j0 < Wo; j0 += 32 * RUB) {
+    int kk[RUB];
+    float gg[RUB];
+#pragma unroll
+    for (int u = 0; u < RUB; ++u) {
+      const int jo = j0 + u * 32 + lane;
+      kk[u] = -1;
+      gg[u] = 0.f;
+      if (jo < Wo) {
+        kk[u] = __ldg(idx + row * Wo + jo);
+        gg[u] = __ldg(g + row * Wo + jo);
+      }
     }
-    const unsigned peers = __match_any_sync(0xffffffffu, hit ? k : -1 - lane);
-    const int rank = __popc(peers & ((1u << lane) - 1u));
-    const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
-    for (int r = 0; r <= last; ++r) {
-      if (hit && rank == r) hist[k] = __fadd_rn(hist[k], gv);
-      __syncwarp();
+#pragma unroll
+    for (int u = 0; u < RUB; ++u) {
+      if (j0 + u * 32 >= Wo) break;
+      const int jo = j0 + u * 32 + lane;
+      const int k = kk[u];
+      const float gv = gg[u];
+      bool hit = false;
+      if (jo < Wo) {
+        const int64_t o = i + jo - r_lu;
+        const int k2 = k - jo + Wb - 1;
+        const int64_t p = i + k - d.a_lu;
+        hit = o >= 0 && o < n && k >= 0 && k < Wa && k2 >= 0 && k2 < Wb && p >= 0 && p < n;
+      }
+      const unsigned peers = __match_any_sync(0xffffffffu, hit ? k : -1 - lane);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
+      for (int r = 0; r <= last; ++r) {
+        if (hit && rank == r) hist[k] = __fadd_rn(hist[k], gv);
+        __syncwarp();
+      }
     }
   }
   for (int k = lane; k < Wa; k += 32) grad_a[row * Wa + k] = hist[k];
@@ -345,6 +362,7 @@ __global__ void __launch_bounds__(256) band_route_a_kernel(const int* __restrict
 // turned through shared memory: warp w then owns o = o0 + w, its lanes 32 consecutive i, and lanes that
 // target the same bucket k2 add one after another in lane (= i) order — the ascending-i sum a sequential
 // walk would give.  hist: [32 rows o][Wb + 1].
+constexpr int PD = 2;
 __global__ void __launch_bounds__(1024) band_route_b_kernel(const int* __restrict__ idx, const float* __restrict__ g,
                                                             float* __restrict__ grad_b, BandDims d, int tiles_o) {
   extern __shared__ float hist_all[];
@@ -360,33 +378,51 @@ __global__ void __launch_bounds__(1024) band_route_b_kernel(const int* __restric
   float* hist = hist_all + warp * (Wb + 1);
   for (int k = lane; k < Wb; k += 32) hist[k] = 0.f;
   const int64_t i_lo = max((int64_t)0, o0 - r_ld), i_hi = min(n - 1, o0 + 31 + r_lu);
-  for (int64_t i0 = i_lo; i0 <= i_hi; i0 += 32) {
-    // tile row = warp (i = i0 + warp), tile column c <-> jo = jbase + c, c in [0, 63)
+  // tile row = warp (i = i0 + warp), tile column c <-> jo = jbase + c, c in [0, 63); PD tiles are in flight
+  // in registers, the walk is otherwise one global-load latency per tile
+  int kq[PD][2];
+  float gq[PD][2];
+  auto fetch = [&](int64_t i0, int (&kv)[2], float (&gv)[2]) {
     const int64_t jbase = o0 - i0 - 31 + r_lu, ii = i0 + warp;
-    __syncthreads();  // the previous tile has been consumed
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int c = lane + 32 * h;
       const int64_t jo = jbase + c;
       const bool ok = c < 63 && ii <= i_hi && jo >= 0 && jo < Wo;
-      si[warp][c] = ok ? __ldg(ib + ii * Wo + jo) : -1;
-      sg[warp][c] = ok ? __ldg(gb + ii * Wo + jo) : 0.f;
+      kv[h] = ok ? __ldg(ib + ii * Wo + jo) : -1;
+      gv[h] = ok ? __ldg(gb + ii * Wo + jo) : 0.f;
     }
-    __syncthreads();
-    // lane = row of the tile; this warp's o meets it at column warp + 31 - lane
-    const int ja = si[lane][warp + 31 - lane];
-    const float gv = sg[lane][warp + 31 - lane];
-    const int64_t i = i0 + lane, jo = o - i + r_lu;
-    const int k2 = ja - (int)jo + Wb - 1;
-    const int64_t p = i + ja - d.a_lu;
-    const bool hit = o < n && ja >= 0 && ja < Wa && k2 >= 0 && k2 < Wb && p >= 0 && p < n;
-    // lanes without a target get distinct negative keys so they group with nobody
-    const unsigned peers = __match_any_sync(0xffffffffu, hit ? k2 : -1 - lane);
-    const int rank = __popc(peers & ((1u << lane) - 1u));
-    const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
-    for (int r = 0; r <= last; ++r) {
-      if (hit && rank == r) hist[k2] = __fadd_rn(hist[k2], gv);
-      __syncwarp();
+  };
+#pragma unroll
+  for (int u = 0; u < PD; ++u) fetch(i_lo + 32 * u, kq[u], gq[u]);
+  for (int64_t ib0 = i_lo; ib0 <= i_hi; ib0 += 32 * PD) {
+#pragma unroll
+    for (int u = 0; u < PD; ++u) {
+      const int64_t i0 = ib0 + 32 * u;
+      if (i0 > i_hi) break;
+      __syncthreads();  // the previous tile has been consumed
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        si[warp][lane + 32 * h] = kq[u][h];
+        sg[warp][lane + 32 * h] = gq[u][h];
+      }
+      fetch(i0 + 32 * PD, kq[u], gq[u]);
+      __syncthreads();
+      // lane = row of the tile; this warp's o meets it at column warp + 31 - lane
+      const int ja = si[lane][warp + 31 - lane];
+      const float gv = sg[lane][warp + 31 - lane];
+      const int64_t i = i0 + lane, jo = o - i + r_lu;
+      const int k2 = ja - (int)jo + Wb - 1;
+      const int64_t p = i + ja - d.a_lu;
+      const bool hit = o < n && ja >= 0 && ja < Wa && k2 >= 0 && k2 < Wb && p >= 0 && p < n;
+      // lanes without a target get distinct negative keys so they group with nobody
+      const unsigned peers = __match_any_sync(0xffffffffu, hit ? k2 : -1 - lane);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int last = __reduce_max_sync(0xffffffffu, hit ? rank : 0);
+      for (int r = 0; r <= last; ++r) {
+        if (hit && rank == r) hist[k2] = __fadd_rn(hist[k2], gv);
+        __syncwarp();
+      }
     }
   }
   __syncwarp();
