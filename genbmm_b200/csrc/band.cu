@@ -49,15 +49,15 @@ __host__ __device__ inline int b_pitch(int Wb) { return (Wb & 1) ? Wb + 1 : Wb; 
 
 // ------------------------------------------------------------------ forward
 template <int MODE>
-__global__ void __launch_bounds__(NT) band_fwd_kernel(const float* __restrict__ a, const float* __restrict__ b,
+__device__ __forceinline__ void band_fwd_tile(const int64_t tile_id, const float* __restrict__ a, const float* __restrict__ b,
                                                       float* __restrict__ out, int* __restrict__ idx,
                                                       float* __restrict__ maxes, BandDims d, int TI,
                                                       int tiles_i, int staged, const int* __restrict__ flags) {
   extern __shared__ float smem[];
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
   const int64_t n = d.n;
-  const int64_t bt = blockIdx.x / tiles_i;
-  const int64_t i0 = (int64_t)(blockIdx.x % tiles_i) * TI;
+  const int64_t bt = tile_id / tiles_i;
+  const int64_t i0 = (int64_t)(tile_id % tiles_i) * TI;
   // behind the block-banded fast path only the flagged 64-row blocks are recomputed
   if (flags && __ldg(flags + bt * ((n + 63) / 64) + i0 / 64) == 0) return;
   const float* ab = a + bt * n * Wa;
@@ -123,17 +123,42 @@ __global__ void __launch_bounds__(NT) band_fwd_kernel(const float* __restrict__ 
   }
 }
 
+// LISTED false: one tile per CTA (grid = `total` tiles).  LISTED true (behind a fast path, flags != nullptr):
+// a capped grid whose CTAs gather the tiles that have flagged rows and work through them.
+template <int MODE, bool LISTED>
+__global__ void __launch_bounds__(NT) band_fwd_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                                                      int* __restrict__ idx, float* __restrict__ maxes, BandDims d, int TI,
+                                                      int tiles_i, int staged, const int* __restrict__ flags, int64_t total) {
+  if (!LISTED) {
+    band_fwd_tile<MODE>(blockIdx.x, a, b, out, idx, maxes, d, TI, tiles_i, staged, flags);
+    return;
+  }
+  __shared__ int list[NT];
+  __shared__ int count;
+  const int64_t fb = (d.n + 63) / 64;
+  auto flagged = [&](int64_t id) {
+    return __ldg(flags + (id / tiles_i) * fb + ((id % tiles_i) * TI) / 64) != 0;
+  };
+  for (int64_t base = 0; base < total; base += (int64_t)gridDim.x * NT) {
+    const int nw = collect_tiles(base, total, list, &count, flagged);
+    for (int w = 0; w < nw; ++w) {
+      band_fwd_tile<MODE>(list[w], a, b, out, idx, maxes, d, TI, tiles_i, staged, flags);
+      __syncthreads();
+    }
+  }
+}
+
 // ------------------------------------------------------------------ grad_a
 template <int MODE>
-__global__ void __launch_bounds__(NT) band_bwd_a_kernel(const float* __restrict__ a, const float* __restrict__ b,
+__device__ __forceinline__ void band_bwd_a_tile(const int64_t tile_id, const float* __restrict__ a, const float* __restrict__ b,
                                                         const float* __restrict__ g, const void* __restrict__ part,
                                                         float* __restrict__ grad_a, BandDims d, int TI,
                                                         int tiles_i, int staged, const int* __restrict__ flags) {
   extern __shared__ float smem[];
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
   const int64_t n = d.n;
-  const int64_t bt = blockIdx.x / tiles_i;
-  const int64_t i0 = (int64_t)(blockIdx.x % tiles_i) * TI;
+  const int64_t bt = tile_id / tiles_i;
+  const int64_t i0 = (int64_t)(tile_id % tiles_i) * TI;
   if (flags && __ldg(flags + bt * ((n + 63) / 64) + i0 / 64) == 0) return;  // rows of flagged blocks only
   const float* ab = a + bt * n * Wa;
   const float* bb = b + bt * n * Wb;
@@ -188,11 +213,37 @@ __global__ void __launch_bounds__(NT) band_bwd_a_kernel(const float* __restrict_
   }
 }
 
+// LISTED false: one tile per CTA (grid = `total` tiles).  LISTED true (behind a fast path, flags != nullptr):
+// a capped grid whose CTAs gather the tiles that have flagged rows and work through them.
+template <int MODE, bool LISTED>
+__global__ void __launch_bounds__(NT) band_bwd_a_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                        const float* __restrict__ g, const void* __restrict__ part,
+                                                        float* __restrict__ grad_a, BandDims d, int TI, int tiles_i,
+                                                        int staged, const int* __restrict__ flags, int64_t total) {
+  if (!LISTED) {
+    band_bwd_a_tile<MODE>(blockIdx.x, a, b, g, part, grad_a, d, TI, tiles_i, staged, flags);
+    return;
+  }
+  __shared__ int list[NT];
+  __shared__ int count;
+  const int64_t fb = (d.n + 63) / 64;
+  auto flagged = [&](int64_t id) {
+    return __ldg(flags + (id / tiles_i) * fb + ((id % tiles_i) * TI) / 64) != 0;
+  };
+  for (int64_t base = 0; base < total; base += (int64_t)gridDim.x * NT) {
+    const int nw = collect_tiles(base, total, list, &count, flagged);
+    for (int w = 0; w < nw; ++w) {
+      band_bwd_a_tile<MODE>(list[w], a, b, g, part, grad_a, d, TI, tiles_i, staged, flags);
+      __syncthreads();
+    }
+  }
+}
+
 // ------------------------------------------------------------------ grad_b
 // CTA owns TO consecutive rows o of b; the contributing rows i = o-jo+r_lu span
 // [o0-(Wo-1-r_lu), o0+TO-1+r_lu] and are walked in ascending chunks of TI rows.
 template <int MODE>
-__global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict__ a, const float* __restrict__ b,
+__device__ __forceinline__ void band_bwd_b_tile(const int64_t tile_id, const float* __restrict__ a, const float* __restrict__ b,
                                                         const float* __restrict__ g, const void* __restrict__ part,
                                                         float* __restrict__ grad_b, BandDims d, int TO, int TI,
                                                         int tiles_o, int staged, const int* __restrict__ flags) {
@@ -200,8 +251,8 @@ __global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict_
   const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu();
   const int r_ld = Wo - 1 - r_lu;
   const int64_t n = d.n;
-  const int64_t bt = blockIdx.x / tiles_o;
-  const int64_t o0 = (int64_t)(blockIdx.x % tiles_o) * TO;
+  const int64_t bt = tile_id / tiles_o;
+  const int64_t o0 = (int64_t)(tile_id % tiles_o) * TO;
   const float* ab = a + bt * n * Wa;
   const float* bb = b + bt * n * Wb;
   const float* gb = g + bt * n * Wo;
@@ -292,6 +343,38 @@ __global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict_
       const int ol = e / Wb;
       if (o0 + ol >= n) break;
       ob[(o0 + ol) * Wb + (e - ol * Wb)] = 0.f;
+    }
+  }
+}
+
+// LISTED false: one tile per CTA (grid = `total` tiles).  LISTED true (behind a fast path, flags != nullptr):
+// a capped grid whose CTAs gather the tiles that have flagged rows and work through them.
+template <int MODE, bool LISTED>
+__global__ void __launch_bounds__(NT) band_bwd_b_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                        const float* __restrict__ g, const void* __restrict__ part,
+                                                        float* __restrict__ grad_b, BandDims d, int TO, int TI,
+                                                        int tiles_o, int staged, const int* __restrict__ flags, int64_t total) {
+  if (!LISTED) {
+    band_bwd_b_tile<MODE>(blockIdx.x, a, b, g, part, grad_b, d, TO, TI, tiles_o, staged, flags);
+    return;
+  }
+  __shared__ int list[NT];
+  __shared__ int count;
+  const int64_t fb = (d.n + 63) / 64;
+  const int r_lu = d.r_lu(), r_ld = d.Wo() - 1 - r_lu;
+  auto flagged = [&](int64_t id) {
+    const int64_t o0 = (id % tiles_o) * TO;
+    const int64_t i_begin = max((int64_t)0, o0 - r_ld), i_end = min(d.n, o0 + TO + r_lu);
+    const int* frow = flags + (id / tiles_o) * fb;
+    bool any = false;
+    for (int64_t q = i_begin / 64; q <= (i_end - 1) / 64; ++q) any |= (__ldg(frow + q) != 0);
+    return any;
+  };
+  for (int64_t base = 0; base < total; base += (int64_t)gridDim.x * NT) {
+    const int nw = collect_tiles(base, total, list, &count, flagged);
+    for (int w = 0; w < nw; ++w) {
+      band_bwd_b_tile<MODE>(list[w], a, b, g, part, grad_b, d, TO, TI, tiles_o, staged, flags);
+      __syncthreads();
     }
   }
 }
@@ -558,11 +641,19 @@ static int exact_forward(int mode, const float* a, const float* b, float* out, i
   const size_t smem = staged ? ((size_t)TI * Wa + (size_t)(TI + Wo - 1) * ldb) * sizeof(float) : 0;
   const int64_t tiles = ceil_div(n, TI), blocks = B * tiles;
   if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+  unsigned grid = 0;
+  if (int rc = capped_grid(blocks, &grid)) return rc;
 #define GBMM_LAUNCH_BAND_FWD(MODE)                                                                      \
   do {                                                                                                  \
-    if (smem > 48 * 1024 && !allow_smem(band_fwd_kernel<MODE>, smem)) return GBMM_ERR_LAUNCH;           \
-    band_fwd_kernel<MODE><<<(unsigned)blocks, NT, smem, st>>>(a, b, out, idx, maxes, d, TI, (int)tiles, \
-                                                             staged, flags);                           \
+    if (flags) {                                                                                        \
+      if (smem + 2048 > 48 * 1024 && !allow_smem(band_fwd_kernel<MODE, true>, smem)) return GBMM_ERR_LAUNCH; \
+      band_fwd_kernel<MODE, true><<<grid, NT, smem, st>>>(a, b, out, idx, maxes, d, TI, (int)tiles, staged, \
+                                                          flags, blocks);                               \
+    } else {                                                                                            \
+      if (smem > 48 * 1024 && !allow_smem(band_fwd_kernel<MODE, false>, smem)) return GBMM_ERR_LAUNCH;  \
+      band_fwd_kernel<MODE, false><<<(unsigned)blocks, NT, smem, st>>>(a, b, out, idx, maxes, d, TI,    \
+                                                                       (int)tiles, staged, flags, blocks); \
+    }                                                                                                   \
   } while (0)
   if (mode == GBMM_BAND_MUL) GBMM_LAUNCH_BAND_FWD(GBMM_BAND_MUL);
   else if (mode == GBMM_BAND_MAX) GBMM_LAUNCH_BAND_FWD(GBMM_BAND_MAX);
@@ -611,11 +702,19 @@ static int exact_backward(int mode, const float* a, const float* b, const float*
     const size_t smem = staged ? ((size_t)(TI + Wo - 1) * ldb + 2 * (size_t)TI * Wo) * sizeof(float) : 0;
     const int64_t tiles = ceil_div(n, TI), blocks = B * tiles;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+    unsigned grid = 0;
+    if (int rc = capped_grid(blocks, &grid)) return rc;
 #define GBMM_LAUNCH_BAND_BWD_A(MODE)                                                                      \
   do {                                                                                                    \
-    if (smem > 48 * 1024 && !allow_smem(band_bwd_a_kernel<MODE>, smem)) return GBMM_ERR_LAUNCH;           \
-    band_bwd_a_kernel<MODE><<<(unsigned)blocks, NT, smem, st>>>(a, b, grad_out, part, grad_a, d, TI,      \
-                                                               (int)tiles, staged, flags);               \
+    if (flags) {                                                                                          \
+      if (smem + 2048 > 48 * 1024 && !allow_smem(band_bwd_a_kernel<MODE, true>, smem)) return GBMM_ERR_LAUNCH; \
+      band_bwd_a_kernel<MODE, true><<<grid, NT, smem, st>>>(a, b, grad_out, part, grad_a, d, TI, (int)tiles, \
+                                                            staged, flags, blocks);                       \
+    } else {                                                                                              \
+      if (smem > 48 * 1024 && !allow_smem(band_bwd_a_kernel<MODE, false>, smem)) return GBMM_ERR_LAUNCH;  \
+      band_bwd_a_kernel<MODE, false><<<(unsigned)blocks, NT, smem, st>>>(a, b, grad_out, part, grad_a, d, TI, \
+                                                                         (int)tiles, staged, flags, blocks); \
+    }                                                                                                     \
   } while (0)
     if (mode == GBMM_BAND_MUL) GBMM_LAUNCH_BAND_BWD_A(GBMM_BAND_MUL);
     else if (mode == GBMM_BAND_MAX) GBMM_LAUNCH_BAND_BWD_A(GBMM_BAND_MAX);
@@ -637,11 +736,19 @@ static int exact_backward(int mode, const float* a, const float* b, const float*
     const size_t smem = staged ? ((size_t)TO * Wb + (size_t)TI * (Wa + 2 * (size_t)Wo)) * sizeof(float) : 0;
     const int64_t tiles = ceil_div(n, TO), blocks = B * tiles;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+    unsigned grid = 0;
+    if (int rc = capped_grid(blocks, &grid)) return rc;
 #define GBMM_LAUNCH_BAND_BWD_B(MODE)                                                                      \
   do {                                                                                                    \
-    if (smem > 48 * 1024 && !allow_smem(band_bwd_b_kernel<MODE>, smem)) return GBMM_ERR_LAUNCH;           \
-    band_bwd_b_kernel<MODE><<<(unsigned)blocks, NT, smem, st>>>(a, b, grad_out, part, grad_b, d, TO, TI,  \
-                                                               (int)tiles, staged, flags);               \
+    if (flags) {                                                                                          \
+      if (smem + 2048 > 48 * 1024 && !allow_smem(band_bwd_b_kernel<MODE, true>, smem)) return GBMM_ERR_LAUNCH; \
+      band_bwd_b_kernel<MODE, true><<<grid, NT, smem, st>>>(a, b, grad_out, part, grad_b, d, TO, TI,      \
+                                                            (int)tiles, staged, flags, blocks);           \
+    } else {                                                                                              \
+      if (smem > 48 * 1024 && !allow_smem(band_bwd_b_kernel<MODE, false>, smem)) return GBMM_ERR_LAUNCH;  \
+      band_bwd_b_kernel<MODE, false><<<(unsigned)blocks, NT, smem, st>>>(a, b, grad_out, part, grad_b, d, TO, TI, \
+                                                                         (int)tiles, staged, flags, blocks); \
+    }                                                                                                     \
   } while (0)
     if (mode == GBMM_BAND_MUL) GBMM_LAUNCH_BAND_BWD_B(GBMM_BAND_MUL);
     else if (mode == GBMM_BAND_MAX) GBMM_LAUNCH_BAND_BWD_B(GBMM_BAND_MAX);

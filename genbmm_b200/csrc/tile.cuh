@@ -112,30 +112,4 @@ struct Micro8x4 {
   }
 };
 
-// Work list of a fix-up kernel launched with a capped grid.  CTA c of G = gridDim.x looks at the tile ids
-// c, c + G, c + 2G, ...: in the round starting at `base` thread t tests id base + c + t * G, and the ids for
-// which `flagged` holds are appended to `list` (one entry per thread of the CTA) in shared memory, in no
-// particular order.  Returns how many there are; every thread of the CTA gets the same count.
-template <class Pred>
-__device__ __forceinline__ int collect_tiles(int64_t base, int64_t total, int* list, int* count, Pred flagged) {
-  __syncthreads();  // the previous round's list is no longer read
-  if (threadIdx.x == 0) *count = 0;
-  __syncthreads();
-  const int64_t id = base + blockIdx.x + (int64_t)threadIdx.x * gridDim.x;
-  if (id < total && flagged(id)) list[atomicAdd(count, 1)] = (int)id;
-  __syncthreads();
-  return *count;
-}
-
-// Grid of such a kernel: enough CTAs to fill the device a few times over, never more than there are tiles.
-inline int capped_grid(int64_t tiles, unsigned* grid) {
-  int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess ||
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-    return GBMM_ERR_DEVICE;
-  const int64_t cap = (int64_t)sms * 4;
-  *grid = (unsigned)(tiles < cap ? tiles : cap);
-  return GBMM_OK;
-}
-
 }  // namespace gbmm
