@@ -1,5 +1,6 @@
 // Shared device helpers for the genbmm_b200 kernels (sm_100a only).
 #pragma once
+#include <cstdlib>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -55,12 +56,17 @@ __device__ __forceinline__ int collect_tiles(int64_t base, int64_t total, int* l
 }
 
 // Grid of such a kernel: enough CTAs to fill the device a few times over, never more than there are tiles.
+// GENBMM_B200_FIXUP_CTAS=<n> replaces the cap (tests use a tiny one to drive a CTA through several rounds).
 inline int capped_grid(int64_t tiles, unsigned* grid) {
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
     return GBMM_ERR_DEVICE;
-  const int64_t cap = (int64_t)sms * 4;
+  static const int64_t forced = [] {
+    const char* e = getenv("GENBMM_B200_FIXUP_CTAS");
+    return e ? (int64_t)atoll(e) : (int64_t)0;
+  }();
+  const int64_t cap = forced > 0 ? forced : (int64_t)sms * 4;
   *grid = (unsigned)(tiles < cap ? tiles : cap);
   return GBMM_OK;
 }

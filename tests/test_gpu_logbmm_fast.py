@@ -166,3 +166,44 @@ def test_host_pipeline_matches_the_plain_call():
     assert abs(loss - float(c.detach().sum().double())) <= 1e-5 * abs(loss)
     assert torch.allclose(ga_h.cuda(), want_a, rtol=1e-5, atol=5e-6)
     assert torch.allclose(gb_h.cuda(), want_b, rtol=1e-5, atol=5e-6)
+
+
+_FIXUP_CHILD = r"""
+import sys, numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+from genbmm_b200 import _native as nat
+gen = torch.Generator().manual_seed(1)
+B, M, K, N = 40, 200, 96, 260
+a, b = torch.randn(B, M, K, generator=gen), torch.randn(B, K, N, generator=gen)
+g = torch.rand(B, M, N, generator=gen)
+a[:, :60, :48] -= 400.0
+b[:, 48:, :70] -= 400.0
+a[::3] = torch.randn(a[::3].shape, generator=gen)     # every third element has no flagged tile
+ad, bd, gd = a.cuda(), b.cuda(), g.cuda()
+out, rowmax, colmax, flags = nat.logbmm_fast_forward(ad, bd, check=True, tensor_cores=True)
+ga, gb = nat.logbmm_fast_backward(ad, bd, gd, out, rowmax, colmax, flags, check=True, tensor_cores=True)
+np.savez(sys.argv[2], out=out.cpu().numpy(), ga=ga.cpu().numpy(), gb=gb.cpu().numpy(), nflag=int(flags.sum()))
+"""
+
+
+def test_fixup_work_list_over_several_rounds(tmp_path):
+    """The exact fix-up kernels on one CTA (400 tiles: two rounds of its 256-entry work list) and on the
+    default grid give the same bits: a tile's result does not depend on who gathers it."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = []
+    for cap in ("1", None):
+        env = dict(os.environ)
+        env.pop("GENBMM_B200_FIXUP_CTAS", None)
+        if cap:
+            env["GENBMM_B200_FIXUP_CTAS"] = cap
+        path = str(tmp_path / ("fix_%s.npz" % cap))
+        subprocess.run([sys.executable, "-c", _FIXUP_CHILD, root, path], env=env, check=True, timeout=300)
+        res.append(np.load(path))
+    one, many = res
+    assert int(one["nflag"]) == int(many["nflag"]) > 0
+    for k in ("out", "ga", "gb"):
+        assert np.array_equal(one[k], many[k]), k
+    assert np.isfinite(one["out"]).all()
