@@ -665,11 +665,11 @@ __global__ void __launch_bounds__(256) colsplit_kernel(const float* __restrict__
 // whole strip in registers (thread = column lane x row slice, NV rows each), so b is read once and every
 // load of the strip is in flight together; measured 76 us against 92 us for the two-pass kernel at
 // 32 x 1024 x 1024.
-template <int NV>
-__global__ void __launch_bounds__(1024) colsplit_reg_kernel(const float* __restrict__ src, float* __restrict__ colmax,
+template <int NV, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) colsplit_reg_kernel(const float* __restrict__ src, float* __restrict__ colmax,
                                                        float* __restrict__ hi_out, float* __restrict__ lo_out, int R,
                                                        int C, int64_t pitch, int tiles_c) {
-  __shared__ float part[32][33];
+  __shared__ float part[WARPS][33];
   const int lane = threadIdx.x % 32, slice = threadIdx.x / 32;
   const int64_t bt = blockIdx.x / tiles_c;
   const int c = (blockIdx.x % tiles_c) * 32 + lane;
@@ -678,7 +678,7 @@ __global__ void __launch_bounds__(1024) colsplit_reg_kernel(const float* __restr
   float v[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int r = slice + 32 * i;
+    const int r = slice + WARPS * i;
     v[i] = (c < C && r < R) ? __ldg(sp + (int64_t)r * C) : ninf;
   }
   float m = ninf;
@@ -687,7 +687,7 @@ __global__ void __launch_bounds__(1024) colsplit_reg_kernel(const float* __restr
   part[slice][lane] = m;
   __syncthreads();
 #pragma unroll
-  for (int s2 = 0; s2 < 32; ++s2) m = fmaxf(m, part[s2][lane]);
+  for (int s2 = 0; s2 < WARPS; ++s2) m = fmaxf(m, part[s2][lane]);
   const float sh = (m == ninf) ? 0.f : m;
   if (c >= C) return;
   if (slice == 0) colmax[bt * C + c] = sh;
@@ -695,7 +695,7 @@ __global__ void __launch_bounds__(1024) colsplit_reg_kernel(const float* __restr
   float* lp = lo_out + bt * R * pitch + c;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int r = slice + 32 * i;
+    const int r = slice + WARPS * i;
     if (r < R) {
       const float e = exp_sfu(v[i] - sh);
       const float h = tf32_round(e);
@@ -827,11 +827,11 @@ int build_factors_with_maxima(const float* a, const float* b, float* rowmax, flo
   const unsigned cblocks = (unsigned)(B * tn);
   const int k = (int)K, n = (int)N;
   if (K <= 256)
-    colsplit_reg_kernel<8><<<cblocks, 1024, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
+    colsplit_reg_kernel<32, 8><<<cblocks, 256, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
   else if (K <= 512)
-    colsplit_reg_kernel<16><<<cblocks, 1024, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
+    colsplit_reg_kernel<32, 16><<<cblocks, 512, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
   else if (K <= 1024)
-    colsplit_reg_kernel<32><<<cblocks, 1024, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
+    colsplit_reg_kernel<32, 32><<<cblocks, 1024, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
   else
     colsplit_kernel<<<cblocks, 256, 0, st>>>(b, colmax, f.eb_hi, f.eb_lo, k, n, pad32(N), (int)tn);
   return launch_status();
