@@ -235,6 +235,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=32, help="1024^3 problems per GPU per step")
     ap.add_argument("--e2e-chunks", type=int, default=16, help="batch chunks of the host pipeline (end-to-end leg)")
+    ap.add_argument("--e2e-graph", type=int, default=0, help="1: the host pipeline replays one CUDA graph per chunk")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the side measurements of configs 1-5")
     args = ap.parse_args()
@@ -320,13 +321,14 @@ def main():
     # genbmm_b200.host.HostPipeline: the package's call for host-resident operands; it overlaps the
     # two PCIe directions with the kernels by cutting the batch into chunks on three streams
     from genbmm_b200.host import HostPipeline
-    pipe = HostPipeline(B, SIZE, SIZE, SIZE, chunks=args.e2e_chunks, device=dev)
+    pipe = HostPipeline(B, SIZE, SIZE, SIZE, chunks=args.e2e_chunks, device=dev, graph=bool(args.e2e_graph))
 
     def step_e2e():
         return pipe.step(a_h, b_h, ga_h, gb_h)
 
-    e2e_steps = max(2, min(args.steps, 5))
-    t_e2e = torch.tensor([time_steps(step_e2e, e2e_steps, 1, sync) / e2e_steps], device=dev)
+    e2e_steps = max(2, min(args.steps, 50))
+    # three untimed steps first (with --e2e-graph 1 the pipeline captures its kernels at the second)
+    t_e2e = torch.tensor([time_steps(step_e2e, e2e_steps, 3, sync) / e2e_steps], device=dev)
     if dist is not None:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
     t_e2e = float(t_e2e.item())

@@ -44,10 +44,19 @@ def bind_host_near(device):
 
 
 class HostPipeline:
-    def __init__(self, B, M, K, N, chunks=4, device=None, tensor_cores=True):
+    def __init__(self, B, M, K, N, chunks=4, device=None, tensor_cores=True, graph=False):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.shape = (B, M, K, N)
         self.tensor_cores = tensor_cores
+        # graph=True: the second step captures the kernels of every chunk (forward, loss, backward) into one
+        # CUDA graph per chunk, all in one memory pool, and later steps replay them between the copies,
+        # which stay ordinary stream copies; the host then issues about a hundred calls per step instead
+        # of several hundred.  Off by default: a 32 x 1024^3 step is bound by the PCIe copies, not by the
+        # host (measured 7.4 ms with graphs against 6.6-6.9 ms without on one GPU, 31.5 ms either way
+        # with eight ranks sharing one host's links).
+        self.use_graph = graph
+        self._graphs = None
+        self._warm = False
         chunks = max(1, min(chunks, B))
         self.bounds = [(i * B // chunks, (i + 1) * B // chunks) for i in range(chunks)]
         with torch.cuda.device(self.device):
@@ -68,31 +77,52 @@ class HostPipeline:
         pinned; the gradients are complete in grad_*_host when this returns.  Returns the loss."""
         B, M, K, N = self.shape
         assert tuple(a_host.shape) == (B, M, K) and tuple(b_host.shape) == (B, K, N)
-        comp = torch.cuda.current_stream(self.device)
         with torch.cuda.device(self.device):
+            if self.use_graph and self._warm and self._graphs is None:
+                # the first step ran directly (every kernel loaded, allocator filled): capture now
+                torch.cuda.synchronize(self.device)
+                graphs, pool = [], None
+                for i in range(len(self.bounds)):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, pool=pool):
+                        self._compute(i)
+                    pool = g.pool()
+                    graphs.append(g)
+                self._graphs = graphs
+            comp = torch.cuda.current_stream(self.device)
             self.loss.zero_()
             # the copy streams start after whatever the compute stream was doing with the buffers
             self.ev_step.record(comp)
             self.s_in.wait_event(self.ev_step)
             self.s_out.wait_event(self.ev_step)
-            for i, (lo, hi) in enumerate(self.bounds):
-                with torch.cuda.stream(self.s_in):
+            with torch.cuda.stream(self.s_in):
+                for i, (lo, hi) in enumerate(self.bounds):
                     self.a[lo:hi].copy_(a_host[lo:hi], non_blocking=True)
                     self.b[lo:hi].copy_(b_host[lo:hi], non_blocking=True)
                     self.ev_in[i].record(self.s_in)
             for i, (lo, hi) in enumerate(self.bounds):
                 comp.wait_event(self.ev_in[i])
-                a, b = self.a[lo:hi], self.b[lo:hi]
-                out, rowmax, colmax, flags, factors = _native.logbmm_fast_forward(
-                    a, b, tensor_cores=self.tensor_cores, keep_factors=True)
-                self.loss += out.sum(dtype=torch.float64)
-                ga, gb = _native.logbmm_fast_backward(a, b, self.ones[: hi - lo], out, rowmax, colmax, flags,
-                                                      tensor_cores=self.tensor_cores, factors=factors,
-                                                      out_grads=(self.grad_a[lo:hi], self.grad_b[lo:hi]))
+                if self._graphs is not None:
+                    self._graphs[i].replay()
+                else:
+                    self._compute(i)
                 self.ev_done[i].record(comp)
                 with torch.cuda.stream(self.s_out):
                     self.s_out.wait_event(self.ev_done[i])
-                    grad_a_host[lo:hi].copy_(ga, non_blocking=True)
-                    grad_b_host[lo:hi].copy_(gb, non_blocking=True)
+                    grad_a_host[lo:hi].copy_(self.grad_a[lo:hi], non_blocking=True)
+                    grad_b_host[lo:hi].copy_(self.grad_b[lo:hi], non_blocking=True)
             comp.wait_stream(self.s_out)
+            self._warm = True
             return float(self.loss.item())
+
+    def _compute(self, i):
+        """Kernels of chunk i on the current stream: forward, its share of the loss, backward into the
+        chunk's rows of the gradient buffers."""
+        lo, hi = self.bounds[i]
+        a, b = self.a[lo:hi], self.b[lo:hi]
+        out, rowmax, colmax, flags, factors = _native.logbmm_fast_forward(
+            a, b, tensor_cores=self.tensor_cores, keep_factors=True)
+        self.loss += out.sum(dtype=torch.float64)
+        _native.logbmm_fast_backward(a, b, self.ones[: hi - lo], out, rowmax, colmax, flags,
+                                     tensor_cores=self.tensor_cores, factors=factors,
+                                     out_grads=(self.grad_a[lo:hi], self.grad_b[lo:hi]))

@@ -156,10 +156,22 @@ def test_host_pipeline_matches_the_plain_call():
     a_h = torch.randn(B, M, K, generator=gen).pin_memory()
     b_h = torch.randn(B, K, N, generator=gen).pin_memory()
     ga_h, gb_h = torch.empty(B, M, K).pin_memory(), torch.empty(B, K, N).pin_memory()
-    pipe = HostPipeline(B, M, K, N, chunks=4)
-    for _ in range(2):   # buffers are reused across steps
-        loss = pipe.step(a_h, b_h, ga_h, gb_h)
+    pipe = HostPipeline(B, M, K, N, chunks=4, graph=True)
+    # buffers are reused across steps: the first step is issued directly, the second captures one CUDA graph
+    # per chunk, the third replays them on new contents of the host tensors
+    first = pipe.step(a_h, b_h, ga_h, gb_h)
+    ga_first = ga_h.clone()
+    assert pipe.step(a_h, b_h, ga_h, gb_h) == first and torch.equal(ga_h, ga_first)
+    a_h.copy_(torch.randn(B, M, K, generator=gen))
+    ga_h.zero_(); gb_h.zero_()
+    loss = pipe.step(a_h, b_h, ga_h, gb_h)
+    assert pipe._graphs is not None and len(pipe._graphs) == 4
     torch.cuda.synchronize()
+    plain = HostPipeline(B, M, K, N, chunks=4)
+    ga_p, gb_p = torch.empty(B, M, K).pin_memory(), torch.empty(B, K, N).pin_memory()
+    for _ in range(2):
+        assert plain.step(a_h, b_h, ga_p, gb_p) == loss
+    assert plain._graphs is None and torch.equal(ga_p, ga_h) and torch.equal(gb_p, gb_h)
     ad, bd = a_h.cuda().requires_grad_(True), b_h.cuda().requires_grad_(True)
     c = gb.logbmm(ad, bd)
     want_a, want_b = torch.autograd.grad(c.sum(), (ad, bd))
