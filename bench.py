@@ -254,13 +254,12 @@ def main():
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path"
     torch.cuda.set_device(local)
-    # pinned host buffers next to this rank's GPU: with several ranks on one box the end-to-end number is
-    # bound by host memory and PCIe roots, not by the kernels (at N = 1 all host cores stay available to the
-    # CPU baseline leg)
-    near = None
-    if world > 1:
-        from genbmm_b200.host import bind_host_near
-        near = bind_host_near(torch.device("cuda", local))
+    # pinned host buffers next to this rank's GPU: the end-to-end number is bound by host memory and the PCIe
+    # roots, not by the kernels.  At N = 1 the full core set is given back before the CPU baseline leg (the
+    # buffers are pinned where they were allocated).
+    from genbmm_b200.host import bind_host_near
+    all_cores = os.sched_getaffinity(0) if hasattr(os, "sched_getaffinity") else None
+    near = bind_host_near(torch.device("cuda", local))
     dev = torch.device("cuda", local)
     dist = None
     if world > 1:
@@ -426,6 +425,8 @@ def main():
         except Exception as exc:  # the headline must not depend on the side measurements
             line["configs"] = {"error": repr(exc)}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        if all_cores is not None:
+            os.sched_setaffinity(0, all_cores)
         host_threads()
         value, secs, threads = cpu_logbmm_sample(8192, 64)
         line["cpu_baseline"] = {
