@@ -13,6 +13,7 @@
 // up to 218 KB); the winning tile of each result is then searched there for the first p whose term equals
 // the maximum, with no second trip to global memory.  Ascending p is ascending index in a's band for a fixed
 // row, so this is the reference's lowest-index tie rule; the stored index is p - i + a_lu.
+#include <type_traits>
 #include <algorithm>
 
 #include "band.cuh"
@@ -90,6 +91,7 @@ constexpr int XS = (BK / 2) * LDX * 2 + 4, YS = (BK / 2) * LDY * 2 + 4;  // floa
 constexpr int kMaxSteps = 17;  // 272 reduction steps: 17 * (XS + YS) * 4 bytes = 213 KB
 __host__ __device__ constexpr size_t max_smem_bytes(int steps) { return (size_t)steps * (XS + YS) * sizeof(float); }
 
+template <bool SKIP>
 __global__ void __launch_bounds__(NT, 1) band_max_kernel(MaxArgs g) {
   extern __shared__ __align__(16) float smem_dyn[];
   const Micro8x4 mt;
@@ -164,38 +166,79 @@ __global__ void __launch_bounds__(NT, 1) band_max_kernel(MaxArgs g) {
     }
   }
 
-  auto tile_step = [&](int t, float (&acc)[8][4], const float (&prev)[8][4]) {
+  // A warp owns rows 8w..8w+7 and 64+8w..64+8w+7 of the block.  Row r meets reduction steps r - a_lu .. r + a_ld
+  // only, so for a 16-step tile near either end of the block's range one or both of the warp's row groups
+  // hold nothing but -inf terms; with SKIP those halves of the micro-tile are carried over instead of
+  // multiplied.  The barrier per tile still waits for the warps that are live in it, so the gain is what the
+  // idle warps leave to the pipes: 6 % at 129 x 129 diagonals; where the range is short next to a's band no
+  // warp is ever idle and the launcher takes the plain kernel.
+  const int rw = r0 + (tid >> 5) * 8;
+  auto half_live = [&](int t, int first_row) {
+    const int s = s0 + t * BK;
+    return s <= first_row + 7 + g.a_ld && s + BK - 1 >= first_row - g.a_lu;
+  };
+  auto tile_body = [&](auto UP, auto LOW, int t, float (&acc)[8][4], const float (&prev)[8][4]) {
+    constexpr bool kUp = decltype(UP)::value, kLow = decltype(LOW)::value;
     const float* tx_ = sx + (size_t)t * XS;
     const float* ty_ = sy + (size_t)t * YS;
-    if (t + 1 < nt) fetch(t + 1);
+    if (!kUp) {
 #pragma unroll
-    for (int kp2 = 0; kp2 < BK / 2; ++kp2) {
-      const float* xs = tx_ + (kp2 * LDX + mt.ty * 4) * 2;
-      const float* ys = ty_ + (kp2 * LDY + mt.tx * 4) * 2;
-      const ulonglong2 x01 = *reinterpret_cast<const ulonglong2*>(xs);
-      const ulonglong2 x23 = *reinterpret_cast<const ulonglong2*>(xs + 4);
-      const ulonglong2 x45 = *reinterpret_cast<const ulonglong2*>(xs + 128);
-      const ulonglong2 x67 = *reinterpret_cast<const ulonglong2*>(xs + 132);
-      const ulonglong2 y01 = *reinterpret_cast<const ulonglong2*>(ys);
-      const ulonglong2 y23 = *reinterpret_cast<const ulonglong2*>(ys + 4);
-      const unsigned long long xp[8] = {x01.x, x01.y, x23.x, x23.y, x45.x, x45.y, x67.x, x67.y};
-      const unsigned long long yp[4] = {y01.x, y01.y, y23.x, y23.y};
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+        for (int j = 0; j < 4; ++j) acc[i][j] = prev[i][j];
+    }
+    if (!kLow) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float v0, v1;
-          unpack2(add2(xp[i], yp[j]), v0, v1);
-          acc[i][j] = max3(kp2 == 0 ? prev[i][j] : acc[i][j], v0, v1);
+      for (int i = 4; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = prev[i][j];
+    }
+    if (kUp || kLow) {
+#pragma unroll
+      for (int kp2 = 0; kp2 < BK / 2; ++kp2) {
+        const float* xs = tx_ + (kp2 * LDX + mt.ty * 4) * 2;
+        const float* ys = ty_ + (kp2 * LDY + mt.tx * 4) * 2;
+        const ulonglong2 y01 = *reinterpret_cast<const ulonglong2*>(ys);
+        const ulonglong2 y23 = *reinterpret_cast<const ulonglong2*>(ys + 4);
+        const unsigned long long yp[4] = {y01.x, y01.y, y23.x, y23.y};
+        unsigned long long xp[8];
+        if (kUp) {
+          const ulonglong2 x01 = *reinterpret_cast<const ulonglong2*>(xs);
+          const ulonglong2 x23 = *reinterpret_cast<const ulonglong2*>(xs + 4);
+          xp[0] = x01.x; xp[1] = x01.y; xp[2] = x23.x; xp[3] = x23.y;
         }
-    }
+        if (kLow) {
+          const ulonglong2 x45 = *reinterpret_cast<const ulonglong2*>(xs + 128);
+          const ulonglong2 x67 = *reinterpret_cast<const ulonglong2*>(xs + 132);
+          xp[4] = x45.x; xp[5] = x45.y; xp[6] = x67.x; xp[7] = x67.y;
+        }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {  // strict `>`: an equal maximum in a later tile does not move the index
-      if (acc[i][0] > prev[i][0]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3214);
-      if (acc[i][1] > prev[i][1]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3240);
-      if (acc[i][2] > prev[i][2]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3410);
-      if (acc[i][3] > prev[i][3]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x4210);
+        for (int i = kUp ? 0 : 4; i < (kLow ? 8 : 4); ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float v0, v1;
+            unpack2(add2(xp[i], yp[j]), v0, v1);
+            acc[i][j] = max3(kp2 == 0 ? prev[i][j] : acc[i][j], v0, v1);
+          }
+      }
+#pragma unroll
+      for (int i = kUp ? 0 : 4; i < (kLow ? 8 : 4); ++i) {  // strict `>`: an equal maximum in a later tile keeps the index
+        if (acc[i][0] > prev[i][0]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3214);
+        if (acc[i][1] > prev[i][1]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3240);
+        if (acc[i][2] > prev[i][2]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3410);
+        if (acc[i][3] > prev[i][3]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x4210);
+      }
     }
+  };
+  auto tile_step = [&](int t, float (&acc)[8][4], const float (&prev)[8][4]) {
+    if (t + 1 < nt) fetch(t + 1);
+    const bool up = !SKIP || half_live(t, rw), low = !SKIP || half_live(t, rw + 64);
+    using T = std::true_type;
+    using F = std::false_type;
+    if (up && low) tile_body(T{}, T{}, t, acc, prev);
+    else if (up) tile_body(T{}, F{}, t, acc, prev);
+    else if (low) tile_body(F{}, T{}, t, acc, prev);
+    else tile_body(F{}, F{}, t, acc, prev);
     if (t + 1 < nt) stage(t + 1);
     __syncthreads();
   };
@@ -309,12 +352,20 @@ int band_max_forward(const float* a, const float* b, float* out, int* idx, const
   const int64_t blocks = B * g.nrb * g.ncb;
   if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
   const size_t smem = max_smem_bytes(kMaxSteps);
-  if (cudaFuncSetAttribute(band_max_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  if (cudaFuncSetAttribute(band_max_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(band_max_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+          cudaSuccess)
     return GBMM_ERR_LAUNCH;
   // every block gets the size of the longest range (the sizes differ by block, the launch has one)
   const int64_t range = std::min<int64_t>(BM - 1 + d.Wa(), BN - 1 + d.Wb()) + 2 * (BK - 1);
   const int steps = (int)std::min<int64_t>(kMaxSteps, ceil_div(range, BK));
-  band_max_kernel<<<(unsigned)blocks, NT, max_smem_bytes(steps), st>>>(g);
+  // a warp's 8 rows are live in about Wa + 23 of the block's steps: skipping pays when that leaves a good part
+  // of the range idle
+  if ((d.Wa() + 23) * 20 < range * 17)
+    band_max_kernel<true><<<(unsigned)blocks, NT, max_smem_bytes(steps), st>>>(g);
+  else
+    band_max_kernel<false><<<(unsigned)blocks, NT, max_smem_bytes(steps), st>>>(g);
   return launch_status();
 }
 
