@@ -11,6 +11,7 @@ reference's CHECK_CUDA does, and a missing library is an ImportError.
 """
 import ctypes
 import os
+import threading
 
 import torch
 
@@ -54,6 +55,9 @@ _SIGNATURES = {
     "gbmm_logbmm_forward_noalloc_max_bytes": ([], _L),
     "gbmm_logbmm_forward_noalloc_need_bytes": ([_L, _L, _L, _L], _L),
     "gbmm_logbmm_forward_noalloc_f32": ([_P, _P, _P, _L, _L, _L, _L, _P], _I),
+    "gbmm_logbmm_forward_noalloc_check": ([_P], _I),
+    "gbmm_launch_count": ([], ctypes.c_uint64),
+    "gbmm_poison_on_error": ([_P, _P, _L, _P], _I),
     "gbmm_gather_blocks_f32": ([_P, _P, _P, _L, _L, _I, _P], _I),
     "gbmm_profile_enable": ([_I], None),
     "gbmm_profile_last_ms": ([_I], ctypes.c_float),
@@ -252,66 +256,87 @@ def _check_band(a, a_lu, a_lb, b, b_lu, b_lb):
         raise RuntimeError("a and b must be on the same device")
 
 
-# Workspaces of the banded tensor-core path, kept between calls: their zero padding is written once, when
-# a workspace is created (the library never rewrites it).  One entry per device, replaced when the shape
-# changes; a backward-sized workspace also serves the forward.
-_band_tc_cache = {}
+# Workspaces of the banded fast paths, kept between calls: their padding (zeros for the tensor-core path, -inf
+# for the max-plus path) is written once, when a workspace is created; the library never rewrites it.
+#
+# One workspace per (device, stream, kind): a workspace is only ever touched by kernels of the stream it was
+# created on, so two products on different streams never share scratch, and a workspace that is dropped goes
+# back to the allocator pool of the stream that used it.  A workspace is replaced when the problem's dimensions
+# change.  At most _WS_MAX of them are kept (the oldest is dropped); `release_workspaces()` drops all of them.
+# cfg5-sized problems (32 x 8192, 129 diagonals) keep about 2.3 GB per stream this way.
+_WS_MAX = 8
+_ws_lock = threading.Lock()
+_ws_cache = {}       # (kind, device index, stream handle) -> _Workspace, in order of last use
+
+
+class _Workspace:
+    """`generation` counts the calls that wrote operands into `buf`; `holds` is the banded mode whose forward
+    wrote them last (None after a call that left them incomplete)."""
+    __slots__ = ("dims", "buf", "generation", "holds")
+
+    def __init__(self, dims, buf):
+        self.dims, self.buf, self.generation, self.holds = dims, buf, 0, None
+
+
+def release_workspaces(device=None):
+    """Drop the cached workspaces of the banded fast paths (all devices, or one).  The memory returns to
+    torch's allocator; the next banded call builds a new workspace."""
+    with _ws_lock:
+        for key in [k for k in _ws_cache if device is None or k[1] == torch.device(device).index]:
+            del _ws_cache[key]
+
+
+def _cached_workspace(kind, dims, need, device, init):
+    dev = device.index if device.index is not None else torch.cuda.current_device()
+    stream = _stream(device)
+    key = (kind, dev, stream)
+    with _ws_lock:
+        hit = _ws_cache.pop(key, None)
+        if hit is None or hit.dims != dims or hit.buf.numel() < need:
+            hit = None
+            buf = torch.empty((need,), dtype=torch.uint8, device=device)
+            _check(init(_ptr(buf), buf.numel(), stream), "workspace init")
+            hit = _Workspace(dims, buf)
+        _ws_cache[key] = hit            # most recently used last
+        while len(_ws_cache) > _WS_MAX:
+            del _ws_cache[next(iter(_ws_cache))]
+    return hit
 
 
 def _band_tc_workspace(mode, backward, B, n, bands, device):
-    """The cached workspace for these dimensions on this device, or None when the tensor-core path is not
-    taken (GENBMM_B200_BAND=block keeps the FP32 block kernels, GENBMM_B200_BANDLOG=exact the direct ones).
+    """The cached workspace (_Workspace) for these dimensions on this device and stream, or None when the
+    tensor-core path is not taken (GENBMM_B200_BAND=block keeps the FP32 block kernels, GENBMM_B200_BANDLOG=exact
+    the direct ones).  A backward-sized workspace also serves the forward.
     For the ordinary (sum) semiring the 3xTF32 result is about 1.7 times further from the exact sum than the
     FP32 block kernel's, both a few units in the last place of the sum of the terms' magnitudes."""
     if os.environ.get("GENBMM_B200_BAND", "auto") == "block" or os.environ.get("GENBMM_B200_BANDLOG") == "exact":
         return None
     lib = load()
-    key = (B, n) + tuple(bands)
-    dev = device.index if device.index is not None else torch.cuda.current_device()
-    hit = _band_tc_cache.get(dev)
     need = lib.gbmm_band_tc_workspace_bytes(1 if backward else 0, B, n, *bands)
-    if hit is not None and hit[0] == key and hit[1].numel() >= need:
-        return hit[1]
-    _band_tc_cache.pop(dev, None)
-    ws = torch.empty((need,), dtype=torch.uint8, device=device)
-    _check(lib.gbmm_band_tc_workspace_init(_ptr(ws), ws.numel(), _stream(device)), "gbmm_band_tc_workspace_init")
-    _band_tc_cache[dev] = [key, ws, None]
-    return ws
-
-
-_band_max_cache = {}
+    return _cached_workspace("tc", (B, n) + tuple(bands), need, device, lib.gbmm_band_tc_workspace_init)
 
 
 def _band_max_workspace(B, n, bands, device):
-    """Cached workspace of the fast max-plus forward (its -inf padding is written once), or None when
-    GENBMM_B200_BAND=block."""
+    """Cached workspace (a tensor) of the fast max-plus forward, or None when GENBMM_B200_BAND=block."""
     if os.environ.get("GENBMM_B200_BAND", "auto") == "block":
         return None
     lib = load()
-    key = (B, n) + tuple(bands)
-    dev = device.index if device.index is not None else torch.cuda.current_device()
-    hit = _band_max_cache.get(dev)
-    if hit is not None and hit[0] == key:
-        return hit[1]
-    _band_max_cache.pop(dev, None)
-    ws = torch.empty((lib.gbmm_band_max_workspace_bytes(B, n, *bands),), dtype=torch.uint8, device=device)
-    _check(lib.gbmm_band_max_workspace_init(_ptr(ws), ws.numel(), _stream(device)), "gbmm_band_max_workspace_init")
-    _band_max_cache[dev] = (key, ws)
-    return ws
+    need = lib.gbmm_band_max_workspace_bytes(B, n, *bands)
+    return _cached_workspace("max", (B, n) + tuple(bands), need, device, lib.gbmm_band_max_workspace_init).buf
 
 
-def _band_tc_tag(mode, a, b):
-    """Identifies the operand contents a workspace holds: storage address and version counter of both."""
-    return (mode, a.data_ptr(), a._version, b.data_ptr(), b._version, torch.cuda.current_stream(a.device).cuda_stream)
+class BandForwardToken:
+    """What a banded tensor-core forward left in its workspace, for the backward of the same operands: the
+    workspace and the value of its generation counter right after the forward.  The backward may reuse the
+    forward's converted operands, row maxima and guard flags only while the counter still has that value, i.e.
+    while no other call has written into that workspace."""
+    __slots__ = ("ws", "generation", "mode")
 
+    def __init__(self, ws, mode):
+        self.ws, self.generation, self.mode = ws, ws.generation, mode
 
-def _band_tc_holds(ws, tag, store=False):
-    for entry in _band_tc_cache.values():
-        if entry[1] is ws:
-            if store:
-                entry[2] = tag
-            return entry[2] == tag
-    return False
+    def valid_for(self, ws, mode):
+        return ws is self.ws and ws.generation == self.generation and ws.holds == mode and mode == self.mode
 
 
 def _band_workspace(B, n, device):
@@ -320,18 +345,25 @@ def _band_workspace(B, n, device):
     return torch.empty((max(int(load().gbmm_band_workspace_bytes(B, n)), 256),), dtype=torch.uint8, device=device)
 
 
-def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode, want_maxes=False):
+def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode, want_maxes=False, want_token=False):
     """`_genbmm.forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode)` -> [out, indices, maxes].
 
     Only the outputs the mode defines are produced (the reference allocates and zero-fills all
     three every call, banded_cuda_kernel.cu:373-387); the others are returned as None, and the
     log mode's `maxes` only on request (the backward does not need it).
+    want_token=True appends a BandForwardToken (or None when the tensor-core path was not taken) that
+    `backward_band(reuse=...)` accepts.
     """
     _check_band(a, a_lu, a_lb, b, b_lu, b_lb)
     if mode not in (BAND_LOG, BAND_MAX, BAND_MUL):
         raise RuntimeError("unknown banded mode %r" % (mode,))
     B, n, Wa = a.shape
     Wo = Wa + b.shape[2] - 1
+    token = None
+
+    def result(out, idx, maxes):
+        return [out, idx, maxes, token] if want_token else [out, idx, maxes]
+
     with torch.cuda.device(a.device):
         out = torch.empty((B, n, Wo), dtype=a.dtype, device=a.device)
         idx = torch.empty((B, n, Wo), dtype=torch.int32, device=a.device) if mode == BAND_MAX else None
@@ -341,40 +373,43 @@ def forward_band(a, a_lu, a_lb, b, b_lu, b_lb, mode, want_maxes=False):
             st = load().gbmm_band_forward_f64(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), _ptr(idx),
                                               _ptr(maxes), B, n, _stream(a.device))
             _check(st, "gbmm_band_forward_f64")
-            return [out, idx, maxes]
+            return result(out, idx, maxes)
         if mode == BAND_MAX and load().gbmm_band_max_eligible(n, *bands):
             mx_ws = _band_max_workspace(B, n, bands, a.device)
             if mx_ws is not None:
                 st = load().gbmm_band_max_forward_f32(_ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), _ptr(idx),
                                                       B, n, _ptr(mx_ws), mx_ws.numel(), _stream(a.device))
                 _check(st, "gbmm_band_max_forward_f32")
-                return [out, idx, maxes]
-        tc_ws = None
+                return result(out, idx, maxes)
+        tc = None
         if maxes is None and load().gbmm_band_tc_eligible(mode, n, *bands):
-            tc_ws = _band_tc_workspace(mode, False, B, n, bands, a.device)
-        if tc_ws is not None:
+            tc = _band_tc_workspace(mode, False, B, n, bands, a.device)
+        if tc is not None:
+            tc.generation += 1
+            tc.holds = None
             st = load().gbmm_band_tc_forward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), B, n,
-                                                 _ptr(tc_ws), tc_ws.numel(), _stream(a.device))
+                                                 _ptr(tc.buf), tc.buf.numel(), _stream(a.device))
             _check(st, "gbmm_band_tc_forward_f32")
-            _band_tc_holds(tc_ws, _band_tc_tag(mode, a, b), store=True)
-            return [out, idx, maxes]
+            tc.holds = mode
+            token = BandForwardToken(tc, mode)
+            return result(out, idx, maxes)
         ws = _band_workspace(B, n, a.device) if mode == BAND_LOG else None
         st = load().gbmm_band_forward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(out), _ptr(idx),
                                           _ptr(maxes), B, n, _ptr(ws), 0 if ws is None else ws.numel(),
                                           _stream(a.device))
     _check(st, "gbmm_band_forward_f32")
-    return [out, idx, maxes]
+    return result(out, idx, maxes)
 
 
-def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=False, reuse_forward=False):
+def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=False, reuse=None):
     """`_genbmm.backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode)` -> [grad_a].
 
     With both=True returns [grad_a, grad_b], grad_b computed directly by a second kernel rather
     than by the reference's swap-and-transpose route (sparse.py:436-446).  `part` is the forward
     output (mode 0), the int32 or float indices in a's band coordinate (mode 1), ignored (mode 3).
-    reuse_forward=True (for callers that kept a and b alive and unmodified since `forward_band`, as autograd
-    does): when that forward was the last banded tensor-core call on this device and stream, its converted
-    operands, row maxima and guard flags are reused.
+    reuse = the BandForwardToken of the forward of these very operands (for callers that kept a and b alive
+    and unmodified since, as autograd does): while no other call has written into that forward's workspace,
+    its converted operands, row maxima and guard flags are reused instead of rebuilt.
     """
     _check_band(a, a_lu, a_lb, b, b_lu, b_lb)
     _check_input(grad_output, "grad_output", _compute_dtype(a))
@@ -401,21 +436,17 @@ def backward_band(a, a_lu, a_lb, b, b_lu, b_lb, grad_output, part, mode, both=Fa
             _check(st, "gbmm_band_backward_f64")
             return [grad_a, grad_b] if both else [grad_a]
         bands = (a_lu, a_lb, b_lu, b_lb)
-        tc_ws = None
+        tc = None
         if load().gbmm_band_tc_eligible(mode, n, *bands):
-            tc_ws = _band_tc_workspace(mode, True, B, n, bands, a.device)
-        if tc_ws is not None:
-            # the forward of these very operands (same storage, unmodified, same stream) may have been the last
-            # banded call on this device: its converted operands, row maxima and flags are still in place
-            ready = 1 if reuse_forward and _band_tc_holds(tc_ws, _band_tc_tag(mode, a, b)) else 0
+            tc = _band_tc_workspace(mode, True, B, n, bands, a.device)
+        if tc is not None:
+            ready = 1 if (reuse is not None and reuse.valid_for(tc, mode)) else 0
+            tc.generation += 1
+            tc.holds = None
             st = load().gbmm_band_tc_backward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(grad_output),
-                                                  _ptr(part), _ptr(grad_a), _ptr(grad_b), B, n, _ptr(tc_ws),
-                                                  tc_ws.numel(), ready, _stream(a.device))
+                                                  _ptr(part), _ptr(grad_a), _ptr(grad_b), B, n, _ptr(tc.buf),
+                                                  tc.buf.numel(), ready, _stream(a.device))
             _check(st, "gbmm_band_tc_backward_f32")
-            if not both:  # only b's copy is rebuilt when grad_b is not wanted (sum semiring)
-                _band_tc_holds(tc_ws, None, store=True)
-            else:
-                _band_tc_holds(tc_ws, _band_tc_tag(mode, a, b), store=True)
             return [grad_a, grad_b] if both else [grad_a]
         ws = _band_workspace(B, n, a.device) if mode == BAND_LOG else None
         st = load().gbmm_band_backward_f32(mode, _ptr(a), a_lu, a_lb, _ptr(b), b_lu, b_lb, _ptr(grad_output),

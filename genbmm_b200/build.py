@@ -69,7 +69,8 @@ def build(force=False, verbose=False):
         for _, log in results:
             sys.stderr.write(log)
     cmd = [_nvcc(), "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a",
-           "-Xcompiler", "-fPIC", "-o", LIB, *objs]
+           "-Xcompiler", "-fPIC", "-Xlinker", "--wrap=__cudaPushCallConfiguration", "-o", LIB, *objs]
+    # --wrap: every kernel launch of the library goes through the counter in csrc/capi.cu (gbmm_launch_count)
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (" ".join(cmd), r.stdout + r.stderr))

@@ -15,6 +15,7 @@ broadcast-reduce expression instead.
 """
 import torch
 import torch.distributed as dist
+from torch.autograd.function import once_differentiable
 
 
 def _default_bmm():
@@ -84,6 +85,7 @@ class _ChainMajor(torch.autograd.Function):
         return tuple(out)
 
     @staticmethod
+    @once_differentiable
     def backward(ctx, *grads):
         if ctx.maps is not None:
             from . import _native
@@ -140,7 +142,8 @@ class _Halves(torch.autograd.Function):
 class _PairLevel(torch.autograd.Function):
     """One level of the tree on the GPU: x (2p, B, C, C) -> (p, B, C, C), first half (x) second half, through the
     factorised tensor-core logbmm.  The backward hands the two halves of one gradient buffer to the kernels as
-    their outputs, so nothing is joined or copied.  First-order only."""
+    their outputs, so nothing is joined or copied.  First-order only: a double backward through this node raises
+    (pass `bmm=genbmm_b200.logbmm` to chain_product for second-order gradients; logbmm implements them)."""
 
     @staticmethod
     def forward(ctx, x):
@@ -150,10 +153,14 @@ class _PairLevel(torch.autograd.Function):
         left, right = x[:p].view(p * B, C, D), x[p:].view(p * B, C, D)
         out, rowmax, colmax, flags, factors = _native.logbmm_fast_forward(left, right, tensor_cores=True,
                                                                           keep_factors=True)
+        from .genmul import _keep_factors
+        if not _keep_factors(left, right):
+            factors = None      # the backward rebuilds them
         ctx.save_for_backward(x, out, rowmax, colmax, flags, factors)
         return out.view(p, B, C, D)
 
     @staticmethod
+    @once_differentiable
     def backward(ctx, g):
         from . import _native
         x, out, rowmax, colmax, flags, factors = ctx.saved_tensors

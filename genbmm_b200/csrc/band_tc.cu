@@ -551,8 +551,11 @@ int band_tc_forward(int mode, const float* a, const float* b, float* out, const 
   args.flags = w.flags;
   args.error = w.error;
   *flags_out = lg ? w.flags : nullptr;
-  return lg ? launch_band_tc<E_LOG, false, false>(w.A, w.Bm, args, B, st)
-            : launch_band_tc<E_SUM, false, false>(w.A, w.Bm, args, B, st);
+  rc = lg ? launch_band_tc<E_LOG, false, false>(w.A, w.Bm, args, B, st)
+          : launch_band_tc<E_SUM, false, false>(w.A, w.Bm, args, B, st);
+  if (rc != GBMM_OK) return rc;
+  // a product kernel that gave up on a bounded wait set the error word: the result becomes NaN
+  return launch_poison_on_error(w.error, out, B * d.n * d.Wo(), nullptr, 0, st);
 }
 
 int band_tc_backward(int mode, const float* a, const float* b, const float* g, const float* part, float* grad_a,
@@ -620,9 +623,11 @@ int band_tc_backward(int mode, const float* a, const float* b, const float* g, c
       band_scale_kernel<<<(unsigned)ceil_div(B * d.n, 8), 256, 0, st>>>(grad_b, b, w.rb, B * d.n, (int)d.n, d.b_lu,
                                                                       d.Wb());
       rc = launch_status();
+      if (rc != GBMM_OK) return rc;
     }
   }
-  return rc;
+  // a product kernel that gave up on a bounded wait set the error word: both gradients become NaN
+  return launch_poison_on_error(w.error, grad_a, B * d.n * d.Wa(), grad_b, B * d.n * d.Wb(), st);
 }
 
 }  // namespace gbmm

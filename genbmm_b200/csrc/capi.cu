@@ -13,7 +13,26 @@ extern "C" const char* gbmm_status_string(int status) {
   }
 }
 
-extern "C" int gbmm_abi_version(void) { return 1; }
+extern "C" int gbmm_abi_version(void) { return 2; }
+
+// ---- launch counter ------------------------------------------------------------------------------
+// Every `kernel<<<...>>>(...)` in this library compiles to a call of the runtime's launch-configuration push
+// followed by the launch itself.  The library is linked with `--wrap` on that symbol (genbmm_b200/build.py), so
+// every kernel launch any entry point makes passes through the function below exactly once: the count is of
+// launches actually issued, not an estimate kept beside them.  Memsets and copies are not kernels and are not
+// counted.
+#include <atomic>
+namespace gbmm {
+namespace {
+std::atomic<unsigned long long> g_launches{0};
+}
+}  // namespace gbmm
+extern "C" unsigned __real___cudaPushCallConfiguration(dim3 grid, dim3 block, size_t shared, struct CUstream_st* st);
+extern "C" unsigned __wrap___cudaPushCallConfiguration(dim3 grid, dim3 block, size_t shared, struct CUstream_st* st) {
+  gbmm::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return __real___cudaPushCallConfiguration(grid, block, shared, st);
+}
+extern "C" uint64_t gbmm_launch_count(void) { return gbmm::g_launches.load(std::memory_order_relaxed); }
 
 // Diagnostic timing of the product kernels of the factorised logbmm (FP32-pipe and tensor-core
 // variants).  While enabled, every gbmm_logbmm_* call brackets its product launch with CUDA
@@ -52,6 +71,30 @@ extern "C" float gbmm_profile_last_ms(int which) {
   if (cudaEventSynchronize(g_events[which][1]) != cudaSuccess) return -1.f;
   if (cudaEventElapsedTime(&ms, g_events[which][0], g_events[which][1]) != cudaSuccess) return -1.f;
   return ms;
+}
+
+// ---- NaN fill of an output whose product kernel gave up (see poison_if_failed in common.cuh) -------
+namespace gbmm {
+namespace {
+__global__ void __launch_bounds__(256) poison_on_error_kernel(const int* __restrict__ error, float* out0,
+                                                              int64_t count0, float* out1, int64_t count1) {
+  if (!poison_if_failed(error, out0, count0)) return;
+  poison_if_failed(error, out1, count1);
+}
+}  // namespace
+
+int launch_poison_on_error(const int* error, float* out0, int64_t count0, float* out1, int64_t count1,
+                           cudaStream_t st) {
+  unsigned grid = 0;
+  if (int rc = capped_grid(1LL << 20, &grid)) return rc;
+  poison_on_error_kernel<<<grid, 256, 0, st>>>(error, out0, count0, out1, count1);
+  return launch_status();
+}
+}  // namespace gbmm
+
+extern "C" int gbmm_poison_on_error(const int32_t* error_word, float* out, int64_t count, void* stream) {
+  if (!error_word || count < 0 || (count > 0 && !out)) return GBMM_ERR_INVALID_ARG;
+  return gbmm::launch_poison_on_error(error_word, out, count, nullptr, 0, static_cast<cudaStream_t>(stream));
 }
 
 // ---- block gather: the chain driver's layout changes ---------------------------------------------

@@ -38,6 +38,23 @@ __host__ __device__ __forceinline__ int64_t ceil_div(int64_t a, int64_t b) { ret
 bool profile_begin(int slot, cudaStream_t st);
 void profile_end(int slot, cudaStream_t st);
 
+// What a give-up looks like to the caller.  A product kernel whose bounded wait for a TMA copy or a tensor-core
+// commit ran out sets its call's error word and leaves an unknown part of its output unwritten.  The kernel that
+// follows it on the stream (the exact fix-up kernel where there is one, else poison_on_error_kernel) looks at
+// the word first and, when it is set, overwrites the WHOLE output with NaN, so the failure cannot be taken for
+// a result and no host synchronisation is needed to find out.  Returns true when it did (the caller returns).
+__device__ __forceinline__ bool poison_if_failed(const int* error, float* out, int64_t count) {
+  if (error == nullptr || *reinterpret_cast<const volatile int*>(error) == 0) return false;
+  const float nan = __int_as_float(0x7fc00000);
+  if (out != nullptr)
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x)
+      out[i] = nan;
+  return true;
+}
+// The stand-alone form (capi.cu): up to two outputs, either may be null.
+int launch_poison_on_error(const int* error, float* out0, int64_t count0, float* out1, int64_t count1,
+                           cudaStream_t st);
+
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? GBMM_OK : GBMM_ERR_LAUNCH; }
 
 // Work list of a fix-up kernel launched with a capped grid.  CTA c of G = gridDim.x looks at the tile ids

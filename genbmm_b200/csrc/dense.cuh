@@ -6,14 +6,16 @@ namespace gbmm {
 
 // Exact (SFU) log-sum-exp forward restricted to the 128x128 result tiles whose entry in
 // flags[batch][ceil(M/128)][ceil(N/128)] is non-zero; flags == nullptr means every tile.
+// `error` (with flags): the error word of the product kernel that ran before; when it is set the whole of `out`
+// is overwritten with NaN instead (poison_if_failed, common.cuh).
 int launch_log_fwd_flagged(const float* a, const float* b, float* out, const int* flags, int64_t B, int64_t M,
-                           int64_t K, int64_t N, cudaStream_t st);
+                           int64_t K, int64_t N, cudaStream_t st, const int* error = nullptr);
 
 // Exact log backward restricted to the terms of flagged result tiles, ADDED to grad_a and
-// grad_b (either may be null).
+// grad_b (either may be null).  `error`: as above, for both gradients.
 int launch_log_bwd_flagged(const float* a, const float* b, const float* c, const float* g, float* grad_a,
                            float* grad_b, const int* flags, int64_t B, int64_t M, int64_t K, int64_t N,
-                           cudaStream_t st);
+                           cudaStream_t st, const int* error = nullptr);
 
 // Row maxima of a and column maxima of b for the factorised logbmm (dense_fast.cu).
 int launch_rowcol_max(const float* a, const float* b, float* rowmax, float* colmax, int64_t B, int64_t M, int64_t K,

@@ -152,7 +152,8 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __rest
                                                              const float* __restrict__ g,
                                                              float* __restrict__ grad_a, int M, int K, int N,
                                                              int tiles_r, int tiles_c,
-                                                             const int* __restrict__ flags, int64_t total) {
+                                                             const int* __restrict__ flags, int64_t total,
+                                                             const int* error, int64_t out_count) {
   __shared__ __align__(16) float sc[2][BK * LDR];
   __shared__ __align__(16) float sg[2][BK * LDR];
   __shared__ __align__(16) float sb[2][BK * LDC];
@@ -161,6 +162,8 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_a_kernel(const float* __rest
                           tiles_r, flags);
     return;
   }
+  // the product kernel before this one gave up on a bounded wait: the whole gradient becomes NaN
+  if (poison_if_failed(error, grad_a, out_count)) return;
   __shared__ int list[NT];
   __shared__ int count;
   const int ngrp = (N + 127) / 128;
@@ -264,7 +267,8 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __rest
                                                              const float* __restrict__ g,
                                                              float* __restrict__ grad_b, int M, int K, int N,
                                                              int tiles_r, int tiles_c,
-                                                             const int* __restrict__ flags, int64_t total) {
+                                                             const int* __restrict__ flags, int64_t total,
+                                                             const int* error, int64_t out_count) {
   __shared__ __align__(16) float sa[2][BK * LDR];
   __shared__ __align__(16) float sc[2][BK * LDC];
   __shared__ __align__(16) float sg[2][BK * LDC];
@@ -272,6 +276,7 @@ __global__ void __launch_bounds__(NT) dense_log_bwd_b_kernel(const float* __rest
     log_bwd_b_tile<false>(TileCoord(blockIdx.x, tiles_r, tiles_c), sa, sc, sg, a, b, c, g, grad_b, M, K, N, flags);
     return;
   }
+  if (poison_if_failed(error, grad_b, out_count)) return;
   __shared__ int list[NT];
   __shared__ int count;
   const int ngrp = (M + 127) / 128, fpitch = (N + 127) / 128;
@@ -440,14 +445,15 @@ namespace gbmm {
 // grad_a / grad_b (see dense.cuh).
 int launch_log_bwd_flagged(const float* a, const float* b, const float* c, const float* g, float* grad_a,
                            float* grad_b, const int* flags, int64_t B, int64_t M, int64_t K, int64_t N,
-                           cudaStream_t st) {
+                           cudaStream_t st, const int* error) {
   const int m = (int)M, k = (int)K, n = (int)N;
   if (grad_a) {
     const int64_t tr = ceil_div(M, BR), tcn = ceil_div(K, BC), blocks = B * tr * tcn;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
     unsigned grid = 0;
     if (int rc = capped_grid(blocks, &grid)) return rc;
-    dense_log_bwd_a_kernel<true><<<grid, NT, 0, st>>>(a, b, c, g, grad_a, m, k, n, (int)tr, (int)tcn, flags, blocks);
+    dense_log_bwd_a_kernel<true><<<grid, NT, 0, st>>>(a, b, c, g, grad_a, m, k, n, (int)tr, (int)tcn, flags, blocks,
+                                                      error, B * M * K);
     if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
   }
   if (grad_b) {
@@ -455,7 +461,8 @@ int launch_log_bwd_flagged(const float* a, const float* b, const float* c, const
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
     unsigned grid = 0;
     if (int rc = capped_grid(blocks, &grid)) return rc;
-    dense_log_bwd_b_kernel<true><<<grid, NT, 0, st>>>(a, b, c, g, grad_b, m, k, n, (int)tr, (int)tcn, flags, blocks);
+    dense_log_bwd_b_kernel<true><<<grid, NT, 0, st>>>(a, b, c, g, grad_b, m, k, n, (int)tr, (int)tcn, flags, blocks,
+                                                      error, B * K * N);
   }
   return launch_status();
 }
@@ -487,14 +494,14 @@ extern "C" int gbmm_dense_backward_f32(int mode, const float* a, const float* b,
       const int64_t tr = ceil_div(M, BR), tcn = ceil_div(K, BC), blocks = B * tr * tcn;
       if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
       dense_log_bwd_a_kernel<false><<<(unsigned)blocks, NT, 0, st>>>(a, b, part, grad_out, grad_a, m, k, n,
-                                                                     (int)tr, (int)tcn, nullptr, blocks);
+                                                                     (int)tr, (int)tcn, nullptr, blocks, nullptr, 0);
       if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
     }
     if (grad_b) {
       const int64_t tr = ceil_div(K, BR), tcn = ceil_div(N, BC), blocks = B * tr * tcn;
       if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
       dense_log_bwd_b_kernel<false><<<(unsigned)blocks, NT, 0, st>>>(a, b, part, grad_out, grad_b, m, k, n,
-                                                                     (int)tr, (int)tcn, nullptr, blocks);
+                                                                     (int)tr, (int)tcn, nullptr, blocks, nullptr, 0);
     }
     return launch_status();
   }

@@ -300,9 +300,14 @@ __global__ void __launch_bounds__(GNT, 2) sgemm_tn_kernel(const __grid_constant_
   }
   if (fail) {
     // give the copies still in flight a bounded chance to land before the CTA's shared memory
-    // is released, record the failure, write nothing
+    // is released, record the failure, write no result
     for (int u = t + 1; u < nt && u < t + GS; ++u) mbar_wait_bounded(&sm.full[u % GS], (u / GS) & 1);
-    if (tid == 0) atomicExch(ep.error, 1);
+    // the fix-up kernel that follows sees the word and turns the whole result into NaN; the tile's guard
+    // flag is still written so that nothing downstream ever reads a stale one
+    if (tid == 0) {
+      atomicExch(ep.error, 1);
+      if (EPI == EPI_LOG) ep.flags[blockIdx.x] = 0;
+    }
     return;
   }
 
@@ -472,7 +477,7 @@ extern "C" int gbmm_logbmm_forward_f32(const float* a, const float* b, float* ou
   EpiParams ep{out, rowmax, colmax, nullptr, flags, error};
   rc = launch_gemm<EPI_LOG>(eat, pad4(M), eb, pad4(N), ep, B, K, M, N, st, 0);
   if (rc != GBMM_OK) return rc;
-  return launch_log_fwd_flagged(a, b, out, flags, B, M, K, N, st);
+  return launch_log_fwd_flagged(a, b, out, flags, B, M, K, N, st, error);
 }
 
 extern "C" int gbmm_logbmm_backward_f32(const float* a, const float* b, const float* grad_out, const float* out,
@@ -513,7 +518,7 @@ extern "C" int gbmm_logbmm_backward_f32(const float* a, const float* b, const fl
     rc = launch_gemm<EPI_GRAD>(ea, pad4(K), gp, pad4(N), ep, B, M, K, N, st, 2);
     if (rc != GBMM_OK) return rc;
   }
-  return launch_log_bwd_flagged(a, b, out, grad_out, grad_a, grad_b, flags, B, M, K, N, st);
+  return launch_log_bwd_flagged(a, b, out, grad_out, grad_a, grad_b, flags, B, M, K, N, st, error);
 }
 
 // Blocks until the stream's work is done and returns GBMM_ERR_LAUNCH if a kernel of the fast
@@ -613,5 +618,12 @@ extern "C" int gbmm_logbmm_forward_noalloc_f32(const float* a, const float* b, f
   sgemm_tn_kernel<EPI_LOG, true><<<(unsigned)blocks, GNT, smem, st>>>(mx, my, ep, (int)K, (int)M, (int)N,
                                                                       (int)ti, (int)tj);
   if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
-  return launch_log_fwd_flagged(a, b, out, flags, B, M, K, N, st);
+  return launch_log_fwd_flagged(a, b, out, flags, B, M, K, N, st, error);
+}
+
+extern "C" int gbmm_logbmm_forward_noalloc_check(void* stream) {
+  void* base = nullptr;
+  int rc = noalloc_scratch(&base);
+  if (rc != GBMM_OK) return rc;
+  return gbmm_logbmm_check(base, stream);  // the error word is the first word of the array
 }

@@ -487,13 +487,16 @@ __global__ void __launch_bounds__(NT) dense_log_fwd_kernel(const float* __restri
                                                            float* __restrict__ out,
                                                            float* __restrict__ maxes, int M, int K, int N,
                                                            int tiles_m, int tiles_n,
-                                                           const int* __restrict__ flags, int64_t total) {
+                                                           const int* __restrict__ flags, int64_t total,
+                                                           const int* error, int64_t out_count) {
   __shared__ __align__(16) float sx[2][BK * LDX];
   __shared__ __align__(16) float sy[2][BK * LDY];
   if (!FLAGGED) {
     log_fwd_tile(TileCoord(blockIdx.x, tiles_m, tiles_n), sx, sy, a, b, out, maxes, M, K, N);
     return;
   }
+  // the product kernel before this one gave up on a bounded wait: the whole result becomes NaN
+  if (poison_if_failed(error, out, out_count)) return;
   __shared__ int list[NT];
   __shared__ int count;
   const int fm = (M + 127) / 128, fn = (N + 127) / 128;
@@ -602,18 +605,19 @@ __global__ void __launch_bounds__(NT) dense_sample_pick_kernel(const float* __re
 namespace gbmm {
 // Exact log-sum-exp of the result tiles marked in `flags` (all tiles when flags is null).
 int launch_log_fwd_flagged(const float* a, const float* b, float* out, const int* flags, int64_t B, int64_t M,
-                           int64_t K, int64_t N, cudaStream_t st) {
+                           int64_t K, int64_t N, cudaStream_t st, const int* error) {
   const int64_t tiles_m = ceil_div(M, BM), tiles_n = ceil_div(N, BN), blocks = B * tiles_m * tiles_n;
   if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
   if (!flags) {
     dense_log_fwd_kernel<false><<<(unsigned)blocks, NT, 0, st>>>(a, b, out, nullptr, (int)M, (int)K, (int)N,
-                                                                 (int)tiles_m, (int)tiles_n, nullptr, blocks);
+                                                                 (int)tiles_m, (int)tiles_n, nullptr, blocks,
+                                                                 nullptr, 0);
     return launch_status();
   }
   unsigned grid = 0;
   if (int rc = capped_grid(blocks, &grid)) return rc;
   dense_log_fwd_kernel<true><<<grid, NT, 0, st>>>(a, b, out, nullptr, (int)M, (int)K, (int)N, (int)tiles_m,
-                                                  (int)tiles_n, flags, blocks);
+                                                  (int)tiles_n, flags, blocks, error, B * M * N);
   return launch_status();
 }
 }  // namespace gbmm
@@ -660,7 +664,7 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
   switch (mode) {
     case GBMM_MODE_LOG:
       dense_log_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, static_cast<float*>(aux), m, k, n, tm, tn, nullptr,
-                                                          blocks);
+                                                          blocks, nullptr, 0);
       break;
     case GBMM_MODE_MAX:
     case GBMM_MODE_PRODMAX: {
@@ -691,7 +695,8 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
       break;
     }
     case GBMM_MODE_SAMPLE:
-      dense_log_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, nullptr, m, k, n, tm, tn, nullptr, blocks);
+      dense_log_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, nullptr, m, k, n, tm, tn, nullptr, blocks,
+                                                          nullptr, 0);
       if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
       dense_sample_pick_kernel<<<grid, block, 0, st>>>(a, b, u, out, static_cast<int*>(aux), m, k, n, tm, tn);
       break;

@@ -13,17 +13,20 @@
 // result indices), so the three products of a step all read EA, EB and G' in the layout a, b and
 // grad_out already have and no transposed copy is made.
 //
-// CTA = 6 warps: warp 0 issues the TMA loads, warp 1 owns the TMEM allocation and issues the
-// MMAs (one elected lane each), warps 2-5 read the accumulator back with tcgen05.ld (each warp
-// its own 32-lane quarter) and write log(S) + ra + rb (or the gradient) to global memory.
+// Two kernels share this scheme.  tc_gemm_kernel: one persistent CTA per SM on 128x128 tiles (cta_group::1).
+// tc_pair_gemm_kernel: a cluster of two CTAs on a 256x256 tile (cta_group::2 loads and MMAs; the only
+// cluster-multicast instruction is the tcgen05.commit barrier arrive, never a load).  In both, warp 0 issues
+// the TMA loads, warp 1 owns the TMEM allocation and issues the MMAs (one elected lane each), the remaining
+// warps read the accumulator back with tcgen05.ld (each its own 32-lane quarter) and write log(S) + ra + rb
+// (or the gradient) to global memory.
 // The tensor core adds into its fp32 accumulator with truncation, an error that grows with the
 // length of the sum; so the reduction is cut into chunks of 256 steps, each accumulated in one of
 // two TMEM buffers and then added, in round-to-nearest fp32, to per-thread register sums by the
 // epilogue warps while the MMAs fill the other buffer.
 // Stages are handed over with mbarriers (full: TMA -> MMA; empty: tcgen05.commit -> TMA;
 // chunk_full: commit -> epilogue; chunk_empty: epilogue -> MMA).  Every wait is bounded; a wait that gives up sets the error
-// word, and all paths meet at the final barrier so that the TMEM columns are always released.
-// No cluster launch, no multicast, cta_group::1 only.
+// word, and all paths meet at the final barrier so that the TMEM columns are always released.  Every load reads
+// this GPU's own memory; no TMA load uses cluster multicast.
 #include <cstdlib>
 
 #include "dense.cuh"
@@ -881,7 +884,7 @@ extern "C" int gbmm_logbmm_tc_forward_f32(const float* a, const float* b, float*
   rc = launch_tc<TC_LOG, false, true>(TcOperand{f.ea_hi, f.ea_lo, M, K, pad32(K)},
                                       TcOperand{f.eb_hi, f.eb_lo, K, N, pad32(N)}, ep, B, K, M, N, st, 0);
   if (rc != GBMM_OK) return rc;
-  return launch_log_fwd_flagged(a, b, out, flags, B, M, K, N, st);
+  return launch_log_fwd_flagged(a, b, out, flags, B, M, K, N, st, error);
 }
 
 extern "C" int gbmm_logbmm_tc_backward_f32(const float* a, const float* b, const float* grad_out, const float* out,
@@ -929,5 +932,5 @@ extern "C" int gbmm_logbmm_tc_backward_f32(const float* a, const float* b, const
     rc = launch_tc<TC_GRAD, true, true>(EA, GP, ep, B, M, K, N, st, 2);
     if (rc != GBMM_OK) return rc;
   }
-  return launch_log_bwd_flagged(a, b, out, grad_out, grad_a, grad_b, flags, B, M, K, N, st);
+  return launch_log_bwd_flagged(a, b, out, grad_out, grad_a, grad_b, flags, B, M, K, N, st, error);
 }

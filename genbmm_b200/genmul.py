@@ -7,8 +7,8 @@ an optional third argument, the uniforms that drive the sample.
 
 Differences from the reference that a caller can observe:
   * the logbmm backward makes no transposed copies (genmul.py:38-41 makes six);
-  * half / bfloat16 inputs are computed in float32 and cast back; float64 is rejected
-    (the kernels are fp32);
+  * half / bfloat16 inputs are computed in float32 and cast back; float64 runs float64 kernels of its own
+    (plain tiled ones: a checking path, not a fast one);
   * inputs must be contiguous CUDA tensors, as in the reference (matmul_cuda.cpp:65-67).
 """
 import os
@@ -45,6 +45,22 @@ def _log_path(M, K, N):
     if mode == "tensor":
         return "tensor"
     return "tensor" if M * K * N >= 128 * 128 * 64 else "exact"
+
+
+def _keep_factors(a, b):
+    """Whether the tensor-core forward's split exponentiated operands (four times the bytes of a and b) stay
+    alive until the backward, which then does not rebuild them (two HBM-bound passes saved).  The reference
+    saves only a, b, out and maxes, and a chain of products keeps one such set per product alive, so large ones
+    are kept only while the device has room for them several times over.
+    GENBMM_B200_KEEP_FACTORS=1 always keeps them, =0 never does."""
+    mode = os.environ.get("GENBMM_B200_KEEP_FACTORS", "auto")
+    if mode in ("0", "1"):
+        return mode == "1"
+    nbytes = 4 * (a.numel() + b.numel()) * 4
+    if nbytes <= (1 << 30):
+        return True
+    free, _ = torch.cuda.mem_get_info(a.device)
+    return free >= 4 * nbytes
 
 
 class LogMatMulBack(torch.autograd.Function):
@@ -85,9 +101,7 @@ class LogMatMul(torch.autograd.Function):
             path = "exact"  # the factorised paths are float32 kernels
         if path != "exact":
             tc = path == "tensor"
-            # the split exponentiated operands (4x the size of a and b) stay alive until the backward
-            # unless GENBMM_B200_KEEP_FACTORS=0, in which case the backward rebuilds them
-            keep = tc and os.environ.get("GENBMM_B200_KEEP_FACTORS", "1") != "0"
+            keep = tc and _keep_factors(a32, b32)
             out, rowmax, colmax, flags, factors = _native.logbmm_fast_forward(a32, b32, tensor_cores=tc,
                                                                               keep_factors=True)
             ctx.aux = (rowmax, colmax, flags, tc, factors if keep else None)

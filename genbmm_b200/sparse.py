@@ -186,7 +186,7 @@ class _BandedProduct(torch.autograd.Function):
     def _forward(cls, ctx, a, a_lu, a_ld, b, b_lu, b_ld, o_lu, o_ld):
         a = a.contiguous()
         b = b.contiguous()
-        out, idx, _ = _native.forward_band(a, a_lu, a_ld, b, b_lu, b_ld, cls.MODE)
+        out, idx, _, ctx.token = _native.forward_band(a, a_lu, a_ld, b, b_lu, b_ld, cls.MODE, want_token=True)
         ctx.bands = (a_lu, a_ld, b_lu, b_ld)
         if cls.MODE == _native.BAND_MAX:
             ctx.save_for_backward(a, b, idx)
@@ -203,7 +203,7 @@ class _BandedProduct(torch.autograd.Function):
         a, b = saved[0], saved[1]
         part = saved[2].detach() if len(saved) > 2 else None
         grad_a, grad_b = _native.backward_band(a, a_lu, a_ld, b, b_lu, b_ld, grad_output.contiguous(), part,
-                                               cls.MODE, both=True, reuse_forward=True)
+                                               cls.MODE, both=True, reuse=ctx.token)
         return grad_a, None, None, grad_b, None, None, None, None
 
 
@@ -224,12 +224,12 @@ class BandedLogMulBack(torch.autograd.Function):
     forward returns (grad_a, grad_b), backward the second-order terms."""
 
     @staticmethod
-    def forward(ctx, a, b, grad_out, part, bands):
+    def forward(ctx, a, b, grad_out, part, bands, token=None):
         ctx.save_for_backward(a, b, grad_out, part)
         ctx.bands = bands
         a_lu, a_ld, b_lu, b_ld = bands
         grad_a, grad_b = _native.backward_band(a, a_lu, a_ld, b, b_lu, b_ld, grad_out, part, _native.BAND_LOG,
-                                               both=True, reuse_forward=True)
+                                               both=True, reuse=token)
         return grad_a, grad_b
 
     @staticmethod
@@ -237,7 +237,7 @@ class BandedLogMulBack(torch.autograd.Function):
         a, b, grad_out, part = ctx.saved_tensors
         a_lu, a_ld, b_lu, b_ld = ctx.bands
         d_a, d_b, d_g = _native.backbackward_band(a, a_lu, a_ld, b, b_lu, b_ld, grad_out, part, None, h_a, 0, h_b)
-        return d_a, d_b, d_g, None, None
+        return d_a, d_b, d_g, None, None, None
 
 
 class BandedLogMul(_BandedProduct):
@@ -250,7 +250,7 @@ class BandedLogMul(_BandedProduct):
     @staticmethod
     def backward(ctx, grad_output):
         a, b, out = ctx.saved_tensors
-        grad_a, grad_b = BandedLogMulBack.apply(a, b, grad_output.contiguous(), out.detach(), ctx.bands)
+        grad_a, grad_b = BandedLogMulBack.apply(a, b, grad_output.contiguous(), out.detach(), ctx.bands, ctx.token)
         return grad_a, None, None, grad_b, None, None, None, None
 
 

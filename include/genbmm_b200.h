@@ -237,10 +237,24 @@ int gbmm_logbmm_backward_f32(const float* a, const float* b, const float* grad_o
                              const float* rowmax, const float* colmax, const int32_t* flags,
                              float* grad_a, float* grad_b, void* workspace, int64_t workspace_bytes,
                              int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
-/* Synchronises the stream and reports whether a kernel of the fast path gave up on a bounded
- * wait for a TMA copy (GBMM_ERR_LAUNCH; its outputs are then invalid).  `workspace` is the one
- * passed to the call being checked.  Diagnostic; not needed in normal operation. */
+/* What happens when a kernel of a fast path gives up.  Every wait inside the TMA / tcgen05 product kernels
+ * (dense and banded) is bounded; a wait that runs out sets the first word of the call's workspace, and the kernel
+ * that follows on the stream then overwrites the WHOLE output of that product with NaN.  A caller therefore never
+ * receives a partly written result that looks valid, and needs no host synchronisation to be safe.
+ * gbmm_logbmm_check is the diagnostic on top of that: it synchronises the stream and returns GBMM_ERR_LAUNCH when
+ * the word is set.  `workspace` is the one passed to the call being checked (gbmm_logbmm_*_f32,
+ * gbmm_logbmm_tc_*_f32 or gbmm_band_tc_*_f32). */
 int gbmm_logbmm_check(const void* workspace, void* stream);
+
+/* The NaN fill described above as a call of its own: if *error_word (device memory) is non-zero when the kernel
+ * runs, out[0..count) becomes NaN, otherwise nothing is written.  The fast paths apply it themselves; it is
+ * exported for callers that chain their own kernels behind a workspace's error word, and for tests. */
+int gbmm_poison_on_error(const int32_t* error_word, float* out, int64_t count, void* stream);
+
+/* Number of kernel launches this library has issued in this process (all entry points, all threads).  The
+ * library's link step routes every launch through the counter, so the difference between two reads is the exact
+ * number of kernels launched in between.  No counterpart in the reference. */
+uint64_t gbmm_launch_count(void);
 
 /*
  * Tensor-core variants of gbmm_logbmm_forward_f32 / _backward_f32: the same factorised products computed as
@@ -293,6 +307,10 @@ int64_t gbmm_logbmm_forward_noalloc_max_bytes(void);
 int64_t gbmm_logbmm_forward_noalloc_need_bytes(int64_t B, int64_t M, int64_t K, int64_t N);
 int gbmm_logbmm_forward_noalloc_f32(const float* a, const float* b, float* out,
                                     int64_t B, int64_t M, int64_t K, int64_t N, void* stream);
+/* gbmm_logbmm_check for the built-in scratch (the caller has no workspace pointer to pass): synchronises the
+ * stream, returns GBMM_ERR_LAUNCH if the last no-allocation call on the current device gave up on a bounded
+ * wait (its `out` is then all NaN, see gbmm_logbmm_check).  Allocates nothing. */
+int gbmm_logbmm_forward_noalloc_check(void* stream);
 
 /*
  * Layout helper of the chain (CRF) driver, no counterpart in the reference: dst block d <- src block map[d],

@@ -246,3 +246,36 @@ def crf_log_partition(pot):
     logz = p.flatten(1).logsumexp(1)
     grad, = torch.autograd.grad(logz.sum(), pot)
     return logz.detach(), grad
+
+
+def crf_alpha_beta(pot):
+    """(logZ, edge marginals) of ONE chain, pot:(L, C, C), by the forward-backward recursions in float64
+    numpy — O(L C^2) time and memory, so the full benchmark size (L = 511, C = 256) takes a second, where
+    autograd through a float64 chain product would hold every intermediate.
+
+    With alpha_t[j] = log-mass of the prefixes that end edge t in state j and beta_t[j] = log-mass of the
+    suffixes that follow edge t from state j,
+
+        alpha_t[j] = logsumexp_i alpha_{t-1}[i] + pot[t, i, j]      (alpha_{-1} = 0)
+        beta_t[i]  = logsumexp_j pot[t+1, i, j] + beta_{t+1}[j]     (beta_{L-1} = 0)
+        logZ       = logsumexp_j alpha_{L-1}[j]
+        marginal[t, i, j] = exp(alpha_{t-1}[i] + pot[t, i, j] + beta_t[j] - logZ)
+
+    which is d logZ / d pot[t, i, j] for logZ = logsumexp of all entries of the chain product, the
+    definition `crf_log_partition` differentiates; tests check the two against each other."""
+    p = _np(pot, np.float64)
+    L, C, _ = p.shape
+
+    def lse(x, axis):
+        m = x.max(axis=axis, keepdims=True)
+        return (m + np.log(np.exp(x - m).sum(axis=axis, keepdims=True))).squeeze(axis)
+
+    alpha = np.zeros((L + 1, C))          # alpha[t + 1] = alpha_t, alpha[0] = alpha_{-1} = 0
+    for t in range(L):
+        alpha[t + 1] = lse(alpha[t][:, None] + p[t], 0)
+    beta = np.zeros((L, C))
+    for t in range(L - 2, -1, -1):
+        beta[t] = lse(p[t + 1] + beta[t + 1][None, :], 1)
+    logz = lse(alpha[L], 0)
+    marg = np.exp(alpha[:L, :, None] + p + beta[:, None, :] - logz)
+    return float(logz), marg

@@ -27,6 +27,18 @@ def test_tree_equals_sequential_chain_on_cpu(B, L, C):
     assert torch.allclose(marg.sum((2, 3)), torch.ones(B, L, dtype=torch.float64))
 
 
+@pytest.mark.parametrize("L,C", [(1, 3), (2, 4), (13, 5), (40, 7)])
+def test_alpha_beta_recursions_equal_autograd_of_the_chain_product(L, C):
+    """The memory-light float64 checker used at the full benchmark size against the autograd one."""
+    gen = torch.Generator().manual_seed(L * 10 + C)
+    pot = torch.randn(2, L, C, C, generator=gen, dtype=torch.float64)
+    want_z, want_m = oracle.crf_log_partition(pot)
+    for b in range(2):
+        z, m = oracle.crf_alpha_beta(pot[b])
+        assert abs(z - float(want_z[b])) <= 1e-12 * max(1.0, abs(z))
+        assert np.allclose(m, want_m[b].numpy(), rtol=1e-10, atol=1e-14)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -139,9 +139,9 @@ def test_config5_full_size(gb):
                 t_out, _, _, t_dA, t_dB = oracle.band_fwd_bwd(3, a[:1].abs(), lu, ld, b[:1].abs(), lu, ld, g[:1].abs(),
                                                               dtype=np.float64)
                 bound = (t_out, t_dA, t_dB)
-            assert_close(out[:1], wout, 1e-5, 2e-5, term_sum=bound[0])
-            assert_close(ga[:1], dA, 1e-5, 2e-5, term_sum=bound[1])
-            assert_close(gb_[:1], dB, 1e-5, 2e-5, term_sum=bound[2])
+            assert_close(out[:1], wout, term_sum=bound[0])
+            assert_close(ga[:1], dA, term_sum=bound[1])
+            assert_close(gb_[:1], dB, term_sum=bound[2])
     # linearity of the ordinary product at full size
     out1 = _native.forward_band(ad, lu, ld, bd, lu, ld, 3)[0]
     out2 = _native.forward_band(2 * ad, lu, ld, bd, lu, ld, 3)[0]
@@ -171,9 +171,9 @@ def test_wide_band_falls_back_to_global_reads(gb):
         if mode == 3:
             t_out, _, _, t_dA, t_dB = oracle.band_fwd_bwd(3, a.abs(), lu, ld, b.abs(), lu, ld, g.abs(), dtype=np.float64)
             bound = (t_out, t_dA, t_dB)
-        assert_close(r.data, out, 1e-5, 2e-5, what=method, term_sum=bound[0])
-        assert_close(ga, dA, 1e-5, 2e-5, what=method + " grad_a", term_sum=bound[1])
-        assert_close(gb_, dB, 1e-5, 2e-5, what=method + " grad_b", term_sum=bound[2])
+        assert_close(r.data, out, what=method, term_sum=bound[0])
+        assert_close(ga, dA, what=method + " grad_a", term_sum=bound[1])
+        assert_close(gb_, dB, what=method + " grad_b", term_sum=bound[2])
 
 
 def test_band_rejects_bad_inputs(gb):
@@ -198,14 +198,18 @@ def test_band_log_guard_recomputes_flagged_row_blocks(gb, monkeypatch, lu, ld):
     b[:, 40:120, lu:] -= 300.0      # ... the b rows they meet live on the lower half
     out, ga, gb_ = run(gb, "multiply_log", a, lu, ld, b, lu, ld, g)
     want, _, _, dA, dB = oracle.band_fwd_bwd(0, a, lu, ld, b, lu, ld, g, dtype=np.float64)
-    assert_close(out.data, want, 1e-5, 2e-5, "fwd")
-    assert_close(ga, dA, 3e-4, 1e-5, "grad_a")
-    assert_close(gb_, dB, 3e-4, 1e-5, "grad_b")
+    # results near -300 are stored with the float32 spacing there (3e-5), and so is a + b: the weights
+    # exp(a + b - out) of any float32 implementation inherit that as a relative error
+    rtol_w = 1e-5 + 2 * float(np.spacing(np.float32(np.abs(want).max())))
+    assert 5e-5 < rtol_w < 1e-4
+    assert_close(out.data, want, what="fwd")
+    assert_close(ga, dA, rtol_w, what="grad_a")
+    assert_close(gb_, dB, rtol_w, what="grad_b")
     # and the exact kernels alone agree
     monkeypatch.setenv("GENBMM_B200_BANDLOG", "exact")
     out2, ga2, gb2 = run(gb, "multiply_log", a, lu, ld, b, lu, ld, g)
-    assert torch.allclose(out.data, out2.data, rtol=1e-5, atol=2e-5)
-    assert torch.allclose(ga, ga2, rtol=3e-4, atol=1e-5) and torch.allclose(gb_, gb2, rtol=3e-4, atol=1e-5)
+    assert torch.allclose(out.data, out2.data, rtol=1e-5, atol=2e-6)
+    assert torch.allclose(ga, ga2, rtol=rtol_w, atol=2e-6) and torch.allclose(gb_, gb2, rtol=rtol_w, atol=2e-6)
 
 
 @pytest.mark.parametrize("ci", [0, 1, 2, 3, 4])

@@ -130,3 +130,21 @@ def test_band_layout_operations():
             assert torch.equal(un.data[:, :, 1:], x.data[:, :, :-1])
     y = gb.BandedMatrix(torch.zeros(1, 3, 3), 1, 1, fill=-1e9)
     assert (y.band_pad(1).data[:, :, 0] == -1e9).all() and (y.to_dense()[0, 0, 2] == -1e9)
+
+
+def test_band_forward_token_is_valid_only_until_the_workspace_is_written_again():
+    """Host logic of the operand reuse between a banded forward and its backward (no GPU involved)."""
+    from genbmm_b200 import _native
+    ws = _native._Workspace((2, 128, 20, 20, 20, 20), None)
+    ws.generation, ws.holds = 5, 0
+    tok = _native.BandForwardToken(ws, 0)
+    assert tok.valid_for(ws, 0)
+    assert not tok.valid_for(ws, 3)                       # another semiring's copies
+    other = _native._Workspace(ws.dims, None)
+    other.generation, other.holds = 5, 0
+    assert not tok.valid_for(other, 0)                    # another stream's (or a rebuilt) workspace
+    ws.generation += 1                                    # any later call that writes into it
+    assert not tok.valid_for(ws, 0)
+    ws.generation -= 1
+    ws.holds = None                                       # a call that left the copies incomplete
+    assert not tok.valid_for(ws, 0)

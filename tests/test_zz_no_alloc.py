@@ -7,8 +7,11 @@ pointers, twice in a row with different problems (the array keeps the first call
 when the second starts), and compares with the existing forward entry point.  This file sorts
 last on purpose so that a stop-at-first-failure run has already run every other test.
 """
+import numpy as np
 import pytest
 import torch
+
+import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -43,9 +46,12 @@ def test_no_alloc_forward_matches_the_allocating_entry_points():
         _call(lib, a, b, out)
     torch.cuda.synchronize()
     assert torch.cuda.mem_get_info()[0] == free_before   # the two calls reserved no device memory
-    for got, (want_exact, want_fast) in zip(outs, wants):
+    for got, (want_exact, want_fast), (a, b) in zip(outs, wants, (first, second)):
         assert torch.allclose(got, want_exact, rtol=RTOL, atol=ATOL)
         assert torch.equal(got, want_fast)   # same kernels, same arithmetic
+        # and against the float64 CPU oracle, like every other forward in this suite
+        want = oracle.dense_fwd(0, a.cpu(), b.cpu(), dtype=np.float64)[0]
+        assert np.allclose(got.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
 
 
 def test_no_alloc_forward_rejects_what_does_not_fit():

@@ -92,3 +92,15 @@ def assert_valid_sample(a, b, u, idx, tol=1e-5):
         detail = ["%s idx=%d u=%.8f lo=%.8f hi=%.8f" % (tuple(i), idx[tuple(i)], u[tuple(i)], lo[tuple(i)],
                                                       hi[tuple(i)]) for i in w]
         raise AssertionError("%d sampled indices do not bracket their uniform: %s" % (bad.sum(), "; ".join(detail)))
+
+
+def rel_err(got, want, term_sum=None, rtol=RTOL, atol=ATOL):
+    """The largest error in units in which `assert_close` passes at `rtol`: max |got - want| / (atol / rtol +
+    |want|), the denominator widened to term_sum / 10 where that is larger (1e-6 of the terms' magnitudes)."""
+    got = got.detach().cpu().numpy() if hasattr(got, "detach") else np.asarray(got)
+    want = np.asarray(want, dtype=np.float64)
+    den = atol / rtol + np.abs(want)
+    if term_sum is not None:
+        den = np.maximum(den, np.asarray(term_sum, dtype=np.float64) * (1e-6 / rtol))
+    err = np.abs(got.astype(np.float64) - want) / den
+    return float(np.nanmax(err)) if err.size else 0.0
