@@ -56,16 +56,18 @@ class _ChainMajor(torch.autograd.Function):
     In that order the matrices at even positions are the first half and the ones at odd positions the second
     half, and the pairwise products come out in the bit-reversed order of their own index, so every level of
     the tree multiplies the first half by the second half: contiguous views, no copies.  Padding matrices are
-    the semiring's identity (0 on the diagonal, -1e9 elsewhere).  The backward writes every run's gradient
-    into one buffer."""
+    the semiring's identity (0 on the diagonal, -1e9 elsewhere).  first_order_only=True (GPU, float32, one
+    run) moves the matrices with the library's block gather in both directions; otherwise both directions
+    are torch operations and second-order gradients pass through."""
 
     @staticmethod
-    def forward(ctx, pot):
+    def forward(ctx, pot, first_order_only=False):
         ctx.shape = pot.shape
         B, L, C, D = pot.shape
         runs = _runs(L)
         ctx.maps = None
-        if pot.is_cuda and pot.dtype == torch.float32 and pot.is_contiguous() and len(runs) == 1 and (C * D) % 4 == 0:
+        if (first_order_only and pot.is_cuda and pot.dtype == torch.float32 and pot.is_contiguous()
+                and len(runs) == 1 and (C * D) % 4 == 0):
             # one pass of the library's block gather instead of torch's strided copies
             from . import _native
             n = runs[0][2]
@@ -85,18 +87,16 @@ class _ChainMajor(torch.autograd.Function):
         return tuple(out)
 
     @staticmethod
-    @once_differentiable
     def backward(ctx, *grads):
         if ctx.maps is not None:
+            # taken only together with the fused tree levels, which are first-order themselves
             from . import _native
             B, L, C, D = ctx.shape
-            return _native.gather_blocks(grads[0].contiguous(), ctx.maps, C * D).view(ctx.shape)
-        gp = None
-        for (s, m, n), g in zip(_runs(ctx.shape[1]), grads):
-            if gp is None:
-                gp = torch.empty(ctx.shape, dtype=g.dtype, device=g.device)
-            gp[:, s:s + m].copy_(_bit_reversed(g, n.bit_length() - 1)[:m].transpose(0, 1))
-        return gp
+            return _native.gather_blocks(grads[0].detach().contiguous(), ctx.maps, C * D).view(ctx.shape), None
+        # differentiable torch operations: a double backward passes through here
+        parts = [_bit_reversed(g, n.bit_length() - 1)[:m].transpose(0, 1) for (s, m, n), g in zip(_runs(ctx.shape[1]),
+                                                                                                    grads)]
+        return torch.cat(parts, 1), None
 
 
 _map_cache = {}
@@ -193,7 +193,7 @@ def chain_product(pot, bmm=None):
     B, L, C, D = pot.shape
     assert C == D, "transition matrices must be square"
     parts = []
-    for x in _ChainMajor.apply(pot):
+    for x in _ChainMajor.apply(pot, fused):
         while x.shape[0] > 1:
             if fused:
                 x = _PairLevel.apply(x)

@@ -48,12 +48,14 @@ class HostPipeline:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.shape = (B, M, K, N)
         self.tensor_cores = tensor_cores
+        # Default (graph=False): every chunk is one call of the package's own operator, genbmm_b200.logbmm, and
+        # one torch.autograd.grad — the path a user of the drop-in API takes.
         # graph=True: the second step captures the kernels of every chunk (forward, loss, backward) into one
-        # CUDA graph per chunk, all in one memory pool, and later steps replay them between the copies,
-        # which stay ordinary stream copies; the host then issues about a hundred calls per step instead
-        # of several hundred.  Off by default: a 32 x 1024^3 step is bound by the PCIe copies, not by the
-        # host (measured 7.4 ms with graphs against 6.6-6.9 ms without on one GPU, 31.5 ms either way
-        # with eight ranks sharing one host's links).
+        # CUDA graph per chunk, all in one memory pool, on static gradient buffers through the C-ABI calls
+        # directly, and later steps replay them between the copies, which stay ordinary stream copies; the
+        # host then issues about a hundred calls per step instead of several hundred.  Off by default: a
+        # 32 x 1024^3 step is bound by the PCIe copies, not by the host (measured 7.4 ms with graphs against
+        # 6.6-6.9 ms without on one GPU, 31.5 ms either way with eight ranks sharing one host's links).
         self.use_graph = graph
         self._graphs = None
         self._warm = False
@@ -62,8 +64,8 @@ class HostPipeline:
         with torch.cuda.device(self.device):
             self.a = torch.empty((B, M, K), device=self.device)
             self.b = torch.empty((B, K, N), device=self.device)
-            self.grad_a = torch.empty_like(self.a)
-            self.grad_b = torch.empty_like(self.b)
+            self.grad_a = torch.empty_like(self.a) if graph else None
+            self.grad_b = torch.empty_like(self.b) if graph else None
             self.ones = torch.ones((max(hi - lo for lo, hi in self.bounds), M, N), device=self.device)
             self.loss = torch.zeros((), device=self.device, dtype=torch.float64)
             self.s_in = torch.cuda.Stream(self.device)
@@ -85,7 +87,7 @@ class HostPipeline:
                 for i in range(len(self.bounds)):
                     g = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(g, pool=pool):
-                        self._compute(i)
+                        self._compute_static(i)
                     pool = g.pool()
                     graphs.append(g)
                 self._graphs = graphs
@@ -104,20 +106,38 @@ class HostPipeline:
                 comp.wait_event(self.ev_in[i])
                 if self._graphs is not None:
                     self._graphs[i].replay()
+                    ga, gb = self.grad_a[lo:hi], self.grad_b[lo:hi]
+                elif self.use_graph:
+                    self._compute_static(i)
+                    ga, gb = self.grad_a[lo:hi], self.grad_b[lo:hi]
                 else:
-                    self._compute(i)
+                    ga, gb = self._compute(i)
                 self.ev_done[i].record(comp)
                 with torch.cuda.stream(self.s_out):
                     self.s_out.wait_event(self.ev_done[i])
-                    grad_a_host[lo:hi].copy_(self.grad_a[lo:hi], non_blocking=True)
-                    grad_b_host[lo:hi].copy_(self.grad_b[lo:hi], non_blocking=True)
+                    grad_a_host[lo:hi].copy_(ga, non_blocking=True)
+                    grad_b_host[lo:hi].copy_(gb, non_blocking=True)
+                    if not self.use_graph:   # allocated on the compute stream, last read on the copy stream
+                        ga.record_stream(self.s_out)
+                        gb.record_stream(self.s_out)
             comp.wait_stream(self.s_out)
             self._warm = True
             return float(self.loss.item())
 
     def _compute(self, i):
-        """Kernels of chunk i on the current stream: forward, its share of the loss, backward into the
-        chunk's rows of the gradient buffers."""
+        """Chunk i through the public operator: c = genbmm_b200.logbmm(a, b), its share of the loss, and
+        autograd for both gradients."""
+        from .genmul import logbmm
+        lo, hi = self.bounds[i]
+        a, b = self.a[lo:hi].requires_grad_(True), self.b[lo:hi].requires_grad_(True)
+        c = logbmm(a, b) if self.tensor_cores else _FP32Log.apply(a, b)
+        self.loss += c.detach().sum(dtype=torch.float64)
+        return torch.autograd.grad(c, (a, b), self.ones[: hi - lo])
+
+    def _compute_static(self, i):
+        """Kernels of chunk i on the current stream through the C-ABI calls, into static buffers (what a CUDA
+        graph can capture): forward, its share of the loss, backward into the chunk's rows of the gradient
+        buffers."""
         lo, hi = self.bounds[i]
         a, b = self.a[lo:hi], self.b[lo:hi]
         out, rowmax, colmax, flags, factors = _native.logbmm_fast_forward(
@@ -126,3 +146,18 @@ class HostPipeline:
         _native.logbmm_fast_backward(a, b, self.ones[: hi - lo], out, rowmax, colmax, flags,
                                      tensor_cores=self.tensor_cores, factors=factors,
                                      out_grads=(self.grad_a[lo:hi], self.grad_b[lo:hi]))
+
+
+class _FP32Log(torch.autograd.Function):
+    """logbmm on the FP32-pipe factorised kernels (HostPipeline(tensor_cores=False))."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        out, rowmax, colmax, flags = _native.logbmm_fast_forward(a, b, tensor_cores=False)
+        ctx.save_for_backward(a, b, out, rowmax, colmax, flags)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b, out, rowmax, colmax, flags = ctx.saved_tensors
+        return _native.logbmm_fast_backward(a, b, g.contiguous(), out, rowmax, colmax, flags, tensor_cores=False)

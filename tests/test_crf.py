@@ -129,3 +129,27 @@ def test_graphed_marginals_replay_matches_eager(B, L, C):
         assert torch.allclose(marg, want_m, rtol=1e-5, atol=1e-9)
     with pytest.raises(RuntimeError):
         run(torch.zeros(B, L + 1, C, C, device="cuda"))
+
+
+@pytest.mark.gpu
+def test_sharded_log_partition_over_nccl_on_cuda_tensors():
+    """The chain-chunk path with its NCCL all-gather carrying CUDA tensors (a one-rank group: the collective,
+    its autograd node and the redundant upper levels all run; with one rank the result must equal the unsharded
+    driver), forward and gradient."""
+    from genbmm_b200 import crf
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()))
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    try:
+        gen = torch.Generator().manual_seed(5)
+        pot = torch.randn(3, 31, 128, 128, generator=gen).cuda()
+        x = pot.clone().requires_grad_(True)
+        logz = crf.sharded_log_partition(x)
+        grad, = torch.autograd.grad(logz.sum(), x)
+        want_z, want_m = crf.marginals(pot)
+        assert torch.allclose(logz, want_z, rtol=1e-6, atol=0)
+        assert torch.allclose(grad, want_m, rtol=1e-5, atol=1e-9)
+        oz, om = oracle.crf_alpha_beta(pot[1].cpu())
+        assert abs(float(logz[1]) - oz) <= 1e-5 * abs(oz)
+        assert np.allclose(grad[1].cpu().numpy(), om, rtol=2e-4, atol=1e-9)
+    finally:
+        dist.destroy_process_group()

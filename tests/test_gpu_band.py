@@ -198,10 +198,10 @@ def test_band_log_guard_recomputes_flagged_row_blocks(gb, monkeypatch, lu, ld):
     b[:, 40:120, lu:] -= 300.0      # ... the b rows they meet live on the lower half
     out, ga, gb_ = run(gb, "multiply_log", a, lu, ld, b, lu, ld, g)
     want, _, _, dA, dB = oracle.band_fwd_bwd(0, a, lu, ld, b, lu, ld, g, dtype=np.float64)
-    # results near -300 are stored with the float32 spacing there (3e-5), and so is a + b: the weights
+    # results near -600 are stored with the float32 spacing there (6e-5), and so is a + b: the weights
     # exp(a + b - out) of any float32 implementation inherit that as a relative error
     rtol_w = 1e-5 + 2 * float(np.spacing(np.float32(np.abs(want).max())))
-    assert 5e-5 < rtol_w < 1e-4
+    assert 5e-5 < rtol_w < 2e-4
     assert_close(out.data, want, what="fwd")
     assert_close(ga, dA, rtol_w, what="grad_a")
     assert_close(gb_, dB, rtol_w, what="grad_b")

@@ -97,9 +97,14 @@ def test_default_path_operand_scale_sweep(gb, std, K):
     dA, dB = oracle.dense_bwd(0, a, b, g, want, maxes, dtype=np.float64)
     print("std %-4g K %-4d flagged tiles %d of %d; max rel err out %.2e grad_a %.2e grad_b %.2e" % (
         std, K, int(flags.sum()), flags.numel(), rel_err(c, want), rel_err(ga, dA), rel_err(gb_, dB)))
+    # a + b and the saved result are float32 numbers as large as max|c| (150 at std 20): their spacing there is
+    # a relative error of every weight exp(a + b - c), whatever computes it (at std 20 every tile is flagged
+    # and it is the exact kernels that are measured).  1.1e-5 up to std 1, 1.8e-5 at std 5, 4e-5 at std 20.
+    rtol_w = 1e-5 + 2 * float(np.spacing(np.float32(np.abs(want).max())))
+    assert rtol_w < 5e-5
     assert_close(c, want, what="fwd")
-    assert_close(ga, dA, what="grad_a")
-    assert_close(gb_, dB, what="grad_b")
+    assert_close(ga, dA, rtol_w, what="grad_a")
+    assert_close(gb_, dB, rtol_w, what="grad_b")
 
 
 def test_config4_marginals_against_forward_backward_recursions():
