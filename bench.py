@@ -631,9 +631,9 @@ def run_ours(args, rank, world, local):
     # ---- headline: device-resident inputs ------------------------------------------------
     sampler = ClockSampler(local)
     sampler.start()
-    for _ in range(max(0, args.warmup - 3)):
+    for _ in range(args.warmup):
         step_log()
-    est = ranks.max(region_ms(step_log, 3, ranks.sync) / 3)         # the last three warm-up steps, timed
+    est = ranks.max(region_ms(step_log, 3, ranks.sync) / 3)         # three more untimed-for-the-record steps
     repeats = max(1, min(4000, math.ceil(TARGET_REGION_S * 1e3 / (args.steps * est))))
     if args.inner_repeats > 0:
         repeats = args.inner_repeats

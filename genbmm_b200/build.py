@@ -77,5 +77,46 @@ def build(force=False, verbose=False):
     return LIB
 
 
+SHIM_SRC = os.path.join(CSRC, "shim", "torch_shim.cpp")
+SHIM = os.path.join(HERE, "_shim.so")
+
+
+def shim_stale():
+    if not os.path.exists(SHIM):
+        return True
+    t = os.path.getmtime(SHIM)
+    return any(os.path.getmtime(s) > t for s in [SHIM_SRC] + glob.glob(os.path.join(INCLUDE, "*.h")))
+
+
+def build_shim(force=False):
+    """Compile csrc/shim/torch_shim.cpp (host C++ only: the PyTorch binding of the C ABI with the operators as
+    C++ autograd functions) into genbmm_b200/_shim.so, linked against libgenbmm_b200.so beside it.  Built with
+    the host compiler directly, in tree, so the module that is imported is the file that was built and nothing
+    is compiled at import time.  Returns its path."""
+    if not force and not shim_stale():
+        return SHIM
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension as ext
+    cxx = next((c for c in (os.environ.get("CXX"), "/opt/gcc/bin/g++", shutil.which("g++")) if c and os.path.exists(c)),
+               None)
+    if cxx is None:
+        raise RuntimeError("no C++ compiler for the torch shim")
+    cuda_home = os.path.dirname(os.path.dirname(_nvcc()))
+    inc = ext.include_paths() + [sysconfig.get_paths()["include"], INCLUDE, os.path.join(cuda_home, "include")]
+    libdirs = [os.path.join(os.path.dirname(torch.__file__), "lib"), os.path.join(cuda_home, "lib64")]
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-w",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI), "-DTORCH_EXTENSION_NAME=_shim",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", *["-I" + i for i in inc], SHIM_SRC, "-o", SHIM,
+           *["-L" + d for d in libdirs], "-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10_cuda",
+           "-ltorch_cuda", "-lcudart", "-L" + HERE, "-l:libgenbmm_b200.so", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("torch shim failed to build:\n%s\n%s" % (" ".join(cmd), (r.stdout + r.stderr)[-4000:]))
+    return SHIM
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv))
+    print(build_shim(force="--force" in sys.argv))

@@ -5,6 +5,10 @@ Same public names and call shapes as the reference's genbmm/genmul.py:100-103:
 a:(B,M,K), b:(B,K,N), each returning c:(B,M,N) of a's dtype.  Additive: `samplebmm` takes
 an optional third argument, the uniforms that drive the sample.
 
+The public names are bound to the compiled PyTorch binding (genbmm_b200/_shim.so, C++ autograd functions)
+when it is built, else to the Python autograd Functions of this file over the ctypes binding; both call the
+same C-ABI entry points.
+
 Differences from the reference that a caller can observe:
   * the logbmm backward makes no transposed copies (genmul.py:38-41 makes six);
   * half / bfloat16 inputs are computed in float32 and cast back; float64 runs float64 kernels of its own
@@ -176,9 +180,35 @@ class ProdMaxMatMul(_IndexRouted):
         return ProdMaxMatMul._backward(ctx, grad_output)
 
 
-logbmm = LogMatMul.apply
-maxbmm = MaxMatMul.apply
-prodmaxbmm = ProdMaxMatMul.apply
+def _load_shim():
+    """The compiled PyTorch binding (csrc/shim/torch_shim.cpp: the same four operators as C++ autograd
+    functions over the same C ABI), or None when it is not built or GENBMM_B200_BINDING=ctypes asks for the
+    Python autograd Functions above.  Both bindings run the same kernels and give the same bits; the compiled
+    one costs a fraction of the host time per call."""
+    if os.environ.get("GENBMM_B200_BINDING", "shim") == "ctypes":
+        return None
+    from . import build as _build
+    try:
+        if not os.path.exists(_build.SHIM):
+            _build.build_shim()
+        from . import _shim
+        if _shim.abi_version() != _native.load().gbmm_abi_version():
+            return None
+        return _shim
+    except Exception:  # no host compiler, or a torch whose ABI the module was not built for
+        return None
+
+
+_shim = _load_shim()
+
+if _shim is not None:
+    logbmm = _shim.logbmm
+    maxbmm = _shim.maxbmm
+    prodmaxbmm = _shim.prodmaxbmm
+else:
+    logbmm = LogMatMul.apply
+    maxbmm = MaxMatMul.apply
+    prodmaxbmm = ProdMaxMatMul.apply
 
 
 def samplebmm(a, b, u=None):
@@ -186,4 +216,6 @@ def samplebmm(a, b, u=None):
 
     `u`:(B,M,N) uniforms in [0,1) select the sample; omitted, they are drawn on the device.
     """
+    if _shim is not None:
+        return _shim.samplebmm(a, b, u)
     return SampleMatMul.apply(a, b, u)

@@ -307,3 +307,38 @@ def test_logbmm_second_order_matches_oracle(gb, shape):
     assert_close(da, wa, 1e-4, 2e-5, "d/da")
     assert_close(db, wb, 1e-4, 2e-5, "d/db")
     assert_close(dg, wg, 1e-4, 2e-5, "d/dgrad_out")
+
+
+@pytest.mark.parametrize("shape", [(2, 33, 17, 65), (2, 130, 70, 67), (2, 192, 160, 136)])
+def test_compiled_binding_and_python_binding_give_the_same_bits(gb, shape):
+    """genbmm_b200.logbmm etc. are the C++ autograd functions of genbmm_b200/_shim.so when that module is built;
+    the Python autograd Functions of genmul.py over ctypes are the other binding of the same C ABI."""
+    from genbmm_b200 import genmul
+    if genmul._shim is None:
+        pytest.skip("compiled binding not built")
+    B, M, K, N = shape
+    gen = torch.Generator().manual_seed(sum(shape))
+    a, b, g = tied((B, M, K), gen), tied((B, K, N), gen), torch.rand(B, M, N, generator=gen)
+    u = torch.rand(B, M, N, generator=gen)
+    pairs = [(gb.logbmm, genmul.LogMatMul.apply, ()), (gb.maxbmm, genmul.MaxMatMul.apply, ()),
+             (gb.prodmaxbmm, genmul.ProdMaxMatMul.apply, ()),
+             (gb.samplebmm, genmul.SampleMatMul.apply, (dev(u),))]
+    for compiled, python, extra in pairs:
+        got = run_fwd_bwd(compiled, a, b, g, *extra)
+        want = run_fwd_bwd(python, a, b, g, *extra)
+        for x, y in zip(got, want):
+            assert torch.equal(x, y)
+    # half precision in, half precision out, through both
+    ah, bh = dev(a).half(), dev(b).half()
+    assert torch.equal(gb.logbmm(ah, bh), genmul.LogMatMul.apply(ah, bh)) and gb.logbmm(ah, bh).dtype == torch.float16
+    # second order through the compiled binding equals second order through the Python one
+    res = []
+    for fn in (gb.logbmm, genmul.LogMatMul.apply):
+        ad, bd, gd = dev(a).requires_grad_(True), dev(b).requires_grad_(True), dev(g).requires_grad_(True)
+        ga, gb_ = torch.autograd.grad(fn(ad, bd), (ad, bd), gd, create_graph=True)
+        res.append(torch.autograd.grad((ga * ga).sum() + (gb_ * gb_).sum(), (ad, bd, gd)))
+    for x, y in zip(*res):
+        assert torch.equal(x, y)
+    # float64 takes the float64 kernels in both
+    c64 = gb.logbmm(dev(a).double(), dev(b).double())
+    assert c64.dtype == torch.float64 and torch.equal(c64, genmul.LogMatMul.apply(dev(a).double(), dev(b).double()))
