@@ -21,6 +21,14 @@ int launch_log_bwd_flagged(const float* a, const float* b, const float* c, const
 int launch_rowcol_max(const float* a, const float* b, float* rowmax, float* colmax, int64_t B, int64_t M, int64_t K,
                       int64_t N, cudaStream_t st);
 
+// 32x32-tile exact log kernels for small problems (dense_small.cu); `small_log_wanted` says whether a grid of
+// `large_tile_ctas` CTAs of the 128x64-tile kernels would leave the GPU underfilled.
+bool small_log_wanted(int64_t large_tile_ctas);
+int launch_small_log_fwd(const float* a, const float* b, float* out, float* maxes, int64_t B, int64_t M, int64_t K,
+                         int64_t N, cudaStream_t st);
+int launch_small_log_bwd(const float* a, const float* b, const float* c, const float* g, float* grad_a, float* grad_b,
+                         int64_t B, int64_t M, int64_t K, int64_t N, cudaStream_t st);
+
 int rowmax_only(const float* a, float* rowmax, int64_t B, int64_t M, int64_t K, cudaStream_t st);
 
 }  // namespace gbmm

@@ -490,6 +490,11 @@ extern "C" int gbmm_dense_backward_f32(int mode, const float* a, const float* b,
   const int m = (int)M, k = (int)K, n = (int)N;
   if (mode == GBMM_MODE_LOG) {
     if (!part) return GBMM_ERR_INVALID_ARG;
+    {  // small problems: 32x32 tiles, both gradients in one launch (dense_small.cu)
+      const int64_t big_a = B * ceil_div(M, BR) * ceil_div(K, BC), big_b = B * ceil_div(K, BR) * ceil_div(N, BC);
+      if (small_log_wanted(big_a > big_b ? big_a : big_b))
+        return launch_small_log_bwd(a, b, part, grad_out, grad_a, grad_b, B, M, K, N, st);
+    }
     if (grad_a) {
       const int64_t tr = ceil_div(M, BR), tcn = ceil_div(K, BC), blocks = B * tr * tcn;
       if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;

@@ -663,6 +663,7 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
   const int m = (int)M, k = (int)K, n = (int)N, tm = (int)tiles_m, tn = (int)tiles_n;
   switch (mode) {
     case GBMM_MODE_LOG:
+      if (small_log_wanted(blocks)) return launch_small_log_fwd(a, b, out, static_cast<float*>(aux), B, M, K, N, st);
       dense_log_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, static_cast<float*>(aux), m, k, n, tm, tn, nullptr,
                                                           blocks, nullptr, 0);
       break;
@@ -695,8 +696,12 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
       break;
     }
     case GBMM_MODE_SAMPLE:
-      dense_log_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, nullptr, m, k, n, tm, tn, nullptr, blocks,
-                                                          nullptr, 0);
+      if (small_log_wanted(blocks)) {
+        if (int rc = launch_small_log_fwd(a, b, out, nullptr, B, M, K, N, st)) return rc;
+      } else {
+        dense_log_fwd_kernel<false><<<grid, block, 0, st>>>(a, b, out, nullptr, m, k, n, tm, tn, nullptr, blocks,
+                                                            nullptr, 0);
+      }
       if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
       dense_sample_pick_kernel<<<grid, block, 0, st>>>(a, b, u, out, static_cast<int*>(aux), m, k, n, tm, tn);
       break;

@@ -33,8 +33,14 @@ def tied(shape, gen):
     return (torch.randn(*shape, generator=gen) * 8).round() / 8
 
 
-@pytest.mark.parametrize("shape", SHAPES)
-def test_logbmm_matches_oracle(gb, shape):
+@pytest.mark.parametrize("tiles", ["auto", "large", "small"])
+@pytest.mark.parametrize("shape", SHAPES + [(40, 64, 64, 64), (3, 100, 150, 40)])
+def test_logbmm_matches_oracle(gb, shape, tiles, monkeypatch):
+    """The exact log kernels: 128x64 tiles (GENBMM_B200_SMALL=0), 32x32 tiles with both gradients in one launch
+    (=1), and the rule that picks between them by how many CTAs the large tiles would give."""
+    if tiles != "auto":   # "auto" is the operator as a user gets it (factorised tensor-core path when large)
+        monkeypatch.setenv("GENBMM_B200_LOGBMM", "exact")
+        monkeypatch.setenv("GENBMM_B200_SMALL", "0" if tiles == "large" else "1")
     B, M, K, N = shape
     gen = torch.Generator().manual_seed(sum(shape))
     a, b, g = torch.randn(B, M, K, generator=gen), torch.randn(B, K, N, generator=gen), torch.rand(B, M, N, generator=gen)
