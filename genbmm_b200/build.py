@@ -99,7 +99,9 @@ def build_shim(force=False):
 
     import torch
     from torch.utils import cpp_extension as ext
-    cxx = next((c for c in (os.environ.get("CXX"), "/opt/gcc/bin/g++", shutil.which("g++")) if c and os.path.exists(c)),
+    # the system compiler first: a module built by this image's /opt/gcc wrapper (what $CXX names here) crashed
+    # when a C++ exception crossed it
+    cxx = next((c for c in ("/usr/bin/g++", shutil.which("g++"), os.environ.get("CXX")) if c and os.path.exists(c)),
                None)
     if cxx is None:
         raise RuntimeError("no C++ compiler for the torch shim")
