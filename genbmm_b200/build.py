@@ -50,7 +50,9 @@ def stale():
 
 def _compile(src):
     obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
-    cmd = [_nvcc(), *[f for f in NVCC_FLAGS if f != "--use_fast_math=false"], "-I", INCLUDE, "-c", src, "-o", obj]
+    extra = os.environ.get("GENBMM_B200_NVCC_EXTRA", "").split()   # e.g. -DGBMM_BAND_BOX=64 (experiments)
+    cmd = [_nvcc(), *[f for f in NVCC_FLAGS if f != "--use_fast_math=false"], *extra, "-I", INCLUDE, "-c", src,
+           "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, " ".join(cmd), r.stdout + r.stderr))

@@ -30,8 +30,10 @@ struct alignas(1024) TcSmem {
   uint64_t empty[TST];
   uint64_t chunk_full[TNB];
   uint64_t chunk_empty[TNB];
+  uint64_t raw_full[TST];   // band_sp_kernel: TMA -> splitter warps (fits the alignment slack of this struct)
   uint32_t tmem_base;
 };
+static_assert(sizeof(TcSmem) + 1024 <= 232448, "the ring must fit the 227 KB a CTA can have");
 
 // ---- descriptors -------------------------------------------------------------------------
 // Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the

@@ -14,7 +14,8 @@ CASES = [(2, 5, 2, 1, 1, 2), (3, 8, 0, 3, 2, 0), (2, 6, 3, 3, 3, 3), (1, 4, 5, 4
          (3, 33, 0, 0, 3, 1),
          # bands >= 32 wide and n >= 128: the tensor-core path (sum, log), with odd sizes and offsets
          (2, 300, 20, 15, 18, 17), (1, 128, 40, 3, 5, 40), (2, 517, 64, 64, 64, 64), (1, 257, 0, 40, 35, 0),
-         (1, 1000, 31, 1, 0, 33), (2, 130, 100, 90, 70, 120)]
+         (1, 1000, 31, 1, 0, 33), (2, 130, 100, 90, 70, 120), (3, 700, 33, 30, 31, 40), (2, 1029, 64, 64, 64, 64),
+         (1, 400, 50, 0, 0, 50)]
 MODES = [("multiply", 3), ("multiply_log", 0), ("multiply_max", 1)]
 
 
@@ -67,12 +68,19 @@ def test_band_products_match_oracle(gb, case, method, mode):
 
 
 @pytest.mark.parametrize("case", [c for c in CASES if c[1] >= 128 and min(c[2] + c[3], c[4] + c[5]) >= 31])
-@pytest.mark.parametrize("path", ["auto", "block"])
+@pytest.mark.parametrize("path", ["auto", "hilo", "convert", "block"])
 def test_sum_semiring_both_paths(gb, case, monkeypatch, path):
-    """The ordinary product and its gradients as 3xTF32 on the tensor cores (default for wide bands) and on the
-    FP32 block kernels (GENBMM_B200_BAND=block), with signed cotangents.  Bound: 1e-6 of the sum of the terms'
-    magnitudes."""
-    monkeypatch.setenv("GENBMM_B200_BAND", path)
+    """The ordinary product and its gradients as 3xTF32 on the tensor cores and on the FP32 block kernels
+    (GENBMM_B200_BAND=block), with signed cotangents.  The tensor-core path has three feeds: one zero-padded
+    skewed fp32 copy per operand, fetched by TMA and split into tf32 hi + lo in shared memory (default when
+    every tile fits one accumulation chunk); a hi and a lo copy (GENBMM_B200_BAND_SPLIT=0, and always for
+    wider bands); operand tiles converted from the band tensors themselves by SIMT warps
+    (GENBMM_B200_BAND_CV=1).  Bound: 1e-6 of the sum of the terms' magnitudes."""
+    monkeypatch.setenv("GENBMM_B200_BAND", "block" if path == "block" else "auto")
+    if path == "convert":
+        monkeypatch.setenv("GENBMM_B200_BAND_CV", "1")
+    if path == "hilo":
+        monkeypatch.setenv("GENBMM_B200_BAND_SPLIT", "0")
     B, n, alu, ald, blu, bld = case
     gen = torch.Generator().manual_seed(sum(case))
     a = torch.randn(B, n, alu + ald + 1, generator=gen)
@@ -86,6 +94,26 @@ def test_sum_semiring_both_paths(gb, case, monkeypatch, path):
     assert_close(gb_, dB, what="grad_b", term_sum=t_dB)
     inside = band_inside(B, n, alu + bld, ald + blu)
     assert (r.data.cpu().numpy()[~inside] == 0).all()
+
+
+@pytest.mark.parametrize("case", [c for c in CASES if c[1] >= 128 and min(c[2] + c[3], c[4] + c[5]) >= 31])
+@pytest.mark.parametrize("feed", ["hilo", "convert"])
+def test_log_semiring_other_tensor_feeds(gb, case, monkeypatch, feed):
+    """The log product on the two tensor-core feeds that are not the default (hi + lo copies,
+    GENBMM_B200_BAND_SPLIT=0; SIMT-converted tiles, GENBMM_B200_BAND_CV=1); the default feed is what
+    test_band_products_match_oracle runs for these shapes."""
+    monkeypatch.setenv("GENBMM_B200_BAND_CV" if feed == "convert" else "GENBMM_B200_BAND_SPLIT",
+                       "1" if feed == "convert" else "0")
+    B, n, alu, ald, blu, bld = case
+    gen = torch.Generator().manual_seed(sum(case))
+    a = torch.randn(B, n, alu + ald + 1, generator=gen)
+    b = torch.randn(B, n, blu + bld + 1, generator=gen)
+    g = torch.rand(B, n, alu + ald + blu + bld + 1, generator=gen)
+    r, ga, gb_ = run(gb, "multiply_log", a, alu, ald, b, blu, bld, g)
+    out, _, _, dA, dB = oracle.band_fwd_bwd(0, a, alu, ald, b, blu, bld, g, dtype=np.float64)
+    assert_close(r.data, out, what="multiply_log")
+    assert_close(ga, dA, what="grad_a")
+    assert_close(gb_, dB, what="grad_b")
 
 
 @pytest.mark.parametrize("ci", [0, 1, 2, 3, 4])
