@@ -81,15 +81,57 @@ __device__ __forceinline__ void store_pairs_b(float* s, const TileLoader<BN, BK,
 
 // PACK: the index of the winning reduction tile is kept in one byte (4 results per register), which
 // needs at most 255 tiles (K <= 4080) and lets two CTAs share an SM; otherwise one int per result.
-template <bool MUL, bool PACK>
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async8(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most `pending` of this thread's committed groups are still in flight (pending < 8)
+__device__ __forceinline__ void cp_async_wait(int pending) {
+  switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+  }
+}
+
+// RESIDENT (reductions of at most kResidentTiles tiles, dynamic shared memory): every reduction tile stays in
+// shared memory, so the final search for the first k that attains the maximum reads shared memory instead of
+// going back to global memory — for short reductions that search costs more than the reduction itself
+// (K = 128: 1 MB of search reads per CTA against 100 KB of operands).  All tiles are requested at once with
+// cp.async straight into the pair layout (one group per tile, waited for in order), so the latency of global
+// memory is paid once per CTA instead of once per 16-step tile.
+constexpr int kResidentTiles = 8;
+constexpr int kTileX = BK * LDX, kTileY = BK * LDY;
+// Resident tiles are 4 floats further apart than their size (both sizes are multiples of 32 floats): in the
+// final search the lanes of a warp read the same cell of DIFFERENT tiles, which would otherwise all fall on
+// one bank.
+constexpr int kTileXr = kTileX + 4, kTileYr = kTileY + 4;
+
+template <bool MUL, bool PACK, bool RESIDENT>
 __global__ void __launch_bounds__(NT, PACK ? 2 : 1) dense_max_fwd_kernel(const float* __restrict__ a,
                                                                          const float* __restrict__ b,
                                                                          float* __restrict__ out,
                                                                          int* __restrict__ idx, int M, int K, int N,
                                                                          int tiles_m, int tiles_n,
                                                                          const float* __restrict__ b_t, int kp) {
-  __shared__ __align__(16) float sx[2][BK * LDX];
-  __shared__ __align__(16) float sy[2][BK * LDY];
+  __shared__ __align__(16) float sx_two[RESIDENT ? 1 : 2][RESIDENT ? 4 : kTileX];
+  __shared__ __align__(16) float sy_two[RESIDENT ? 1 : 2][RESIDENT ? 4 : kTileY];
+  extern __shared__ __align__(16) float resident_smem[];   // RESIDENT: nt x tiles, then nt y tiles
+  const int nt_all = (K + BK - 1) / BK;
+  float* const sx_base = RESIDENT ? resident_smem : &sx_two[0][0];
+  float* const sy_base = RESIDENT ? resident_smem + (size_t)nt_all * kTileXr : &sy_two[0][0];
+  auto sx = [&](int t) -> float* { return sx_base + (RESIDENT ? t * kTileXr : (t & 1) * kTileX); };
+  auto sy = [&](int t) -> float* { return sy_base + (RESIDENT ? t * kTileYr : (t & 1) * kTileY); };
   const TileCoord tc(blockIdx.x, tiles_m, tiles_n);
   const Micro8x4 mt;
   const float* ab = a + (int64_t)tc.bt * M * K;
@@ -118,22 +160,63 @@ __global__ void __launch_bounds__(NT, PACK ? 2 : 1) dense_max_fwd_kernel(const f
   TileLoader<BN, BK, NT, false> lb;
   const int nt = (K + BK - 1) / BK;
   // a NaN in the padded reduction steps makes the term a NaN, which the maximum ignores
-  la.load(ab, K, 1, tc.m0, 0, M, K, vec_a, nan_f());
-  lb.load(bb, 1, N, tc.n0, 0, N, K, vec_b, 0.f);
-  store_pairs_a(sx[0], la);
-  store_pairs_b(sy[0], lb);
-  __syncthreads();
+  if (RESIDENT) {
+    const bool pair_ok = (K % 2 == 0) && ((reinterpret_cast<uintptr_t>(ab) & 7) == 0);
+    for (int t = 0; t < nt; ++t) {
+#pragma unroll
+      for (int q = 0; q < TileLoader<BM, BK, NT, true>::NV; ++q) {   // a: 4 consecutive k of one row -> two pairs
+        const int f = threadIdx.x + q * NT, o = f / (BK / 4), r = (f % (BK / 4)) * 4;
+        const int m = tc.m0 + o, k = t * BK + r;
+        float* d0 = sx(t) + ((r / 2) * LDX + o) * 2;
+        float* d1 = sx(t) + ((r / 2 + 1) * LDX + o) * 2;
+        const float* src = ab + (int64_t)m * K + k;
+        if (pair_ok && m < M && k + 3 < K) {
+          cp_async8(d0, src);
+          cp_async8(d1, src + 2);
+        } else {
+          const bool ok = m < M;
+          d0[0] = (ok && k + 0 < K) ? __ldg(src + 0) : nan_f();
+          d0[1] = (ok && k + 1 < K) ? __ldg(src + 1) : nan_f();
+          d1[0] = (ok && k + 2 < K) ? __ldg(src + 2) : nan_f();
+          d1[1] = (ok && k + 3 < K) ? __ldg(src + 3) : nan_f();
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < TileLoader<BN, BK, NT, false>::NV; ++q) {  // b: 4 consecutive columns at one k
+        const int f = threadIdx.x + q * NT, r = f / (BN / 4), o = (f % (BN / 4)) * 4;
+        const int k = t * BK + r, n = tc.n0 + o;
+        float* d = sy(t) + ((r / 2) * LDY + o) * 2 + (r & 1);
+        const float* src = bb + (int64_t)k * N + n;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (k < K && n + e < N)
+            cp_async4(d + 2 * e, src + e);
+          else
+            d[2 * e] = 0.f;
+        }
+      }
+      cp_async_commit();
+    }
+  } else {
+    la.load(ab, K, 1, tc.m0, 0, M, K, vec_a, nan_f());
+    lb.load(bb, 1, N, tc.n0, 0, N, K, vec_b, 0.f);
+    store_pairs_a(sx(0), la);
+    store_pairs_b(sy(0), lb);
+    __syncthreads();
+  }
 
   auto tile_step = [&](int t, float (&acc)[8][4], const float (&prev)[8][4]) {
-    const int cur = t & 1;
-    if (t + 1 < nt) {
+    if (RESIDENT) {   // tile t has landed (this thread's copies, then everyone's)
+      cp_async_wait(nt - 1 - t);
+      __syncthreads();
+    } else if (t + 1 < nt) {
       la.load(ab, K, 1, tc.m0, (t + 1) * BK, M, K, vec_a, nan_f());
       lb.load(bb, 1, N, tc.n0, (t + 1) * BK, N, K, vec_b, 0.f);
     }
 #pragma unroll
     for (int kp2 = 0; kp2 < BK / 2; ++kp2) {
-      const float* xs = sx[cur] + (kp2 * LDX + mt.ty * 4) * 2;
-      const float* ys = sy[cur] + (kp2 * LDY + mt.tx * 4) * 2;
+      const float* xs = sx(t) + (kp2 * LDX + mt.ty * 4) * 2;
+      const float* ys = sy(t) + (kp2 * LDY + mt.tx * 4) * 2;
       const ulonglong2 x01 = *reinterpret_cast<const ulonglong2*>(xs);
       const ulonglong2 x23 = *reinterpret_cast<const ulonglong2*>(xs + 4);
       const ulonglong2 x45 = *reinterpret_cast<const ulonglong2*>(xs + 128);
@@ -165,11 +248,13 @@ __global__ void __launch_bounds__(NT, PACK ? 2 : 1) dense_max_fwd_kernel(const f
           if (acc[i][j] > prev[i][j]) cid[i][j] = t;
       }
     }
-    if (t + 1 < nt) {
-      store_pairs_a(sx[cur ^ 1], la);
-      store_pairs_b(sy[cur ^ 1], lb);
+    if (!RESIDENT) {
+      if (t + 1 < nt) {
+        store_pairs_a(sx(t + 1), la);
+        store_pairs_b(sy(t + 1), lb);
+      }
+      __syncthreads();
     }
-    __syncthreads();
   };
   int t = 0;
   for (; t + 1 < nt; t += 2) {
@@ -205,7 +290,33 @@ __global__ void __launch_bounds__(NT, PACK ? 2 : 1) dense_max_fwd_kernel(const f
       val[j] = Y[i][j];
       ind[j] = -1;
     }
-    if (b_t) {
+    if (RESIDENT) {
+      // every tile is still in shared memory: each thread searches the winning tile of its own results, from
+      // the last pair down so that the lowest matching k is the assignment that sticks; a NaN (padding beyond
+      // K) never equals the maximum
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int ct = tile_of(i, j);
+        if (ct < 0) continue;
+        const float* xs = sx(ct) + mt.row(i) * 2;
+        const float* ys = sy(ct) + mt.col(j) * 2;
+#pragma unroll
+        for (int kp2 = BK / 2 - 1; kp2 >= 0; --kp2) {
+          const float2 xv = *reinterpret_cast<const float2*>(xs + kp2 * LDX * 2);
+          const float2 yv = *reinterpret_cast<const float2*>(ys + kp2 * LDY * 2);
+          const float t1 = MUL ? __fmul_rn(xv.y, yv.y) : __fadd_rn(xv.y, yv.y);
+          const float t0 = MUL ? __fmul_rn(xv.x, yv.x) : __fadd_rn(xv.x, yv.x);
+          if (t1 == Y[i][j]) {
+            val[j] = t1;
+            ind[j] = ct * BK + 2 * kp2 + 1;
+          }
+          if (t0 == Y[i][j]) {
+            val[j] = t0;
+            ind[j] = ct * BK + 2 * kp2;
+          }
+        }
+      }
+    } else if (b_t) {
       // Quad-cooperative scan: the four lanes of a quad take the quad's results one owner at a
       // time; each lane loads a quarter (16 bytes of a, 16 of b_t) of the winning tile's two
       // 64-byte segments, so one warp-wide load touches 8 segments instead of 32, and the lowest
@@ -640,6 +751,7 @@ extern "C" int gbmm_dense_sample_pick_f32(const float* a, const float* b, const 
 extern "C" int64_t gbmm_dense_forward_workspace_bytes(int mode, int64_t B, int64_t M, int64_t K, int64_t N) {
   if (B < 0 || M < 0 || K < 0 || N < 0) return -1;
   if (mode != GBMM_MODE_MAX && mode != GBMM_MODE_PRODMAX) return 0;
+  if ((K + BK - 1) / BK <= kResidentTiles) return 0;   // short reductions search shared memory, no copy of b
   return (int64_t)sizeof(float) * B * N * ((K + 15) / 16 * 16);
 }
 
@@ -669,6 +781,18 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
       break;
     case GBMM_MODE_MAX:
     case GBMM_MODE_PRODMAX: {
+      const bool pack = ceil_div(K, BK) <= 255;
+      int* ix = static_cast<int*>(aux);
+      const bool mul = mode == GBMM_MODE_PRODMAX;
+      if (K > 0 && ceil_div(K, BK) <= kResidentTiles) {
+        // short reductions: every tile stays in shared memory and the index search reads it there
+        const size_t dyn = (size_t)ceil_div(K, BK) * (kTileXr + kTileYr) * sizeof(float);
+        auto kernel = mul ? dense_max_fwd_kernel<true, true, true> : dense_max_fwd_kernel<false, true, true>;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn) != cudaSuccess)
+          return GBMM_ERR_LAUNCH;
+        kernel<<<grid, block, dyn, st>>>(a, b, out, ix, m, k, n, tm, tn, nullptr, 0);
+        break;
+      }
       // with scratch for a transposed copy of b the final index search reads contiguous segments
       float* b_t = nullptr;
       const int kp = (int)((K + 15) / 16 * 16);
@@ -680,18 +804,16 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
         transpose_b_kernel<<<(unsigned)tb, 256, 0, st>>>(b, b_t, k, n, kp, (int)tk, (int)tnn);
         if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
       }
-      const bool pack = ceil_div(K, BK) <= 255;
-      int* ix = static_cast<int*>(aux);
-      if (mode == GBMM_MODE_MAX) {
+      if (!mul) {
         if (pack)
-          dense_max_fwd_kernel<false, true><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
+          dense_max_fwd_kernel<false, true, false><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
         else
-          dense_max_fwd_kernel<false, false><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
+          dense_max_fwd_kernel<false, false, false><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
       } else {
         if (pack)
-          dense_max_fwd_kernel<true, true><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
+          dense_max_fwd_kernel<true, true, false><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
         else
-          dense_max_fwd_kernel<true, false><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
+          dense_max_fwd_kernel<true, false, false><<<grid, block, 0, st>>>(a, b, out, ix, m, k, n, tm, tn, b_t, kp);
       }
       break;
     }
