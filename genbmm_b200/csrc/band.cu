@@ -513,6 +513,64 @@ __global__ void __launch_bounds__(1024) band_route_b_kernel(const int* __restric
     for (int k = lane; k < Wb; k += 32) grad_b[(bt * n + o) * Wb + k] = hist[k];
 }
 
+// grad_b, one THREAD per row o of b (RB_T rows per CTA), each with its own Wb-bucket histogram in shared memory
+// (odd pitch: the threads of a warp hit 32 different banks for the same bucket).  A warp walks the rows i that
+// reach any of its 32 rows o in ascending order; at a given i its lanes read the cells (i, jo = o - i + r_lu),
+// which are consecutive in memory, and every lane adds its cell's cotangent to the bucket its index names.  A
+// thread therefore accumulates its row's buckets in ascending i — the order of a sequential walk, with no
+// ordering work between lanes (the kernel above spends most of its time ranking lanes that share a bucket).
+constexpr int RB_T = 128;
+__global__ void __launch_bounds__(RB_T) band_route_b_rows_kernel(const int* __restrict__ idx,
+                                                                 const float* __restrict__ g,
+                                                                 float* __restrict__ grad_b, BandDims d,
+                                                                 int64_t rows) {
+  extern __shared__ float hist_all[];
+  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  const int Wa = d.Wa(), Wb = d.Wb(), Wo = d.Wo(), r_lu = d.r_lu(), r_ld = Wo - 1 - r_lu;
+  const int pitch = Wb | 1;
+  const int64_t n = d.n;
+  float* hist = hist_all + threadIdx.x * pitch;
+  for (int k = 0; k < Wb; ++k) hist[k] = 0.f;
+  // this warp's rows: row0 .. row0 + 31 of the flattened (batch, o) index; a warp may straddle two batch
+  // elements, so every lane keeps its own batch element and row
+  const int64_t row = (int64_t)blockIdx.x * RB_T + threadIdx.x;
+  const bool live = row < rows;
+  const int64_t bt = live ? row / n : 0, o = live ? row % n : 0;
+  const int* ib = idx + bt * n * Wo;
+  const float* gb = g + bt * n * Wo;
+  // steps s = 0 .. 31 + Wo - 1: lane l looks at i = o - r_ld - l' ... every lane walks ITS OWN ascending i range
+  // [o - r_ld, o + r_lu], offset so that the lanes of a warp are at the same i (hence at consecutive cells)
+  // whenever their rows are consecutive: i = (o - lane) - r_ld + s
+  const int64_t ibase = o - lane - r_ld;
+  const int steps = 31 + Wo;
+  constexpr int U = 8;   // cells fetched together: the walk is otherwise one global-load latency per step
+  for (int s0 = 0; s0 < steps; s0 += U) {
+    int ja[U];
+    float gv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = ibase + s0 + u, jo = o - i + r_lu;
+      const bool ok = live && s0 + u < steps && i >= 0 && i < n && jo >= 0 && jo < Wo;
+      ja[u] = ok ? __ldg(ib + i * Wo + jo) : -1;
+      gv[u] = ok ? __ldg(gb + i * Wo + jo) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = ibase + s0 + u, jo = o - i + r_lu;
+      const int k2 = ja[u] - (int)jo + Wb - 1;
+      const int64_t p = i + ja[u] - d.a_lu;
+      if (ja[u] >= 0 && ja[u] < Wa && k2 >= 0 && k2 < Wb && p >= 0 && p < n)
+        hist[k2] = __fadd_rn(hist[k2], gv[u]);
+    }
+  }
+  __syncthreads();
+  for (int r = warp; r < RB_T; r += RB_T / 32) {
+    const int64_t grow = (int64_t)blockIdx.x * RB_T + r;
+    if (grow >= rows) break;
+    for (int k = lane; k < Wb; k += 32) grad_b[grow * Wb + k] = hist_all[r * pitch + k];
+  }
+}
+
 // ------------------------------------------------------------------ log semiring, second order
 // With the weight s = exp(a[i][ja] + b[o][k2] - out[i][jo]) of a triple, cotangents h_a, h_b of
 // the first-order gradients, H = h_a[i][ja] + h_b[o][k2] and t[i][jo] = sum_ja s H:
@@ -677,6 +735,18 @@ static int route_max_backward(const float* grad_out, const int* idx, float* grad
   if (grad_b) {
     const int64_t tiles = ceil_div(d.n, 32), blocks = B * tiles;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+    const size_t smem_rows = sizeof(float) * RB_T * (d.Wb() | 1);
+    static const bool by_rows = [] {
+      const char* e = getenv("GENBMM_B200_BAND_ROUTE_B");
+      return !(e && e[0] == 'w');   // "warp": the warp-per-row kernel
+    }();
+    if (by_rows && smem_rows <= (size_t)100 * 1024) {   // two CTAs per SM
+      const int64_t rows = B * d.n, rblocks = ceil_div(rows, RB_T);
+      if (rblocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+      if (smem_rows > 48 * 1024 && !allow_smem(band_route_b_rows_kernel, smem_rows)) return GBMM_ERR_LAUNCH;
+      band_route_b_rows_kernel<<<(unsigned)rblocks, RB_T, smem_rows, st>>>(idx, grad_out, grad_b, d, rows);
+      return launch_status();
+    }
     // the kernel also holds 16.5 KB of static tiles; together they may pass the 48 KB default
     if (smem_b + 17 * 1024 > 48 * 1024 && !allow_smem(band_route_b_kernel, smem_b)) return GBMM_ERR_LAUNCH;
     band_route_b_kernel<<<(unsigned)blocks, 1024, smem_b, st>>>(idx, grad_out, grad_b, d, (int)tiles);
