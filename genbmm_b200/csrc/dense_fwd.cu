@@ -18,6 +18,7 @@
 //       running sum in ascending k and its strict double inequality.
 #include "dense.cuh"
 #include "tile.cuh"
+#include "tma.cuh"
 
 namespace gbmm {
 namespace {
@@ -453,6 +454,243 @@ __global__ void __launch_bounds__(NT, PACK ? 2 : 1) dense_max_fwd_kernel(const f
   }
 }
 
+// ------------------------------------------------------------------ max-plus / prod-max, TMA-staged
+// The same reduction with the operand tiles brought in by TMA instead of through registers: per 32-step stage one
+// 128 x 32 box of a and one 64 x 32 box of the transposed copy of b (both k-contiguous, 128-byte rows, 128-byte
+// swizzle) land in a four-stage shared-memory ring; `full` barriers carry the byte counts, `empty` barriers one
+// arrival per warp.  Thread 0 issues the copies: after its warp has finished a stage it waits for the other
+// warps' arrivals on that stage and refills the slot with the tile four stages ahead (the other warps never wait
+// for anything but data).  Reduction steps beyond K read as NaN (the tensor map's out-of-bounds fill), a term the
+// maximum ignores, exactly like the padding of the kernel above.
+// Pairs (k, k+1) are contiguous in a k-major row, so the packed add needs no special layout; a thread's eight rows
+// are ty + 16 i and its four columns tx + 16 j, which gives all of its rows one swizzle phase (row & 7) and all of
+// its columns another: the 16-byte chunk q of a row sits at chunk q ^ phase, one XOR per chunk and operand, and
+// every load of a chunk is an immediate offset from there.  With the staging gone, the ALU pipe carries the
+// 3-input maxima, the index tracking (per 16 steps, as above) and a handful of address instructions per chunk.
+constexpr int XS_STAGES = 4, XS_K = 32;
+struct alignas(1024) MaxTmaSmem {
+  float a[XS_STAGES][BM * XS_K];
+  float b[XS_STAGES][BN * XS_K];
+  uint64_t full[XS_STAGES];
+  uint64_t empty[XS_STAGES];
+};
+
+template <bool MUL>
+__global__ void __launch_bounds__(NT, 2) dense_max_tma_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                              const __grid_constant__ CUtensorMap map_bt,
+                                                              const float* __restrict__ a,
+                                                              const float* __restrict__ b_t, float* __restrict__ out,
+                                                              int* __restrict__ idx, int M, int K, int N, int tiles_m,
+                                                              int tiles_n, int kp, int* __restrict__ error) {
+  extern __shared__ unsigned char smem_raw[];
+  MaxTmaSmem& sm = *reinterpret_cast<MaxTmaSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const TileCoord tc(blockIdx.x, tiles_m, tiles_n);
+  const int tid = threadIdx.x, lane = tid & 31, tx = tid % 16, ty = tid / 16;
+  const int nst = (K + XS_K - 1) / XS_K;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < XS_STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], NT / 32);
+    }
+    fence_barrier_init();
+  }
+  __syncthreads();
+  auto issue = [&](int t) {
+    const int s = t % XS_STAGES;
+    mbar_arrive_expect_tx(&sm.full[s], (BM + BN) * XS_K * sizeof(float));
+    tma_load_3d(sm.a[s], &map_a, &sm.full[s], t * XS_K, tc.m0, tc.bt);
+    tma_load_3d(sm.b[s], &map_bt, &sm.full[s], t * XS_K, tc.n0, tc.bt);
+  };
+  if (tid == 0)
+    for (int t = 0; t < XS_STAGES && t < nst; ++t) issue(t);
+
+  float X[8][4], Y[8][4];
+  unsigned cidp[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    cidp[i] = 0xffffffffu;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      X[i][j] = kFloor;
+      Y[i][j] = kFloor;
+    }
+  }
+  const int xph = ty & 7, yph = tx & 7;   // swizzle phases of this thread's rows and columns
+  bool fail = false;
+
+  // one 16-step sub-tile: chunks q0 .. q0 + 3 of the stage; u = its index among all 16-step tiles
+  auto sub_tile = [&](const float* xs, const float* ys, int q0, int u, float (&acc)[8][4], const float (&prev)[8][4]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float* xc = xs + (((q0 + c) ^ xph) << 2);
+      const float* yc = ys + (((q0 + c) ^ yph) << 2);
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        unsigned long long xp[8], yp[4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xp[i] = *reinterpret_cast<const unsigned long long*>(xc + i * 16 * XS_K + 2 * p);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) yp[j] = *reinterpret_cast<const unsigned long long*>(yc + j * 16 * XS_K + 2 * p);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float v0, v1;
+            unpack2(MUL ? mul2(xp[i], yp[j]) : add2(xp[i], yp[j]), v0, v1);
+            acc[i][j] = max3((c == 0 && p == 0) ? prev[i][j] : acc[i][j], v0, v1);
+          }
+      }
+    }
+    // strict `>`: an equal maximum in a later tile does not move the index
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (acc[i][0] > prev[i][0]) cidp[i] = __byte_perm(cidp[i], (unsigned)u, 0x3214);
+      if (acc[i][1] > prev[i][1]) cidp[i] = __byte_perm(cidp[i], (unsigned)u, 0x3240);
+      if (acc[i][2] > prev[i][2]) cidp[i] = __byte_perm(cidp[i], (unsigned)u, 0x3410);
+      if (acc[i][3] > prev[i][3]) cidp[i] = __byte_perm(cidp[i], (unsigned)u, 0x4210);
+    }
+  };
+
+  for (int t = 0; t < nst; ++t) {
+    const int s = t % XS_STAGES;
+    if (!mbar_wait_bounded(&sm.full[s], (t / XS_STAGES) & 1)) fail = true;
+    if (__any_sync(0xffffffffu, fail)) {
+      fail = true;
+      break;
+    }
+    const float* xs = sm.a[s] + ty * XS_K;
+    const float* ys = sm.b[s] + tx * XS_K;
+    sub_tile(xs, ys, 0, 2 * t, X, Y);
+    sub_tile(xs, ys, 4, 2 * t + 1, Y, X);
+    __syncwarp();
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.empty[s])) : "memory");
+    if (tid == 0 && t + XS_STAGES < nst) {
+      // every warp is done with this slot: refill it with the tile four stages ahead
+      if (!mbar_wait_bounded(&sm.empty[s], (t / XS_STAGES) & 1)) {
+        fail = true;
+      } else {
+        issue(t + XS_STAGES);
+      }
+    }
+  }
+  if (__syncthreads_or(fail)) {
+    // a wait gave up: record it (the caller's next kernel turns the result into NaN) and write nothing.  The
+    // copies still in flight get a bounded chance to land before the shared memory is released.
+    if (tid == 0) {
+      for (int t2 = 0; t2 < XS_STAGES; ++t2) mbar_wait_bounded(&sm.full[t2], 0);
+      if (error) atomicExch(error, 1);
+    }
+    return;
+  }
+  // from here on Y holds the maxima (two sub-tiles per stage: the roles are back where they started)
+  auto tile_of = [&](int i, int j) -> int {
+    const unsigned c = (cidp[i] >> (8 * j)) & 0xffu;
+    return c == 0xffu ? -1 : (int)c;
+  };
+  const float* ab = a + (int64_t)tc.bt * M * K;
+  float* ob = out + (int64_t)tc.bt * M * N;
+  int* ib = idx + (int64_t)tc.bt * M * N;
+  // Quad-cooperative search of the winning 16-step tile, as in the kernel above: the four lanes of a quad share
+  // their rows (same ty) and own four consecutive columns; they take the quad's results one owner at a time, each
+  // lane loading a quarter (16 bytes of a, 16 of b_t) of the tile's two 64-byte segments.
+  const unsigned full = 0xffffffffu;
+  const int q = lane & 3, tx_quad = tx & ~3;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int m = tc.m0 + ty + 16 * i;
+    float val[4];
+    int ind[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      val[j] = Y[i][j];
+      ind[j] = -1;
+    }
+#pragma unroll
+    for (int o = 0; o < 4; ++o) {
+      const int src = (lane & ~3) | o;
+      float bo[4], av[4][4], bv[4][4];
+      int ct[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        bo[j] = __shfl_sync(full, Y[i][j], src);
+        ct[j] = __shfl_sync(full, tile_of(i, j), src);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = tc.n0 + tx_quad + o + 16 * j;
+        const int k0 = ct[j] * BK + 4 * q;
+        const bool ok = ct[j] >= 0 && m < M && n < N;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          av[j][kk] = nan_f();
+          bv[j][kk] = 0.f;
+        }
+        if (ok) {
+          if (k0 + 3 < K) {   // K is a multiple of 4 on this path
+            const float4 t4 = __ldg(reinterpret_cast<const float4*>(ab + (int64_t)m * K + k0));
+            av[j][0] = t4.x; av[j][1] = t4.y; av[j][2] = t4.z; av[j][3] = t4.w;
+          }
+          const float4 u4 = __ldg(reinterpret_cast<const float4*>(b_t + ((int64_t)tc.bt * N + n) * kp + k0));
+          bv[j][0] = u4.x; bv[j][1] = u4.y; bv[j][2] = u4.z; bv[j][3] = u4.w;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int loc = 99;
+        float vm = 0.f;
+#pragma unroll
+        for (int kk = 3; kk >= 0; --kk) {
+          // a NaN (padding beyond K, or no winner) never equals the maximum
+          const float t = MUL ? __fmul_rn(av[j][kk], bv[j][kk]) : __fadd_rn(av[j][kk], bv[j][kk]);
+          if (t == bo[j]) {
+            loc = 4 * q + kk;
+            vm = t;
+          }
+        }
+#pragma unroll
+        for (int d = 1; d <= 2; d <<= 1) {
+          const int oloc = __shfl_xor_sync(full, loc, d);
+          const float ovm = __shfl_xor_sync(full, vm, d);
+          if (oloc < loc) {
+            loc = oloc;
+            vm = ovm;
+          }
+        }
+        if (q == o && loc != 99) {
+          ind[j] = ct[j] * BK + loc;
+          val[j] = vm;
+        }
+      }
+    }
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = tc.n0 + tx + 16 * j;
+      if (n < N) {
+        ob[(int64_t)m * N + n] = val[j];
+        ib[(int64_t)m * N + n] = ind[j];
+      }
+    }
+  }
+}
+
+// Tensor map of a (batch, rows, cols) fp32 array with rows `pitch` apart, fetched as (box_rows x 32) boxes with
+// the 128-byte swizzle; elements outside [0, rows) x [0, cols) read as NaN.
+bool make_max_map(CUtensorMap* map, const float* base, uint64_t batch, uint64_t rows, uint64_t cols, uint64_t pitch,
+                  uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || (pitch & 3)) return false;
+  const cuuint64_t dims[3] = {cols, rows, batch};
+  const cuuint64_t strides[2] = {pitch * sizeof(float), rows * pitch * sizeof(float)};
+  const cuuint32_t box[3] = {XS_K, box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NAN_REQUEST_ZERO_FMA) == CUDA_SUCCESS;
+}
+
 // b:(batch, K, N) -> b_t:(batch, N, kp) for the rescan of the max kernels (plain 32x32 tile transpose)
 __global__ void __launch_bounds__(256) transpose_b_kernel(const float* __restrict__ b, float* __restrict__ b_t,
                                                           int K, int N, int kp, int tiles_k, int tiles_n) {
@@ -803,6 +1041,22 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
         if (tb >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
         transpose_b_kernel<<<(unsigned)tb, 256, 0, st>>>(b, b_t, k, n, kp, (int)tk, (int)tnn);
         if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+      }
+      {
+        // TMA-staged kernel (GENBMM_B200_MAX_TMA=1): a's rows must be 16-byte multiples and the transposed copy of
+        // b is its B operand.  Same results; measured 3.09 ms against 3.04 ms for the register-staged kernel at
+        // 32 x 1024^3 (the ALU pipe's 3-input maxima bound both), so it is not the default.
+        const char* e = getenv("GENBMM_B200_MAX_TMA");
+        CUtensorMap ma, mb;
+        if ((e && e[0] == '1') && b_t && pack && K % 4 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+            make_max_map(&ma, a, B, M, K, K, BM) && make_max_map(&mb, b_t, B, N, kp, kp, BN)) {
+          const size_t dyn = sizeof(MaxTmaSmem) + 1024;
+          auto kernel = mul ? dense_max_tma_kernel<true> : dense_max_tma_kernel<false>;
+          if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn) != cudaSuccess)
+            return GBMM_ERR_LAUNCH;
+          kernel<<<grid, block, dyn, st>>>(ma, mb, a, b_t, out, ix, m, k, n, tm, tn, kp, nullptr);
+          break;
+        }
       }
       if (!mul) {
         if (pack)

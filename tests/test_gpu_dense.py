@@ -62,9 +62,17 @@ def test_logbmm_matches_reference_fixture(gb, golden, ci):
     assert_close(gb_, f("gb"), what="grad_b")
 
 
-@pytest.mark.parametrize("shape", SHAPES)
+# reductions longer than 128 steps: the register-staged kernel, or with GENBMM_B200_MAX_TMA=1 and K a multiple of 4
+# the TMA-staged one (ragged tiles, a partial last stage, a stage count that is not a multiple of the ring)
+MAX_SHAPES = SHAPES + [(2, 130, 260, 70), (1, 300, 516, 200), (3, 64, 132, 64), (1, 129, 1028, 65)]
+
+
+@pytest.mark.parametrize("staging", ["auto", "tma"])
+@pytest.mark.parametrize("shape", MAX_SHAPES)
 @pytest.mark.parametrize("name,mode", [("maxbmm", 1), ("prodmaxbmm", 3)])
-def test_max_semirings_bit_exact(gb, shape, name, mode):
+def test_max_semirings_bit_exact(gb, shape, name, mode, staging, monkeypatch):
+    if staging == "tma":
+        monkeypatch.setenv("GENBMM_B200_MAX_TMA", "1")
     B, M, K, N = shape
     gen = torch.Generator().manual_seed(7 + sum(shape))
     a, b, g = tied((B, M, K), gen), tied((B, K, N), gen), torch.rand(B, M, N, generator=gen)
