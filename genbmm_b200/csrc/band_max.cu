@@ -13,11 +13,13 @@
 // up to 218 KB); the winning tile of each result is then searched there for the first p whose term equals
 // the maximum, with no second trip to global memory.  Ascending p is ascending index in a's band for a fixed
 // row, so this is the reference's lowest-index tie rule; the stored index is p - i + a_lu.
+#include <cstdlib>
 #include <type_traits>
 #include <algorithm>
 
 #include "band.cuh"
 #include "tile.cuh"
+#include "tma.cuh"
 
 namespace gbmm {
 namespace {
@@ -81,6 +83,8 @@ struct MaxArgs {
   int nrb, ncb;
   float* out;
   int* idx;
+  int x_ninf, y_ninf;  // offset (from a batch element's base) of 16 bytes of -inf padding
+  int* error;          // set when a bounded wait ran out (band_max_w_kernel)
 };
 
 // Dynamic shared memory: the operand tiles of the block's whole reduction range (at most kMaxSteps tiles of
@@ -301,18 +305,223 @@ __global__ void __launch_bounds__(NT, 1) band_max_kernel(MaxArgs g) {
   }
 }
 
+
+// ---- 64 x 64 blocks, one 16 x 32 sub-block per warp, each warp on its own reduction range ----
+//
+// A term (i, o, p) is a band term only for |p - i| and |p - o| within the bands, so the smaller the sub-block
+// that shares one reduction range, the fewer padded terms it executes: 128 x 64 blocks in lockstep execute 49 000
+// terms per row of the result at 129 x 129 diagonals for 16 600 band terms; 16 x 32 sub-blocks, each walking only
+// the 16-step tiles that meet both of ITS bands, execute 28 000.  For that the warps of a CTA must not wait for
+// one another per tile: every thread requests all tiles of the block's range at once with 16-byte cp.async
+// copies and makes one deferred arrival per tile on that tile's mbarrier, and a warp waits only for the tiles it
+// reads.  At most 107 KB of tiles at 129 diagonals: two CTAs per SM, so one CTA's copies land while the other
+// multiplies.  Measured at 32 x 8192 x 129 diagonals: 1.33 ms against 1.78 ms for the lockstep kernel.  With
+// 8 x 4 results per thread (4 warps per CTA, 8 per SM) the same scheme took 1.76 ms: too few warps to cover the
+// shared-memory and pipe latencies; with 4 x 4 the CTA has 8 warps.
+//
+// Shared-memory layout of a 16-step tile: [quad of steps][row][4 steps], one 128-bit load per row and quad; a
+// thread's rows are ty + 4 i and its columns tx + 8 j, so the lanes of a warp read consecutive 16-byte cells
+// (no bank conflicts), and the two halves of a loaded quad are the (k, k+1) pairs of the packed add.
+constexpr int WB = 64;
+constexpr int WT = 4 * WB * 4 + 4;   // floats per operand tile; + 4: the search reads the same cell of different tiles
+constexpr int kMaxTilesW = 26;       // 26 * 2 * WT * 4 bytes = 214 KB
+__host__ __device__ constexpr size_t w_smem_bytes(int tiles) { return (size_t)tiles * 2 * WT * sizeof(float); }
+
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+// one arrival on `bar` once every cp.async this thread has issued so far has landed (counted in the barrier's
+// initial count: .noinc)
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// IR rows per thread (4 columns): 8 -> 4 warps of 32 x 32 sub-blocks, 4 -> 8 warps of 16 x 32.
+template <int IR, int UQ>
+__global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
+  constexpr int WNT = 1024 / IR, WROWS = 4 * IR;
+  extern __shared__ __align__(16) float smem_dyn[];
+  __shared__ __align__(8) uint64_t landed[kMaxTilesW];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ty = lane >> 3, tx = lane & 7;
+  const int64_t id = blockIdx.x;
+  const int cbi = (int)(id % g.ncb), rbk = (int)((id / g.ncb) % g.nrb);
+  const int64_t bt = id / ((int64_t)g.ncb * g.nrb);
+  const int r0 = rbk * WB;
+  const int lo = r0 - g.r_lu;
+  const int cfirst = lo >= 0 ? lo / WB : -((-lo + WB - 1) / WB);
+  const int c0 = (cfirst + cbi) * WB;
+  const int r_ld = g.Wo - 1 - g.r_lu;
+  if (c0 > r0 + WB - 1 + r_ld) return;  // beyond the band: owns no cell
+  const int s_lo = max(max(r0 - g.a_lu, c0 - g.b_lu), 0);
+  int s_hi = min(min(r0 + WB - 1 + g.a_ld, c0 + WB - 1 + g.b_ld), g.n - 1);
+  if (c0 >= g.n || c0 + WB - 1 < 0) s_hi = s_lo - 1;  // outside the matrix: only zeros to write
+  const int s0 = s_lo & ~(BK - 1);
+  const int nt = s_hi >= s_lo ? (s_hi - s0) / BK + 1 : 0;  // <= the launch's tile count by the eligibility rule
+  float* sx = smem_dyn;
+  float* sy = smem_dyn + (size_t)nt * WT;
+
+  if (tid == 0) {
+    for (int t = 0; t < nt; ++t) mbar_init(&landed[t], WNT);
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  // Requests, in tile order.  Chunk f of a tile: row f / 4, quad f % 4 (four threads cover the 64 contiguous
+  // bytes a row contributes).  Rows and columns outside the matrix read 16 bytes of -inf padding instead.
+  {
+    const float* xbase = g.xs + bt * g.x_bstride;
+    const float* ybase = g.ys + bt * g.y_bstride;
+    constexpr int NQ = 256 / WNT;  // 256 chunks of 16 bytes per tile and operand
+    const float* xsrc[NQ];
+    const float* ysrc[NQ];
+    int dofs[NQ];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+      const int f = tid + q * WNT, row = f >> 2, quad = f & 3;
+      const int i = r0 + row, c = c0 + row;
+      dofs[q] = (quad * WB + row) * 4;
+      xsrc[q] = i < g.n ? xbase + g.x_kofs + (int64_t)i * g.x_rstride + s0 + 4 * quad : nullptr;
+      ysrc[q] = (c >= 0 && c < g.n) ? ybase + g.y_kofs + (int64_t)c * g.y_rstride + s0 + 4 * quad : nullptr;
+    }
+    for (int t = 0; t < nt; ++t) {
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        cp_async16(sx + (size_t)t * WT + dofs[q], xsrc[q] ? xsrc[q] + t * BK : xbase + g.x_ninf);
+        cp_async16(sy + (size_t)t * WT + dofs[q], ysrc[q] ? ysrc[q] + t * BK : ybase + g.y_ninf);
+      }
+      cp_async_arrive(&landed[t]);
+    }
+  }
+
+  // this warp's sub-block and the tiles that meet both of its bands
+  const int rl0 = (warp >> 1) * WROWS, cl0 = (warp & 1) * 32;
+  const int w_lo = max(max(r0 + rl0 - g.a_lu, c0 + cl0 - g.b_lu), s_lo);
+  const int w_hi = min(min(r0 + rl0 + WROWS - 1 + g.a_ld, c0 + cl0 + 31 + g.b_ld), s_hi);
+  const int t_lo = w_hi >= w_lo ? (w_lo - s0) / BK : 0;
+  const int t_hi = w_hi >= w_lo ? (w_hi - s0) / BK : -1;
+
+  // The warps of a CTA are at different tiles at any moment and two CTAs share the SM, so the code must stay
+  // small enough for the instruction cache: one copy of the tile body (the maxima before the tile are copied
+  // aside for the "did this tile raise it" test instead of alternating two register sets) and a rolled search
+  // loop (with 8 x 4 results per thread, everything unrolled and two alternating sets, the schedulers sat
+  // without instructions five cycles for every one they issued).
+  float Y[IR][4];
+  unsigned cidp[IR];
+#pragma unroll
+  for (int i = 0; i < IR; ++i) {
+    cidp[i] = 0xffffffffu;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) Y[i][j] = kFloor;
+  }
+  bool fail = false;
+#pragma unroll 1
+  for (int t = t_lo; t <= t_hi; ++t) {
+    if (!mbar_wait_bounded(&landed[t], 0)) fail = true;
+    const float* xt = sx + (size_t)t * WT + (rl0 + ty) * 4;
+    const float* yt = sy + (size_t)t * WT + (cl0 + tx) * 4;
+    float P[IR][4];
+#pragma unroll
+    for (int i = 0; i < IR; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) P[i][j] = Y[i][j];
+#pragma unroll UQ
+    for (int q = 0; q < BK / 4; ++q) {
+      ulonglong2 xq[IR], yq[4];
+#pragma unroll
+      for (int i = 0; i < IR; ++i) xq[i] = *reinterpret_cast<const ulonglong2*>(xt + (q * WB + 4 * i) * 4);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) yq[j] = *reinterpret_cast<const ulonglong2*>(yt + (q * WB + 8 * j) * 4);
+#pragma unroll
+      for (int i = 0; i < IR; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float v0, v1, v2, v3;
+          unpack2(add2(xq[i].x, yq[j].x), v0, v1);
+          unpack2(add2(xq[i].y, yq[j].y), v2, v3);
+          Y[i][j] = max3(max3(Y[i][j], v0, v1), v2, v3);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < IR; ++i) {  // strict `>`: an equal maximum in a later tile keeps the index
+      if (Y[i][0] > P[i][0]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3214);
+      if (Y[i][1] > P[i][1]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3240);
+      if (Y[i][2] > P[i][2]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3410);
+      if (Y[i][3] > P[i][3]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x4210);
+    }
+  }
+  if (__any_sync(0xffffffffu, fail) && lane == 0) atomicExch(g.error, 1);
+
+  // Y holds the maxima; the winning tile of every result is still in shared memory: search it from the last
+  // step down, so the lowest matching p is the assignment that sticks; the stored value is that term itself.
+  float* ob = g.out + bt * g.n * (int64_t)g.Wo;
+  int* ib = g.idx + bt * g.n * (int64_t)g.Wo;
+#pragma unroll
+  for (int i = 0; i < IR; ++i) {
+    const int ml = rl0 + ty + 4 * i, m = r0 + ml;
+    if (m >= g.n) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int cl = cl0 + tx + 8 * j, c = c0 + cl;
+      const int cell = c - m + g.r_lu;
+      if (cell < 0 || cell >= g.Wo) continue;
+      const bool inside = c >= 0 && c < g.n;
+      const unsigned c8 = (cidp[i] >> (8 * j)) & 0xffu;
+      float val = Y[i][j];
+      int p = -1;
+      if (inside && c8 != 0xffu) {
+        const float* xt = sx + (size_t)c8 * WT + ml * 4;
+        const float* yt = sy + (size_t)c8 * WT + cl * 4;
+#pragma unroll 1
+        for (int q = BK / 4 - 1; q >= 0; --q) {
+          const ulonglong2 xv = *reinterpret_cast<const ulonglong2*>(xt + q * WB * 4);
+          const ulonglong2 yv = *reinterpret_cast<const ulonglong2*>(yt + q * WB * 4);
+          float v0, v1, v2, v3;
+          unpack2(add2(xv.x, yv.x), v0, v1);
+          unpack2(add2(xv.y, yv.y), v2, v3);
+          if (v3 == Y[i][j]) p = 4 * q + 3;
+          if (v2 == Y[i][j]) p = 4 * q + 2;
+          if (v1 == Y[i][j]) p = 4 * q + 1;
+          if (v0 == Y[i][j]) p = 4 * q;
+        }
+        // the stored value is the matching term itself: only for a zero can it differ from the maximum (in
+        // sign), so that is the one case that reads the term again
+        if (val == 0.f && p >= 0) val = __fadd_rn(xt[(p >> 2) * WB * 4 + (p & 3)], yt[(p >> 2) * WB * 4 + (p & 3)]);
+        if (p >= 0) p += s0 + (int)c8 * BK;
+      }
+      const int64_t e = (int64_t)m * g.Wo + cell;
+      ob[e] = inside ? val : 0.f;  // cells outside the matrix stay zero (banded_cuda_kernel.cu:38)
+      ib[e] = inside ? (p >= 0 ? p - m + g.a_lu : -1) : 0;
+    }
+  }
+}
+
+// tiles of 16 steps in the longest reduction range of a 64 x 64 block
+int w_tiles(const BandDims& d) {
+  const int64_t range = std::min<int64_t>(WB - 1 + d.Wa(), WB - 1 + d.Wb()) + (BK - 1);
+  return (int)ceil_div(range, BK);
+}
+
 }  // namespace
 
 // declared in band.cuh
+static bool lockstep_blocks_wanted() {  // GENBMM_B200_BAND_MAX=block keeps the 128 x 64 blocks in lockstep
+  const char* mode = getenv("GENBMM_B200_BAND_MAX");
+  return mode && mode[0] == 'b';
+}
+
 bool band_max_fast_eligible(const BandDims& d) {
-  // a block's whole reduction range stays in shared memory: at most kMaxSteps tiles of 16 steps
+  // a block's whole reduction range stays in shared memory: at most kMaxTilesW tiles of 16 steps for the 64 x 64
+  // blocks (the narrower band up to 338 wide), kMaxSteps for the 128 x 64 blocks
+  if (d.Wa() < 32 || d.Wb() < 32 || d.n < 128 || d.n >= (1LL << 30)) return false;
+  if (!lockstep_blocks_wanted()) return w_tiles(d) <= kMaxTilesW;
   const int64_t range = std::min<int64_t>(BM - 1 + d.Wa(), BN - 1 + d.Wb()) + 2 * (BK - 1);
-  return d.Wa() >= 32 && d.Wb() >= 32 && d.n >= 128 && d.n < (1LL << 30) && range <= kMaxSteps * BK;
+  return range <= kMaxSteps * BK;
 }
 
 int64_t band_max_workspace_bytes(int64_t B, const BandDims& d) {
   const MaxSkew sa = make_max_skew(d.a_lu, d.Wa(), d.n), sb = make_max_skew(d.b_lu, d.Wb(), d.n);
-  return (int64_t)sizeof(float) * (max_skew_floats(sa, B) + max_skew_floats(sb, B));
+  return (int64_t)sizeof(float) * (max_skew_floats(sa, B) + max_skew_floats(sb, B) + 64);  // + the error word
 }
 
 int band_max_workspace_init(void* ws, int64_t bytes, cudaStream_t st) {
@@ -349,6 +558,27 @@ int band_max_forward(const float* a, const float* b, float* out, int* idx, const
   g.ncb = (g.Wo + BM - 1 + BN - 1) / BN + 1;
   g.out = out;
   g.idx = idx;
+  if (!lockstep_blocks_wanted()) {
+    g.x_ninf = (sa.off + d.Wa() + 3) & ~3;  // the first whole 16 bytes of a row's padding
+    g.y_ninf = (sb.off + d.Wb() + 3) & ~3;
+    g.error = reinterpret_cast<int*>(ys + max_skew_floats(sb, B));
+    g.nrb = (int)ceil_div(d.n, WB);
+    g.ncb = (g.Wo + 2 * (WB - 1)) / WB + 1;
+    const int64_t wblocks = B * g.nrb * g.ncb;
+    if (wblocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+    const size_t wsmem = w_smem_bytes(w_tiles(d));
+    auto kern = band_max_w_kernel<4, 4>;
+    if (cudaMemsetAsync(g.error, 0, sizeof(int), st) != cudaSuccess ||
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)w_smem_bytes(kMaxTilesW)) !=
+            cudaSuccess ||
+        // two CTAs per SM need the largest shared-memory carveout
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=
+            cudaSuccess)
+      return GBMM_ERR_LAUNCH;
+    kern<<<(unsigned)wblocks, 256, wsmem, st>>>(g);
+    if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
+    return launch_poison_on_error(g.error, out, B * d.n * d.Wo(), nullptr, 0, st);
+  }
   const int64_t blocks = B * g.nrb * g.ncb;
   if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
   const size_t smem = max_smem_bytes(kMaxSteps);

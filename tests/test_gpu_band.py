@@ -116,6 +116,30 @@ def test_log_semiring_other_tensor_feeds(gb, case, monkeypatch, feed):
     assert_close(gb_, dB, what="grad_b")
 
 
+@pytest.mark.parametrize("case", [c for c in CASES if c[1] >= 128 and min(c[2] + c[3], c[4] + c[5]) >= 31]
+                         + [(2, 640, 64, 64, 64, 64), (1, 333, 100, 20, 10, 90), (2, 256, 31, 0, 0, 31),
+                            (1, 700, 150, 100, 120, 140)])
+@pytest.mark.parametrize("blocks", ["warp-ranges", "lockstep"])
+def test_max_semiring_both_block_kernels(gb, case, monkeypatch, blocks):
+    """multiply_max on the two kernels that read skewed copies: 64 x 64 blocks whose warps walk their own
+    reduction ranges (default) and 128 x 64 blocks in lockstep (GENBMM_B200_BAND_MAX=block).  Values and
+    indices bit for bit, with ties and with rows that nothing lifts above -1e9."""
+    if blocks == "lockstep":
+        monkeypatch.setenv("GENBMM_B200_BAND_MAX", "block")
+    B, n, alu, ald, blu, bld = case
+    gen = torch.Generator().manual_seed(sum(case) + 5)
+    a = (torch.randn(B, n, alu + ald + 1, generator=gen) * 2).round() / 2
+    b = (torch.randn(B, n, blu + bld + 1, generator=gen) * 2).round() / 2
+    a[:, n // 3] = -2e9          # a row whose terms all stay below the reference's floor
+    b[:, n // 2, ::2] = float("-inf")
+    from genbmm_b200 import _native
+    out_gpu, idx_gpu, _ = _native.forward_band(a.cuda(), alu, ald, b.cuda(), blu, bld, 1)
+    g = torch.rand(B, n, alu + ald + blu + bld + 1, generator=gen)
+    out, idx, _, _, _ = oracle.band_fwd_bwd(1, a, alu, ald, b, blu, bld, g)
+    assert_equal_bits(out_gpu, out, "max value")
+    assert_equal_bits(idx_gpu, idx, "max index")
+
+
 @pytest.mark.parametrize("ci", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("method,name", [("multiply", "mul"), ("multiply_log", "log"), ("multiply_max", "max")])
 def test_band_products_match_reference_fixture(gb, golden, ci, method, name):
