@@ -378,7 +378,8 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
     int dofs[NQ];
 #pragma unroll
     for (int q = 0; q < NQ; ++q) {
-      const int f = tid + q * WNT, row = f >> 2, quad = f & 3;
+      // 8 lanes take the same quad of 8 consecutive rows: 128 contiguous bytes of shared memory per quarter warp
+      const int f = tid + q * WNT, row = (f >> 5) * 8 + (f & 7), quad = (f >> 3) & 3;
       const int i = r0 + row, c = c0 + row;
       dofs[q] = (quad * WB + row) * 4;
       xsrc[q] = i < g.n ? xbase + g.x_kofs + (int64_t)i * g.x_rstride + s0 + 4 * quad : nullptr;
@@ -425,8 +426,7 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
     for (int i = 0; i < IR; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) P[i][j] = Y[i][j];
-#pragma unroll UQ
-    for (int q = 0; q < BK / 4; ++q) {
+    auto quad = [&](int q) {
       ulonglong2 xq[IR], yq[4];
 #pragma unroll
       for (int i = 0; i < IR; ++i) xq[i] = *reinterpret_cast<const ulonglong2*>(xt + (q * WB + 4 * i) * 4);
@@ -441,6 +441,15 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
           unpack2(add2(xq[i].y, yq[j].y), v2, v3);
           Y[i][j] = max3(max3(Y[i][j], v0, v1), v2, v3);
         }
+    };
+    if (t > t_lo && t < t_hi) {
+#pragma unroll UQ
+      for (int q = 0; q < BK / 4; ++q) quad(q);
+    } else {  // the first and the last tile of the warp's range: only the quads that meet it
+      const int qa = t == t_lo ? ((w_lo - s0) & (BK - 1)) >> 2 : 0;
+      const int qb = t == t_hi ? ((w_hi - s0) & (BK - 1)) >> 2 : BK / 4 - 1;
+#pragma unroll 1
+      for (int q = qa; q <= qb; ++q) quad(q);
     }
 #pragma unroll
     for (int i = 0; i < IR; ++i) {  // strict `>`: an equal maximum in a later tile keeps the index
@@ -456,42 +465,60 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
   // step down, so the lowest matching p is the assignment that sticks; the stored value is that term itself.
   float* ob = g.out + bt * g.n * (int64_t)g.Wo;
   int* ib = g.idx + bt * g.n * (int64_t)g.Wo;
+  // The four results of a row are searched side by side (one rolled loop over the quads, eight independent
+  // loads in flight): one result at a time, the loop ran at the latency of a shared-memory load per quad.
 #pragma unroll
   for (int i = 0; i < IR; ++i) {
     const int ml = rl0 + ty + 4 * i, m = r0 + ml;
     if (m >= g.n) continue;
+    const float* xt[4];
+    const float* yt[4];
+    int p[4], cell[4];
+    bool hunt[4], inside[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int cl = cl0 + tx + 8 * j, c = c0 + cl;
-      const int cell = c - m + g.r_lu;
-      if (cell < 0 || cell >= g.Wo) continue;
-      const bool inside = c >= 0 && c < g.n;
+      cell[j] = c - m + g.r_lu;
+      inside[j] = c >= 0 && c < g.n;
       const unsigned c8 = (cidp[i] >> (8 * j)) & 0xffu;
-      float val = Y[i][j];
-      int p = -1;
-      if (inside && c8 != 0xffu) {
-        const float* xt = sx + (size_t)c8 * WT + ml * 4;
-        const float* yt = sy + (size_t)c8 * WT + cl * 4;
+      hunt[j] = cell[j] >= 0 && cell[j] < g.Wo && inside[j] && c8 != 0xffu;
+      const unsigned tile = hunt[j] ? c8 : 0u;  // a result with nothing to find reads tile 0 and ignores it
+      xt[j] = sx + (size_t)tile * WT + ml * 4;
+      yt[j] = sy + (size_t)tile * WT + cl * 4;
+      p[j] = -1;
+    }
+    if (hunt[0] || hunt[1] || hunt[2] || hunt[3]) {
 #pragma unroll 1
-        for (int q = BK / 4 - 1; q >= 0; --q) {
-          const ulonglong2 xv = *reinterpret_cast<const ulonglong2*>(xt + q * WB * 4);
-          const ulonglong2 yv = *reinterpret_cast<const ulonglong2*>(yt + q * WB * 4);
+      for (int q = BK / 4 - 1; q >= 0; --q) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const ulonglong2 xv = *reinterpret_cast<const ulonglong2*>(xt[j] + q * WB * 4);
+          const ulonglong2 yv = *reinterpret_cast<const ulonglong2*>(yt[j] + q * WB * 4);
           float v0, v1, v2, v3;
           unpack2(add2(xv.x, yv.x), v0, v1);
           unpack2(add2(xv.y, yv.y), v2, v3);
-          if (v3 == Y[i][j]) p = 4 * q + 3;
-          if (v2 == Y[i][j]) p = 4 * q + 2;
-          if (v1 == Y[i][j]) p = 4 * q + 1;
-          if (v0 == Y[i][j]) p = 4 * q;
+          if (v3 == Y[i][j]) p[j] = 4 * q + 3;
+          if (v2 == Y[i][j]) p[j] = 4 * q + 2;
+          if (v1 == Y[i][j]) p[j] = 4 * q + 1;
+          if (v0 == Y[i][j]) p[j] = 4 * q;
         }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (cell[j] < 0 || cell[j] >= g.Wo) continue;
+      float val = Y[i][j];
+      int pj = hunt[j] ? p[j] : -1;
+      if (pj >= 0) {
         // the stored value is the matching term itself: only for a zero can it differ from the maximum (in
         // sign), so that is the one case that reads the term again
-        if (val == 0.f && p >= 0) val = __fadd_rn(xt[(p >> 2) * WB * 4 + (p & 3)], yt[(p >> 2) * WB * 4 + (p & 3)]);
-        if (p >= 0) p += s0 + (int)c8 * BK;
+        if (val == 0.f)
+          val = __fadd_rn(xt[j][(pj >> 2) * WB * 4 + (pj & 3)], yt[j][(pj >> 2) * WB * 4 + (pj & 3)]);
+        pj += s0 + (int)((cidp[i] >> (8 * j)) & 0xffu) * BK;
       }
-      const int64_t e = (int64_t)m * g.Wo + cell;
-      ob[e] = inside ? val : 0.f;  // cells outside the matrix stay zero (banded_cuda_kernel.cu:38)
-      ib[e] = inside ? (p >= 0 ? p - m + g.a_lu : -1) : 0;
+      const int64_t e = (int64_t)m * g.Wo + cell[j];
+      ob[e] = inside[j] ? val : 0.f;  // cells outside the matrix stay zero (banded_cuda_kernel.cu:38)
+      ib[e] = inside[j] ? (pj >= 0 ? pj - m + g.a_lu : -1) : 0;
     }
   }
 }
