@@ -543,27 +543,45 @@ __global__ void __launch_bounds__(RB_T) band_route_b_rows_kernel(const int* __re
   // steps s = 0 .. 31 + Wo - 1: lane l looks at i = o - r_ld - l' ... every lane walks ITS OWN ascending i range
   // [o - r_ld, o + r_lu], offset so that the lanes of a warp are at the same i (hence at consecutive cells)
   // whenever their rows are consecutive: i = (o - lane) - r_ld + s
-  const int64_t ibase = o - lane - r_ld;
   const int steps = 31 + Wo;
-  constexpr int U = 8;   // cells fetched together: the walk is otherwise one global-load latency per step
-  for (int s0 = 0; s0 < steps; s0 += U) {
-    int ja[U];
-    float gv[U];
+  // 32-bit walk (n < 2^30): at step s this thread is at i = i0 + s, jo = jo0 - s, i.e. Wo - 1 elements further
+  // on in idx / g per step; the steps at which that cell exists are [s_lo, s_hi)
+  const int n32 = (int)n, i0 = (int)o - lane - r_ld, jo0 = lane + Wo - 1;
+  const int s_lo = max(max(0, -i0), jo0 - Wo + 1), s_hi = live ? min(min(steps, n32 - i0), jo0 + 1) : 0;
+  const int* ip = ib + (int64_t)i0 * Wo + jo0;
+  const float* gp = gb + (int64_t)i0 * Wo + jo0;
+  const int stride = Wo - 1;
+  // U cells are fetched together and the next U are requested before this group is added up, so that the walk
+  // costs one global-load latency per 2U steps overlapped with the additions (the histogram updates of a group
+  // are a dependent chain through shared memory: the compiler cannot tell that two cells name different buckets).
+  constexpr int U = 16;
+  int ja[2][U];
+  float gv[2][U];
+  auto fetch = [&](int s0, int (&jd)[U], float (&gd)[U]) {
+    const int* ips = ip + (int64_t)s0 * stride;
+    const float* gps = gp + (int64_t)s0 * stride;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int64_t i = ibase + s0 + u, jo = o - i + r_lu;
-      const bool ok = live && s0 + u < steps && i >= 0 && i < n && jo >= 0 && jo < Wo;
-      ja[u] = ok ? __ldg(ib + i * Wo + jo) : -1;
-      gv[u] = ok ? __ldg(gb + i * Wo + jo) : 0.f;
+      const bool ok = s0 + u >= s_lo && s0 + u < s_hi;
+      jd[u] = ok ? __ldg(ips + u * stride) : -1;
+      gd[u] = ok ? __ldg(gps + u * stride) : 0.f;
     }
+  };
+  auto add_up = [&](int s0, const int (&jd)[U], const float (&gd)[U]) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int64_t i = ibase + s0 + u, jo = o - i + r_lu;
-      const int k2 = ja[u] - (int)jo + Wb - 1;
-      const int64_t p = i + ja[u] - d.a_lu;
-      if (ja[u] >= 0 && ja[u] < Wa && k2 >= 0 && k2 < Wb && p >= 0 && p < n)
-        hist[k2] = __fadd_rn(hist[k2], gv[u]);
+      const int s = s0 + u;
+      const int k2 = jd[u] - (jo0 - s) + Wb - 1, p = i0 + s + jd[u] - d.a_lu;
+      if ((unsigned)jd[u] < (unsigned)Wa && (unsigned)k2 < (unsigned)Wb && (unsigned)p < (unsigned)n32)
+        hist[k2] = __fadd_rn(hist[k2], gd[u]);
     }
+  };
+  fetch(0, ja[0], gv[0]);
+  for (int s0 = 0; s0 < steps; s0 += 2 * U) {
+    fetch(s0 + U, ja[1], gv[1]);
+    add_up(s0, ja[0], gv[0]);
+    fetch(s0 + 2 * U, ja[0], gv[0]);
+    add_up(s0 + U, ja[1], gv[1]);
   }
   __syncthreads();
   for (int r = warp; r < RB_T; r += RB_T / 32) {
@@ -742,7 +760,7 @@ static int route_max_backward(const float* grad_out, const int* idx, float* grad
       const char* e = getenv("GENBMM_B200_BAND_ROUTE_B");
       return !(e && e[0] == 'w');   // "warp": the warp-per-row kernel
     }();
-    if (by_rows && smem_rows <= (size_t)100 * 1024) {   // two CTAs per SM
+    if (by_rows && smem_rows <= (size_t)100 * 1024 && d.n < (1LL << 30)) {   // at least two CTAs per SM; 32-bit walk
       const int64_t rows = B * d.n, rblocks = ceil_div(rows, RB_T);
       if (rblocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
       if (smem_rows > 48 * 1024 && !allow_smem(band_route_b_rows_kernel, smem_rows)) return GBMM_ERR_LAUNCH;
