@@ -113,7 +113,16 @@ __global__ void __launch_bounds__(256) gather_blocks_kernel(const float* __restr
   float4* dp = reinterpret_cast<float4*>(dst + d * elems);
   if (m >= 0) {
     const float4* sp = reinterpret_cast<const float4*>(src + m * elems);
-    for (int64_t e = lo / 4 + threadIdx.x; e < hi / 4; e += 256) dp[e] = __ldg(sp + e);
+    if (hi - lo == 4096) {  // a whole slice: the thread's four loads are in flight together
+      const int64_t e = lo / 4 + threadIdx.x;
+      const float4 v0 = __ldg(sp + e), v1 = __ldg(sp + e + 256), v2 = __ldg(sp + e + 512), v3 = __ldg(sp + e + 768);
+      dp[e] = v0;
+      dp[e + 256] = v1;
+      dp[e + 512] = v2;
+      dp[e + 768] = v3;
+    } else {
+      for (int64_t e = lo / 4 + threadIdx.x; e < hi / 4; e += 256) dp[e] = __ldg(sp + e);
+    }
   } else {
     for (int64_t e = lo / 4 + threadIdx.x; e < hi / 4; e += 256) {
       float v[4];
