@@ -856,7 +856,7 @@ def main():
     ap.add_argument("--batch", type=int, default=32, help="1024^3 problems per GPU per step")
     ap.add_argument("--inner-repeats", type=int, default=0,
                     help="run every counted step this many times (0: as many as make the timed region 2 s)")
-    ap.add_argument("--e2e-chunks", type=int, default=16, help="batch chunks of the host pipeline (end-to-end leg)")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the host pipeline (end-to-end leg)")
     ap.add_argument("--e2e-graph", type=int, default=0, help="1: the host pipeline replays one CUDA graph per chunk")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-cuda", action="store_true")

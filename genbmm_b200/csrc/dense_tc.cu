@@ -294,6 +294,190 @@ __global__ void __launch_bounds__(TNT, 1) tc_gemm_kernel(const __grid_constant__
   }
 }
 
+// ---- split-in-shared-memory variant -------------------------------------------------------------
+// The same product from ONE unsplit fp32 copy per operand (the split passes write half the bytes, the product
+// reads half): a TMA warp lands the raw tile in the stage's `hi` buffer, eight splitter warps rewrite it in place
+// (hi = tf32(x) where x was, lo = x - hi at the same offset of the `lo` buffer; the split does not care which
+// layout the tile has) and hand the stage to the MMA warp (fence.proxy.async, one arrival per splitter warp on
+// `full`).  Selected by GENBMM_B200_TC_SPLIT=1 (see unsplit_mode for what was measured).
+// Roles: warps 0-7 split, 8 issues the MMAs, 9-16 are the epilogue, 17 is the TMA producer.
+constexpr int DSPW = 8;
+constexpr int DSP_NT = (DSPW + 1 + TEW + 1) * 32;
+constexpr int DSP_TMA_WARP = DSPW + 1 + TEW;
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <int EPI, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(DSP_NT, 1) tc_gemm_sp_kernel(const __grid_constant__ CUtensorMap ma,
+                                                               const __grid_constant__ CUtensorMap mb, TcEpi ep, int R,
+                                                               int I, int J, int tiles_i, int tiles_j,
+                                                               int64_t total_tiles) {
+  extern __shared__ unsigned char smem_raw[];
+  TcSmem& sm = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int nt = (R + TK - 1) / TK;
+  const int nchunks = (nt + TCH - 1) / TCH;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < TST; ++s) {
+      mbar_init(&sm.raw_full[s], 1);
+      mbar_init(&sm.full[s], DSPW);
+      mbar_init(&sm.empty[s], 1);
+    }
+#pragma unroll
+    for (int q = 0; q < TNB; ++q) {
+      mbar_init(&sm.chunk_full[q], 1);
+      mbar_init(&sm.chunk_empty[q], TEW);
+    }
+    fence_barrier_init();
+  }
+  if (warp == DSPW) {  // the whole warp allocates; the same warp frees at the end
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  bool fail = false;
+
+  if (warp == DSP_TMA_WARP) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int64_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+        const int j0 = (int)(tile % tiles_j) * TN, i0 = (int)((tile / tiles_j) % tiles_i) * TM;
+        const int bt = (int)(tile / ((int64_t)tiles_j * tiles_i));
+        for (int t = 0; t < nt; ++t, ++it) {
+          const int s = it % TST;
+          if (it >= TST && !mbar_wait_bounded(&sm.empty[s], ((it / TST) - 1) & 1)) {
+            fail = true;
+            break;
+          }
+          mbar_arrive_expect_tx(&sm.raw_full[s], 2 * kTileBytes);
+          tma_tile<A_MN>(sm.a_hi[s], &ma, &sm.raw_full[s], t * TK, i0, bt);
+          tma_tile<B_MN>(sm.b_hi[s], &mb, &sm.raw_full[s], t * TK, j0, bt);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp < DSPW) {
+    uint32_t it = 0;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+      for (int t = 0; t < nt; ++t, ++it) {
+        const int s = it % TST;
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.raw_full[s], (it / TST) & 1))) {
+          fail = true;
+          break;
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float4* hi = reinterpret_cast<float4*>(half ? sm.b_hi[s] : sm.a_hi[s]);
+          float4* lo = reinterpret_cast<float4*>(half ? sm.b_lo[s] : sm.a_lo[s]);
+          constexpr int NQ = TM * TK / 4 / (DSPW * 32);
+          float4 x[NQ];
+#pragma unroll
+          for (int q = 0; q < NQ; ++q) x[q] = hi[tid + q * DSPW * 32];
+#pragma unroll
+          for (int q = 0; q < NQ; ++q) {
+            const float4 h = make_float4(tf32_round(x[q].x), tf32_round(x[q].y), tf32_round(x[q].z),
+                                         tf32_round(x[q].w));
+            hi[tid + q * DSPW * 32] = h;
+            lo[tid + q * DSPW * 32] = make_float4(x[q].x - h.x, x[q].y - h.y, x[q].z - h.z, x[q].w - h.w);
+          }
+        }
+        fence_async_shared();  // these generic-proxy stores, before the tensor core's async-proxy reads
+        __syncwarp();
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.full[s])) : "memory");
+      }
+    }
+  } else if (warp == DSPW) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = kIdesc | (A_MN ? 1u << 15 : 0u) | (B_MN ? 1u << 16 : 0u);
+      uint32_t it = 0, gc = 0;
+      for (int64_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+        for (int t = 0; t < nt; ++t, ++it) {
+          const int s = it % TST, buf = gc % TNB;
+          const bool chunk_start = (t % TCH) == 0;
+          if (chunk_start && gc >= TNB && !mbar_wait_bounded(&sm.chunk_empty[buf], ((gc / TNB) - 1) & 1)) {
+            fail = true;
+            break;
+          }
+          if (!mbar_wait_bounded(&sm.full[s], (it / TST) & 1)) {
+            fail = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t acc = tmem + (uint32_t)(buf * TN);
+#pragma unroll
+          for (int kk = 0; kk < TK / 8; ++kk) {
+            const int ko = kk * 8 * (int)sizeof(float);
+            const uint64_t ah = A_MN ? umma_desc_mn(sm.a_hi[s], kk) : umma_desc(sm.a_hi[s], ko);
+            const uint64_t al = A_MN ? umma_desc_mn(sm.a_lo[s], kk) : umma_desc(sm.a_lo[s], ko);
+            const uint64_t bh = B_MN ? umma_desc_mn(sm.b_hi[s], kk) : umma_desc(sm.b_hi[s], ko);
+            const uint64_t bl = B_MN ? umma_desc_mn(sm.b_lo[s], kk) : umma_desc(sm.b_lo[s], ko);
+            umma_tf32(acc, al, bh, idesc, (!chunk_start || kk > 0) ? 1u : 0u);
+            umma_tf32(acc, ah, bl, idesc, 1u);
+            umma_tf32(acc, ah, bh, idesc, 1u);
+          }
+          umma_commit(&sm.empty[s]);
+          if ((t % TCH) == TCH - 1 || t == nt - 1) {
+            umma_commit(&sm.chunk_full[buf]);
+            ++gc;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int ew = warp - (DSPW + 1), quad = warp % 4;  // TMEM lanes this warp may read: 32*quad .. 32*quad+31
+    const int cbase = (ew / 4) * TEC;
+    float* blk = sm.epi[ew];
+    uint32_t gc = 0;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+      const int j0 = (int)(tile % tiles_j) * TN, i0 = (int)((tile / tiles_j) % tiles_i) * TM;
+      const int bt = (int)(tile / ((int64_t)tiles_j * tiles_i));
+      float sum[TEC];
+#pragma unroll
+      for (int q = 0; q < TEC; ++q) sum[q] = 0.f;
+      if (EPI == TC_GRAD) prefetch_src<TEC>(ep.src, bt, i0 + quad * 32, j0 + cbase, I, J, lane);
+      for (int chunk = 0; chunk < nchunks; ++chunk, ++gc) {
+        const int buf = gc % TNB;
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&sm.chunk_full[buf], (gc / TNB) & 1))) {
+          fail = true;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < TEC / 32; ++c) {
+          float v[32];
+          tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * TN + cbase + c * 32), v);
+#pragma unroll
+          for (int q = 0; q < 32; ++q) sum[c * 32 + q] += v[q];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.chunk_empty[buf])) : "memory");
+      }
+      if (fail) break;
+      bool bad = false;
+      store_sums<EPI, TEC>(sum, blk, ep, bt, i0 + quad * 32, j0 + cbase, I, J, lane, bad);
+      if (EPI == TC_LOG) {
+        if (__any_sync(0xffffffffu, bad) && lane == 0) atomicExch(ep.flags + tile, 1);
+      }
+    }
+  }
+  if (__any_sync(0xffffffffu, fail) && lane == 0) atomicExch(ep.error, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == DSPW) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
 // ---- CTA-pair variant ------------------------------------------------------------------------
 // The same product with tcgen05.mma.cta_group::2: a cluster of two CTAs (two SMs) owns a 256x256
 // result tile.  Each CTA loads 128 rows of A and 128 of the 256 columns of B; one thread of the
@@ -561,12 +745,12 @@ __global__ void __launch_bounds__(256) split_transform_kernel(const float* __res
     if (KIND == 1) v = exp_sfu(x[k] - sc[k]);
     if (KIND == 2) v = dead ? 0.f : gv[k] * exp_sfu((sr + sc[k]) - x[k]);
     if (!full && c + k >= C) v = 0.f;
-    hi[k] = tf32_round(v);
+    hi[k] = lo_out ? tf32_round(v) : v;   // lo_out == nullptr: one unsplit copy (split in shared memory later)
     lo[k] = v - hi[k];
   }
   // pitch % 32 == 0 and c % 4 == 0: the group is 16-byte aligned and lies inside the row's pitch
   *reinterpret_cast<float4*>(hi_out + row * pitch + c) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-  *reinterpret_cast<float4*>(lo_out + row * pitch + c) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+  if (lo_out) *reinterpret_cast<float4*>(lo_out + row * pitch + c) = make_float4(lo[0], lo[1], lo[2], lo[3]);
 }
 
 template <int KIND>
@@ -621,11 +805,11 @@ __global__ void __launch_bounds__(256) rowsplit_kernel(const float* __restrict__
       float h[4], l[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        h[k] = tf32_round(v[k]);
+        h[k] = lo_out ? tf32_round(v[k]) : v[k];
         l[k] = v[k] - h[k];
       }
       hp[gq] = make_float4(h[0], h[1], h[2], h[3]);
-      lp[gq] = make_float4(l[0], l[1], l[2], l[3]);
+      if (lo_out) lp[gq] = make_float4(l[0], l[1], l[2], l[3]);
     }
   }
 }
@@ -658,9 +842,9 @@ __global__ void __launch_bounds__(256) colsplit_kernel(const float* __restrict__
 #pragma unroll 4
   for (int r = slice; r < R; r += 8) {
     const float v = exp_sfu(__ldg(sp + (int64_t)r * C) - sh);
-    const float h = tf32_round(v);
+    const float h = lo_out ? tf32_round(v) : v;
     hp[(int64_t)r * pitch] = h;
-    lp[(int64_t)r * pitch] = v - h;
+    if (lo_out) lp[(int64_t)r * pitch] = v - h;
   }
 }
 
@@ -701,9 +885,9 @@ __global__ void __launch_bounds__(WARPS * 32) colsplit_reg_kernel(const float* _
     const int r = slice + WARPS * i;
     if (r < R) {
       const float e = exp_sfu(v[i] - sh);
-      const float h = tf32_round(e);
+      const float h = lo_out ? tf32_round(e) : e;
       hp[(int64_t)r * pitch] = h;
-      lp[(int64_t)r * pitch] = e - h;
+      if (lo_out) lp[(int64_t)r * pitch] = e - h;
     }
   }
 }
@@ -735,6 +919,11 @@ bool make_map_sw128(CUtensorMap* map, const float* base, uint64_t batch, uint64_
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// the products that take the CTA-pair kernel (long reductions over large results)
+bool pair_wanted(int64_t R, int64_t I, int64_t J) {
+  return I > TM && J > TN && R * (I < J ? I : J) >= 512 * 1024;
+}
+
 // One operand of a product: hi/lo arrays of shape (batch, rows, cols) with the given pitch.
 struct TcOperand {
   const float* hi;
@@ -746,6 +935,28 @@ struct TcOperand {
 template <int EPI, bool A_MN, bool B_MN>
 int launch_tc(const TcOperand& A, const TcOperand& Bo, const TcEpi& ep, int64_t B, int64_t R, int64_t I, int64_t J,
               cudaStream_t st, int slot) {
+  if (!A.lo || !Bo.lo) {  // single unsplit copies: split in shared memory (never the pair kernel, see unsplit_mode)
+    if (A.lo || Bo.lo) return GBMM_ERR_INVALID_ARG;
+    CUtensorMap ua, ub;
+    if (!make_map_sw128<A_MN>(&ua, A.hi, B, A.rows, A.cols, A.pitch) ||
+        !make_map_sw128<B_MN>(&ub, Bo.hi, B, Bo.rows, Bo.cols, Bo.pitch))
+      return GBMM_ERR_LAUNCH;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return GBMM_ERR_DEVICE;
+    const size_t smem = sizeof(TcSmem) + 1024;
+    const int64_t ti = ceil_div(I, TM), tj = ceil_div(J, TN), tiles = B * ti * tj;
+    const unsigned blocks = (unsigned)(tiles < sms ? tiles : sms);
+    if (cudaFuncSetAttribute(tc_gemm_sp_kernel<EPI, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return GBMM_ERR_LAUNCH;
+    const bool timed = profile_begin(slot, st);
+    tc_gemm_sp_kernel<EPI, A_MN, B_MN><<<blocks, DSP_NT, smem, st>>>(ua, ub, ep, (int)R, (int)I, (int)J, (int)ti,
+                                                                    (int)tj, tiles);
+    if (timed) profile_end(slot, st);
+    return launch_status();
+  }
   CUtensorMap m0, m1, m2, m3;
   if (!make_map_sw128<A_MN>(&m0, A.hi, B, A.rows, A.cols, A.pitch) ||
       !make_map_sw128<A_MN>(&m1, A.lo, B, A.rows, A.cols, A.pitch) ||
@@ -765,7 +976,7 @@ int launch_tc(const TcOperand& A, const TcOperand& Bo, const TcEpi& ep, int64_t 
     const char* e = getenv("GENBMM_B200_TC_PAIR");
     return !(e && e[0] == '0');
   }();
-  if (pair_ok && I > TM && J > TN && sms >= 2 && R * (I < J ? I : J) >= 512 * 1024) {
+  if (pair_ok && sms >= 2 && pair_wanted(R, I, J)) {
     const int64_t ti = ceil_div(I, 2 * TM), tj = ceil_div(J, PN), tiles = B * ti * tj;
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
     if (cudaFuncSetAttribute(tc_pair_gemm_kernel<EPI, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -798,17 +1009,30 @@ float* carve(float*& cursor, int64_t floats) {
 // The exponentiated, split operands EA:(B,M,pad32(K)) and EB:(B,K,pad32(N)); the forward writes them
 // behind the 64-float header of its workspace, the backward reads them from there or rebuilds them.
 struct Factors {
-  float *ea_hi, *ea_lo, *eb_hi, *eb_lo;
+  float *ea_hi, *ea_lo, *eb_hi, *eb_lo;   // unsplit mode: ea_hi / eb_hi hold the one copy, the lo pointers are null
 };
+// GENBMM_B200_TC_SPLIT=1: one unsplit copy per operand and tc_gemm_sp_kernel for every problem none of whose three
+// products would take the CTA-pair kernel (one rule for the forward and both gradients, so that they can share
+// the copies).  Half the workspace and half the operand bytes — and not the default: the chain driver's
+// 16 x 511 x 256 x 256 step takes 11.8 ms this way against 10.6 ms with hi + lo copies.  The 128 x 128 tile is
+// already at the shared-memory bandwidth (96 KB of operand reads per 32-step stage for 768 clocks of MMAs); the
+// in-place split adds another 96 KB per stage, which costs more than the HBM bytes it saves.
+bool unsplit_mode(int64_t M, int64_t K, int64_t N) {
+  const char* e = getenv("GENBMM_B200_TC_SPLIT");   // read per call: a forward and its backward must agree, so
+  if (!e || e[0] != '1') return false;              // change it only between problems
+  return !(pair_wanted(K, M, N) || pair_wanted(N, M, K) || pair_wanted(M, K, N));
+}
 int64_t factor_floats(int64_t B, int64_t M, int64_t K, int64_t N) {
-  return 2 * pad64(B * M * pad32(K)) + 2 * pad64(B * K * pad32(N));
+  const int copies = unsplit_mode(M, K, N) ? 1 : 2;
+  return copies * (pad64(B * M * pad32(K)) + pad64(B * K * pad32(N)));
 }
 Factors carve_factors(float*& cur, int64_t B, int64_t M, int64_t K, int64_t N) {
+  const bool one = unsplit_mode(M, K, N);
   Factors f;
   f.ea_hi = carve(cur, B * M * pad32(K));
-  f.ea_lo = carve(cur, B * M * pad32(K));
+  f.ea_lo = one ? nullptr : carve(cur, B * M * pad32(K));
   f.eb_hi = carve(cur, B * K * pad32(N));
-  f.eb_lo = carve(cur, B * K * pad32(N));
+  f.eb_lo = one ? nullptr : carve(cur, B * K * pad32(N));
   return f;
 }
 // forward: maxima and split operands together (one read of a and of b from HBM each)
@@ -855,7 +1079,7 @@ using namespace gbmm;
 extern "C" int64_t gbmm_logbmm_tc_workspace_bytes(int backward, int64_t B, int64_t M, int64_t K, int64_t N) {
   if (B < 0 || M < 0 || K < 0 || N < 0) return -1;
   int64_t floats = 64 + factor_floats(B, M, K, N);
-  if (backward) floats += 2 * pad64(B * M * pad32(N));
+  if (backward) floats += (unsplit_mode(M, K, N) ? 1 : 2) * pad64(B * M * pad32(N));
   return floats * (int64_t)sizeof(float);
 }
 
@@ -906,7 +1130,7 @@ extern "C" int gbmm_logbmm_tc_backward_f32(const float* a, const float* b, const
   int* error = reinterpret_cast<int*>(carve(cur, 64));
   Factors f = carve_factors(cur, B, M, K, N);
   float* gp_hi = carve(cur, B * M * pad32(N));  // G' : (B, M, pad32(N))
-  float* gp_lo = carve(cur, B * M * pad32(N));
+  float* gp_lo = unsplit_mode(M, K, N) ? nullptr : carve(cur, B * M * pad32(N));
   if (cudaMemsetAsync(error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
   int rc = GBMM_OK;
   if (factors) {  // the forward's workspace: same header, same carving

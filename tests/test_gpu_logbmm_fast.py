@@ -32,9 +32,15 @@ def fast_fwd_bwd(nat, a, b, g, tc=False):
     return out, ga, gb, flags
 
 
-@pytest.mark.parametrize("tc", [False, True], ids=["fp32", "tcgen05"])
+@pytest.mark.parametrize("path", ["fp32", "tcgen05", "tcgen05-unsplit"])
 @pytest.mark.parametrize("shape", SHAPES)
-def test_fast_path_matches_oracle(nat, shape, tc):
+def test_fast_path_matches_oracle(nat, shape, path, monkeypatch):
+    """The FP32-pipe products and the tensor-core products in both operand forms: a tf32 hi and a lo copy per
+    operand (GENBMM_B200_TC_SPLIT=0), and one unsplit copy split in shared memory by the product kernel
+    (GENBMM_B200_TC_SPLIT=1; half the workspace, selectable)."""
+    tc = path != "fp32"
+    if path == "tcgen05-unsplit":
+        monkeypatch.setenv("GENBMM_B200_TC_SPLIT", "1")
     B, M, K, N = shape
     gen = torch.Generator().manual_seed(sum(shape))
     a, b = torch.randn(B, M, K, generator=gen), torch.randn(B, K, N, generator=gen)
