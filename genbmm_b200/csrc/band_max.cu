@@ -317,15 +317,19 @@ __global__ void __launch_bounds__(NT, 1) band_max_kernel(MaxArgs g) {
 // reads.  At most 107 KB of tiles at 129 diagonals: two CTAs per SM, so one CTA's copies land while the other
 // multiplies.  Measured at 32 x 8192 x 129 diagonals: 1.33 ms against 1.78 ms for the lockstep kernel.  With
 // 8 x 4 results per thread (4 warps per CTA, 8 per SM) the same scheme took 1.76 ms: too few warps to cover the
-// shared-memory and pipe latencies; with 4 x 4 the CTA has 8 warps.
+// shared-memory and pipe latencies; with 4 x 4 the CTA has 8 warps, and with 4 x 2 on 64 x 32 blocks three CTAs
+// fit an SM (24 warps): 1.23 ms.
 //
 // Shared-memory layout of a 16-step tile: [quad of steps][row][4 steps], one 128-bit load per row and quad; a
 // thread's rows are ty + 4 i and its columns tx + 8 j, so the lanes of a warp read consecutive 16-byte cells
 // (no bank conflicts), and the two halves of a loaded quad are the (k, k+1) pairs of the packed add.
-constexpr int WB = 64;
-constexpr int WT = 4 * WB * 4 + 4;   // floats per operand tile; + 4: the search reads the same cell of different tiles
-constexpr int kMaxTilesW = 26;       // 26 * 2 * WT * 4 bytes = 214 KB
-__host__ __device__ constexpr size_t w_smem_bytes(int tiles) { return (size_t)tiles * 2 * WT * sizeof(float); }
+constexpr int WB = 64;               // rows of a block
+constexpr int WT = 4 * WB * 4 + 4;   // floats per tile of a; + 4: the search reads the same cell of different tiles
+constexpr int kMaxTilesW = 26;       // 26 tiles of a and b at 64 columns = 214 KB
+__host__ __device__ constexpr int w_tile_y(int wc) { return 4 * wc * 4 + 4; }  // floats per tile of b, wc columns
+__host__ __device__ constexpr size_t w_smem_bytes(int tiles, int wc) {
+  return (size_t)tiles * (WT + w_tile_y(wc)) * sizeof(float);
+}
 
 __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -336,10 +340,13 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// IR rows per thread (4 columns): 8 -> 4 warps of 32 x 32 sub-blocks, 4 -> 8 warps of 16 x 32.
-template <int IR, int UQ>
-__global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
-  constexpr int WNT = 1024 / IR, WROWS = 4 * IR;
+// IR x JC results per thread: rows ty + 4 i, columns tx + 8 j; a warp's sub-block is 4 IR rows x 8 JC columns, a
+// block 64 rows x 16 JC columns (two warps across).  8 x 4: 4 warps of 32 x 32; 4 x 4: 8 warps of 16 x 32;
+// 4 x 2: 64 x 32 blocks, 8 warps of 16 x 16 (less shared memory and fewer registers: three CTAs per SM).
+template <int IR, int JC, int UQ>
+__global__ void __launch_bounds__(1024 / IR, JC == 2 ? 3 : 2) band_max_w_kernel(MaxArgs g) {
+  constexpr int WNT = 1024 / IR, WROWS = 4 * IR, WCOLS = 8 * JC, WC = 2 * WCOLS, WTY = w_tile_y(WC);
+  static_assert(WNT == 256 || JC == 4, "the staging below gives every thread at most one chunk of b per tile");
   extern __shared__ __align__(16) float smem_dyn[];
   __shared__ __align__(8) uint64_t landed[kMaxTilesW];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -349,13 +356,13 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
   const int64_t bt = id / ((int64_t)g.ncb * g.nrb);
   const int r0 = rbk * WB;
   const int lo = r0 - g.r_lu;
-  const int cfirst = lo >= 0 ? lo / WB : -((-lo + WB - 1) / WB);
-  const int c0 = (cfirst + cbi) * WB;
+  const int cfirst = lo >= 0 ? lo / WC : -((-lo + WC - 1) / WC);
+  const int c0 = (cfirst + cbi) * WC;
   const int r_ld = g.Wo - 1 - g.r_lu;
   if (c0 > r0 + WB - 1 + r_ld) return;  // beyond the band: owns no cell
   const int s_lo = max(max(r0 - g.a_lu, c0 - g.b_lu), 0);
-  int s_hi = min(min(r0 + WB - 1 + g.a_ld, c0 + WB - 1 + g.b_ld), g.n - 1);
-  if (c0 >= g.n || c0 + WB - 1 < 0) s_hi = s_lo - 1;  // outside the matrix: only zeros to write
+  int s_hi = min(min(r0 + WB - 1 + g.a_ld, c0 + WC - 1 + g.b_ld), g.n - 1);
+  if (c0 >= g.n || c0 + WC - 1 < 0) s_hi = s_lo - 1;  // outside the matrix: only zeros to write
   const int s0 = s_lo & ~(BK - 1);
   const int nt = s_hi >= s_lo ? (s_hi - s0) / BK + 1 : 0;  // <= the launch's tile count by the eligibility rule
   float* sx = smem_dyn;
@@ -367,38 +374,41 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
   }
   __syncthreads();
 
-  // Requests, in tile order.  Chunk f of a tile: row f / 4, quad f % 4 (four threads cover the 64 contiguous
-  // bytes a row contributes).  Rows and columns outside the matrix read 16 bytes of -inf padding instead.
+  // Requests, in tile order.  A tile of a is 256 chunks of 16 bytes (64 rows x 4 quads), a tile of b 4 WC; 8 lanes
+  // take the same quad of 8 consecutive rows: 128 contiguous bytes of shared memory per quarter warp, 64
+  // contiguous bytes of a row per four quads.  Rows and columns outside the matrix read 16 bytes of -inf padding.
   {
     const float* xbase = g.xs + bt * g.x_bstride;
     const float* ybase = g.ys + bt * g.y_bstride;
-    constexpr int NQ = 256 / WNT;  // 256 chunks of 16 bytes per tile and operand
+    constexpr int NQ = 256 / WNT;
     const float* xsrc[NQ];
     const float* ysrc[NQ];
-    int dofs[NQ];
+    int xofs[NQ], yofs[NQ];
+    bool yown[NQ];
 #pragma unroll
     for (int q = 0; q < NQ; ++q) {
-      // 8 lanes take the same quad of 8 consecutive rows: 128 contiguous bytes of shared memory per quarter warp
       const int f = tid + q * WNT, row = (f >> 5) * 8 + (f & 7), quad = (f >> 3) & 3;
       const int i = r0 + row, c = c0 + row;
-      dofs[q] = (quad * WB + row) * 4;
+      xofs[q] = (quad * WB + row) * 4;
+      yofs[q] = (quad * WC + row) * 4;
+      yown[q] = row < WC;
       xsrc[q] = i < g.n ? xbase + g.x_kofs + (int64_t)i * g.x_rstride + s0 + 4 * quad : nullptr;
       ysrc[q] = (c >= 0 && c < g.n) ? ybase + g.y_kofs + (int64_t)c * g.y_rstride + s0 + 4 * quad : nullptr;
     }
     for (int t = 0; t < nt; ++t) {
 #pragma unroll
       for (int q = 0; q < NQ; ++q) {
-        cp_async16(sx + (size_t)t * WT + dofs[q], xsrc[q] ? xsrc[q] + t * BK : xbase + g.x_ninf);
-        cp_async16(sy + (size_t)t * WT + dofs[q], ysrc[q] ? ysrc[q] + t * BK : ybase + g.y_ninf);
+        cp_async16(sx + (size_t)t * WT + xofs[q], xsrc[q] ? xsrc[q] + t * BK : xbase + g.x_ninf);
+        if (yown[q]) cp_async16(sy + (size_t)t * WTY + yofs[q], ysrc[q] ? ysrc[q] + t * BK : ybase + g.y_ninf);
       }
       cp_async_arrive(&landed[t]);
     }
   }
 
   // this warp's sub-block and the tiles that meet both of its bands
-  const int rl0 = (warp >> 1) * WROWS, cl0 = (warp & 1) * 32;
+  const int rl0 = (warp >> 1) * WROWS, cl0 = (warp & 1) * WCOLS;
   const int w_lo = max(max(r0 + rl0 - g.a_lu, c0 + cl0 - g.b_lu), s_lo);
-  const int w_hi = min(min(r0 + rl0 + WROWS - 1 + g.a_ld, c0 + cl0 + 31 + g.b_ld), s_hi);
+  const int w_hi = min(min(r0 + rl0 + WROWS - 1 + g.a_ld, c0 + cl0 + WCOLS - 1 + g.b_ld), s_hi);
   const int t_lo = w_hi >= w_lo ? (w_lo - s0) / BK : 0;
   const int t_hi = w_hi >= w_lo ? (w_hi - s0) / BK : -1;
 
@@ -407,35 +417,35 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
   // aside for the "did this tile raise it" test instead of alternating two register sets) and a rolled search
   // loop (with 8 x 4 results per thread, everything unrolled and two alternating sets, the schedulers sat
   // without instructions five cycles for every one they issued).
-  float Y[IR][4];
+  float Y[IR][JC];
   unsigned cidp[IR];
 #pragma unroll
   for (int i = 0; i < IR; ++i) {
     cidp[i] = 0xffffffffu;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) Y[i][j] = kFloor;
+    for (int j = 0; j < JC; ++j) Y[i][j] = kFloor;
   }
   bool fail = false;
 #pragma unroll 1
   for (int t = t_lo; t <= t_hi; ++t) {
     if (!mbar_wait_bounded(&landed[t], 0)) fail = true;
     const float* xt = sx + (size_t)t * WT + (rl0 + ty) * 4;
-    const float* yt = sy + (size_t)t * WT + (cl0 + tx) * 4;
-    float P[IR][4];
+    const float* yt = sy + (size_t)t * WTY + (cl0 + tx) * 4;
+    float P[IR][JC];
 #pragma unroll
     for (int i = 0; i < IR; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) P[i][j] = Y[i][j];
+      for (int j = 0; j < JC; ++j) P[i][j] = Y[i][j];
     auto quad = [&](int q) {
-      ulonglong2 xq[IR], yq[4];
+      ulonglong2 xq[IR], yq[JC];
 #pragma unroll
       for (int i = 0; i < IR; ++i) xq[i] = *reinterpret_cast<const ulonglong2*>(xt + (q * WB + 4 * i) * 4);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) yq[j] = *reinterpret_cast<const ulonglong2*>(yt + (q * WB + 8 * j) * 4);
+      for (int j = 0; j < JC; ++j) yq[j] = *reinterpret_cast<const ulonglong2*>(yt + (q * WC + 8 * j) * 4);
 #pragma unroll
       for (int i = 0; i < IR; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < JC; ++j) {
           float v0, v1, v2, v3;
           unpack2(add2(xq[i].x, yq[j].x), v0, v1);
           unpack2(add2(xq[i].y, yq[j].y), v2, v3);
@@ -455,8 +465,10 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
     for (int i = 0; i < IR; ++i) {  // strict `>`: an equal maximum in a later tile keeps the index
       if (Y[i][0] > P[i][0]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3214);
       if (Y[i][1] > P[i][1]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3240);
-      if (Y[i][2] > P[i][2]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3410);
-      if (Y[i][3] > P[i][3]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x4210);
+      if (JC > 2) {
+        if (Y[i][JC - 2] > P[i][JC - 2]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x3410);
+        if (Y[i][JC - 1] > P[i][JC - 1]) cidp[i] = __byte_perm(cidp[i], (unsigned)t, 0x4210);
+      }
     }
   }
   if (__any_sync(0xffffffffu, fail) && lane == 0) atomicExch(g.error, 1);
@@ -471,12 +483,12 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
   for (int i = 0; i < IR; ++i) {
     const int ml = rl0 + ty + 4 * i, m = r0 + ml;
     if (m >= g.n) continue;
-    const float* xt[4];
-    const float* yt[4];
-    int p[4], cell[4];
-    bool hunt[4], inside[4];
+    const float* xt[JC];
+    const float* yt[JC];
+    int p[JC], cell[JC];
+    bool hunt[JC], inside[JC];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < JC; ++j) {
       const int cl = cl0 + tx + 8 * j, c = c0 + cl;
       cell[j] = c - m + g.r_lu;
       inside[j] = c >= 0 && c < g.n;
@@ -484,16 +496,19 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
       hunt[j] = cell[j] >= 0 && cell[j] < g.Wo && inside[j] && c8 != 0xffu;
       const unsigned tile = hunt[j] ? c8 : 0u;  // a result with nothing to find reads tile 0 and ignores it
       xt[j] = sx + (size_t)tile * WT + ml * 4;
-      yt[j] = sy + (size_t)tile * WT + cl * 4;
+      yt[j] = sy + (size_t)tile * WTY + cl * 4;
       p[j] = -1;
     }
-    if (hunt[0] || hunt[1] || hunt[2] || hunt[3]) {
+    bool any = false;
+#pragma unroll
+    for (int j = 0; j < JC; ++j) any |= hunt[j];
+    if (any) {
 #pragma unroll 1
       for (int q = BK / 4 - 1; q >= 0; --q) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < JC; ++j) {
           const ulonglong2 xv = *reinterpret_cast<const ulonglong2*>(xt[j] + q * WB * 4);
-          const ulonglong2 yv = *reinterpret_cast<const ulonglong2*>(yt[j] + q * WB * 4);
+          const ulonglong2 yv = *reinterpret_cast<const ulonglong2*>(yt[j] + q * WC * 4);
           float v0, v1, v2, v3;
           unpack2(add2(xv.x, yv.x), v0, v1);
           unpack2(add2(xv.y, yv.y), v2, v3);
@@ -505,7 +520,7 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
       }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < JC; ++j) {
       if (cell[j] < 0 || cell[j] >= g.Wo) continue;
       float val = Y[i][j];
       int pj = hunt[j] ? p[j] : -1;
@@ -513,7 +528,7 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
         // the stored value is the matching term itself: only for a zero can it differ from the maximum (in
         // sign), so that is the one case that reads the term again
         if (val == 0.f)
-          val = __fadd_rn(xt[j][(pj >> 2) * WB * 4 + (pj & 3)], yt[j][(pj >> 2) * WB * 4 + (pj & 3)]);
+          val = __fadd_rn(xt[j][(pj >> 2) * WB * 4 + (pj & 3)], yt[j][(pj >> 2) * WC * 4 + (pj & 3)]);
         pj += s0 + (int)((cidp[i] >> (8 * j)) & 0xffu) * BK;
       }
       const int64_t e = (int64_t)m * g.Wo + cell[j];
@@ -523,9 +538,9 @@ __global__ void __launch_bounds__(1024 / IR, 2) band_max_w_kernel(MaxArgs g) {
   }
 }
 
-// tiles of 16 steps in the longest reduction range of a 64 x 64 block
-int w_tiles(const BandDims& d) {
-  const int64_t range = std::min<int64_t>(WB - 1 + d.Wa(), WB - 1 + d.Wb()) + (BK - 1);
+// tiles of 16 steps in the longest reduction range of a 64 x wc block
+int w_tiles(const BandDims& d, int wc = 64) {
+  const int64_t range = std::min<int64_t>(WB - 1 + d.Wa(), wc - 1 + d.Wb()) + (BK - 1);
   return (int)ceil_div(range, BK);
 }
 
@@ -589,20 +604,28 @@ int band_max_forward(const float* a, const float* b, float* out, int* idx, const
     g.x_ninf = (sa.off + d.Wa() + 3) & ~3;  // the first whole 16 bytes of a row's padding
     g.y_ninf = (sb.off + d.Wb() + 3) & ~3;
     g.error = reinterpret_cast<int*>(ys + max_skew_floats(sb, B));
+    // 64 x 32 blocks (4 x 2 results per thread, 79 registers, 68 KB of tiles at 129 diagonals: three CTAs per SM)
+    // unless GENBMM_B200_BAND_MAX_COLS=64 asks for 64 x 64 blocks (4 x 4 per thread, two CTAs per SM):
+    // 1.23 against 1.31 ms at 32 x 8192 x 129 diagonals
+    const char* shape = getenv("GENBMM_B200_BAND_MAX_COLS");
+    const int wc = (shape && atoi(shape) == 64) ? 64 : 32;
     g.nrb = (int)ceil_div(d.n, WB);
-    g.ncb = (g.Wo + 2 * (WB - 1)) / WB + 1;
+    g.ncb = (g.Wo + (WB - 1) + (wc - 1)) / wc + 1;
     const int64_t wblocks = B * g.nrb * g.ncb;
     if (wblocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
-    const size_t wsmem = w_smem_bytes(w_tiles(d));
-    auto kern = band_max_w_kernel<4, 4>;
-    if (cudaMemsetAsync(g.error, 0, sizeof(int), st) != cudaSuccess ||
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)w_smem_bytes(kMaxTilesW)) !=
-            cudaSuccess ||
-        // two CTAs per SM need the largest shared-memory carveout
-        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=
-            cudaSuccess)
-      return GBMM_ERR_LAUNCH;
-    kern<<<(unsigned)wblocks, 256, wsmem, st>>>(g);
+    const size_t wsmem = w_smem_bytes(w_tiles(d, wc), wc);
+    if (cudaMemsetAsync(g.error, 0, sizeof(int), st) != cudaSuccess) return GBMM_ERR_LAUNCH;
+    auto go = [&](auto kern) {
+      // several CTAs per SM need the largest shared-memory carveout
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)w_smem_bytes(kMaxTilesW, 64)) != cudaSuccess ||
+          cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+        return false;
+      kern<<<(unsigned)wblocks, 256, wsmem, st>>>(g);
+      return true;
+    };
+    if (!(wc == 32 ? go(band_max_w_kernel<4, 2, 4>) : go(band_max_w_kernel<4, 4, 4>))) return GBMM_ERR_LAUNCH;
     if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
     return launch_poison_on_error(g.error, out, B * d.n * d.Wo(), nullptr, 0, st);
   }

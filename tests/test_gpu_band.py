@@ -119,13 +119,16 @@ def test_log_semiring_other_tensor_feeds(gb, case, monkeypatch, feed):
 @pytest.mark.parametrize("case", [c for c in CASES if c[1] >= 128 and min(c[2] + c[3], c[4] + c[5]) >= 31]
                          + [(2, 640, 64, 64, 64, 64), (1, 333, 100, 20, 10, 90), (2, 256, 31, 0, 0, 31),
                             (1, 700, 150, 100, 120, 140)])
-@pytest.mark.parametrize("blocks", ["warp-ranges", "lockstep"])
+@pytest.mark.parametrize("blocks", ["warp-ranges", "warp-ranges-64", "lockstep"])
 def test_max_semiring_both_block_kernels(gb, case, monkeypatch, blocks):
-    """multiply_max on the two kernels that read skewed copies: 64 x 64 blocks whose warps walk their own
-    reduction ranges (default) and 128 x 64 blocks in lockstep (GENBMM_B200_BAND_MAX=block).  Values and
-    indices bit for bit, with ties and with rows that nothing lifts above -1e9."""
+    """multiply_max on the kernels that read skewed copies: blocks whose warps walk their own reduction ranges
+    (64 x 32, the default, and 64 x 64 with GENBMM_B200_BAND_MAX_COLS=64) and 128 x 64 blocks in lockstep
+    (GENBMM_B200_BAND_MAX=block).  Values and indices bit for bit, with ties and with rows that nothing lifts
+    above -1e9."""
     if blocks == "lockstep":
         monkeypatch.setenv("GENBMM_B200_BAND_MAX", "block")
+    if blocks == "warp-ranges-64":
+        monkeypatch.setenv("GENBMM_B200_BAND_MAX_COLS", "64")
     B, n, alu, ald, blu, bld = case
     gen = torch.Generator().manual_seed(sum(case) + 5)
     a = (torch.randn(B, n, alu + ald + 1, generator=gen) * 2).round() / 2
