@@ -671,7 +671,8 @@ def run_ours(args, rank, world, local):
     # the public operator (genbmm_b200.logbmm + torch.autograd.grad).
     ga_h = torch.empty(B, SIZE, SIZE).pin_memory()
     gb_h = torch.empty(B, SIZE, SIZE).pin_memory()
-    pipe = HostPipeline(B, SIZE, SIZE, SIZE, chunks=args.e2e_chunks, device=dev, graph=bool(args.e2e_graph))
+    pipe = HostPipeline(B, SIZE, SIZE, SIZE, chunks=args.e2e_chunks if args.e2e_chunks == "tapered" else int(args.e2e_chunks),
+                        device=dev, graph=bool(args.e2e_graph))
 
     def step_e2e():
         return pipe.step(a_h, b_h, ga_h, gb_h)
@@ -856,7 +857,8 @@ def main():
     ap.add_argument("--batch", type=int, default=32, help="1024^3 problems per GPU per step")
     ap.add_argument("--inner-repeats", type=int, default=0,
                     help="run every counted step this many times (0: as many as make the timed region 2 s)")
-    ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the host pipeline (end-to-end leg)")
+    ap.add_argument("--e2e-chunks", default="8",
+                    help="batch chunks of the host pipeline (end-to-end leg): a count, or 'tapered'")
     ap.add_argument("--e2e-graph", type=int, default=0, help="1: the host pipeline replays one CUDA graph per chunk")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-cuda", action="store_true")

@@ -513,14 +513,15 @@ __global__ void __launch_bounds__(1024) band_route_b_kernel(const int* __restric
     for (int k = lane; k < Wb; k += 32) grad_b[(bt * n + o) * Wb + k] = hist[k];
 }
 
+// (One thread per row for grad_a as well was measured twice and lost both times against the warp-per-row kernel's
+// 0.37 ms at 32 x 8192 x 129 diagonals: 0.75 ms with the cells of 32 rows turned through shared memory first, 0.64
+// ms with every thread walking its own contiguous row by 128-bit loads, whose 32 lanes touch 32 different lines.)
 // grad_b, one THREAD per row o of b (RB_T rows per CTA), each with its own Wb-bucket histogram in shared memory
 // (odd pitch: the threads of a warp hit 32 different banks for the same bucket).  A warp walks the rows i that
 // reach any of its 32 rows o in ascending order; at a given i its lanes read the cells (i, jo = o - i + r_lu),
 // which are consecutive in memory, and every lane adds its cell's cotangent to the bucket its index names.  A
 // thread therefore accumulates its row's buckets in ascending i — the order of a sequential walk, with no
 // ordering work between lanes (the kernel above spends most of its time ranking lanes that share a bucket).
-// (The same scheme for grad_a needs the cells of 32 rows turned through shared memory first, a row's cells being
-// contiguous: measured at 0.75 ms against the warp-per-row kernel's 0.37 ms, and not kept.)
 constexpr int RB_T = 128;
 __global__ void __launch_bounds__(RB_T) band_route_b_rows_kernel(const int* __restrict__ idx,
                                                                  const float* __restrict__ g,
@@ -756,10 +757,8 @@ static int route_max_backward(const float* grad_out, const int* idx, float* grad
     const int64_t tiles = ceil_div(d.n, 32), blocks = B * tiles;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
     const size_t smem_rows = sizeof(float) * RB_T * (d.Wb() | 1);
-    static const bool by_rows = [] {
-      const char* e = getenv("GENBMM_B200_BAND_ROUTE_B");
-      return !(e && e[0] == 'w');   // "warp": the warp-per-row kernel
-    }();
+    const char* eb = getenv("GENBMM_B200_BAND_ROUTE_B");   // "w": the warp-per-row kernel
+    const bool by_rows = !(eb && eb[0] == 'w');
     if (by_rows && smem_rows <= (size_t)100 * 1024 && d.n < (1LL << 30)) {   // at least two CTAs per SM; 32-bit walk
       const int64_t rows = B * d.n, rblocks = ceil_div(rows, RB_T);
       if (rblocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;

@@ -43,6 +43,30 @@ def bind_host_near(device):
         return None
 
 
+def chunk_bounds(B, chunks):
+    """[lo, hi) batch ranges of the pipeline's chunks.  An integer gives that many equal chunks.  "tapered" gives
+    small chunks at both ends and larger ones between (1, 1, 2, then about B / 8 each, then 2, 1, 1): the
+    device-to-host copies cannot start before the first chunk has arrived and been multiplied, and the last
+    chunk's results leave after everything else is done, so the first and the last chunk are pure latency while
+    the number of chunks is what the host pays for."""
+    if chunks == "tapered":
+        if B < 12:
+            sizes = [1] * B
+        else:
+            mid = max(2, B // 8)
+            head = [1, 1, 2]
+            rest = B - 2 * sum(head)
+            sizes = head + [mid] * (rest // mid) + ([rest % mid] if rest % mid else []) + head[::-1]
+        out, lo = [], 0
+        for n in sizes:
+            out.append((lo, lo + n))
+            lo += n
+        assert lo == B
+        return out
+    chunks = max(1, min(int(chunks), B))
+    return [(i * B // chunks, (i + 1) * B // chunks) for i in range(chunks)]
+
+
 class HostPipeline:
     def __init__(self, B, M, K, N, chunks=4, device=None, tensor_cores=True, graph=False):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -59,8 +83,7 @@ class HostPipeline:
         self.use_graph = graph
         self._graphs = None
         self._warm = False
-        chunks = max(1, min(chunks, B))
-        self.bounds = [(i * B // chunks, (i + 1) * B // chunks) for i in range(chunks)]
+        self.bounds = chunk_bounds(B, chunks)
         with torch.cuda.device(self.device):
             self.a = torch.empty((B, M, K), device=self.device)
             self.b = torch.empty((B, K, N), device=self.device)

@@ -143,6 +143,28 @@ def test_max_semiring_both_block_kernels(gb, case, monkeypatch, blocks):
     assert_equal_bits(idx_gpu, idx, "max index")
 
 
+@pytest.mark.parametrize("case", [(2, 300, 20, 15, 18, 17), (2, 517, 64, 64, 64, 64), (1, 257, 0, 40, 35, 0),
+                                  (3, 33, 0, 0, 3, 1), (2, 130, 100, 90, 70, 120), (1, 1001, 33, 30, 31, 40)])
+@pytest.mark.parametrize("route", ["thread-per-row", "warp-per-row"])
+def test_max_backward_both_routings(gb, case, monkeypatch, route):
+    """The index-routed gradients of multiply_max with grad_b by the thread-per-row kernel (default) and by the
+    warp-per-row kernel (GENBMM_B200_BAND_ROUTE_B=w): bit for bit the oracle's sums, on indices with ties, -1
+    entries and odd row lengths."""
+    if route == "warp-per-row":
+        monkeypatch.setenv("GENBMM_B200_BAND_ROUTE_B", "w")
+    B, n, alu, ald, blu, bld = case
+    gen = torch.Generator().manual_seed(sum(case) + 11)
+    a = (torch.randn(B, n, alu + ald + 1, generator=gen) * 2).round() / 2
+    b = (torch.randn(B, n, blu + bld + 1, generator=gen) * 2).round() / 2
+    a[:, n // 3] = -2e9
+    g = torch.randn(B, n, alu + ald + blu + bld + 1, generator=gen)
+    r, ga, gb_ = run(gb, "multiply_max", a, alu, ald, b, blu, bld, g)
+    out, idx, _, dA, dB = oracle.band_fwd_bwd(1, a, alu, ald, b, blu, bld, g)
+    assert_equal_bits(r.data, out, "max value")
+    assert_equal_bits(ga, dA, "max grad_a")
+    assert_equal_bits(gb_, dB, "max grad_b")
+
+
 @pytest.mark.parametrize("ci", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("method,name", [("multiply", "mul"), ("multiply_log", "log"), ("multiply_max", "max")])
 def test_band_products_match_reference_fixture(gb, golden, ci, method, name):

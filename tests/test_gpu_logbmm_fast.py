@@ -195,6 +195,13 @@ def test_host_pipeline_matches_the_plain_call():
     assert abs(loss - float(c.detach().sum().double())) <= 1e-5 * abs(loss)
     assert torch.allclose(ga_h.cuda(), want_a, rtol=1e-5, atol=2e-6)
     assert torch.allclose(gb_h.cuda(), want_b, rtol=1e-5, atol=2e-6)
+    # chunks of unequal sizes (small at both ends) give the same gradients
+    tapered = HostPipeline(B, M, K, N, chunks="tapered")
+    assert len(tapered.bounds) == B
+    ga_t, gb_t = torch.empty(B, M, K).pin_memory(), torch.empty(B, K, N).pin_memory()
+    loss_t = tapered.step(a_h, b_h, ga_t, gb_t)
+    assert abs(loss_t - loss) <= 1e-9 * abs(loss)
+    assert torch.equal(ga_t, ga_p) and torch.equal(gb_t, gb_p)
 
 
 _FIXUP_CHILD = r"""

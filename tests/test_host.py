@@ -148,3 +148,15 @@ def test_band_forward_token_is_valid_only_until_the_workspace_is_written_again()
     ws.generation -= 1
     ws.holds = None                                       # a call that left the copies incomplete
     assert not tok.valid_for(ws, 0)
+
+
+def test_host_pipeline_chunk_bounds():
+    """Equal chunks and the tapered form cover the batch exactly once, in order."""
+    from genbmm_b200.host import chunk_bounds
+    for B in (1, 2, 5, 11, 12, 16, 31, 32, 64, 100):
+        for chunks in (1, 3, 8, 200, "tapered"):
+            bounds = chunk_bounds(B, chunks)
+            assert bounds[0][0] == 0 and bounds[-1][1] == B
+            assert all(lo < hi for lo, hi in bounds)
+            assert all(bounds[i][1] == bounds[i + 1][0] for i in range(len(bounds) - 1))
+    assert [hi - lo for lo, hi in chunk_bounds(32, "tapered")] == [1, 1, 2, 4, 4, 4, 4, 4, 4, 2, 1, 1]
