@@ -63,6 +63,13 @@ def chunk_bounds(B, chunks):
             lo += n
         assert lo == B
         return out
+    if isinstance(chunks, (list, tuple)):   # explicit chunk sizes
+        assert sum(chunks) == B and all(n > 0 for n in chunks)
+        out, lo = [], 0
+        for n in chunks:
+            out.append((lo, lo + n))
+            lo += n
+        return out
     chunks = max(1, min(int(chunks), B))
     return [(i * B // chunks, (i + 1) * B // chunks) for i in range(chunks)]
 
