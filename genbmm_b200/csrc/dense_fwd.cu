@@ -455,18 +455,16 @@ __global__ void __launch_bounds__(NT, PACK ? 2 : 1) dense_max_fwd_kernel(const f
 }
 
 // ------------------------------------------------------------------ max-plus / prod-max, TMA-staged
-// The same reduction with the operand tiles brought in by TMA instead of through registers: per 32-step stage one
-// 128 x 32 box of a and one 64 x 32 box of the transposed copy of b (both k-contiguous, 128-byte rows, 128-byte
-// swizzle) land in a four-stage shared-memory ring; `full` barriers carry the byte counts, `empty` barriers one
-// arrival per warp.  Thread 0 issues the copies: after its warp has finished a stage it waits for the other
-// warps' arrivals on that stage and refills the slot with the tile four stages ahead (the other warps never wait
-// for anything but data).  Reduction steps beyond K read as NaN (the tensor map's out-of-bounds fill), a term the
-// maximum ignores, exactly like the padding of the kernel above.
-// Pairs (k, k+1) are contiguous in a k-major row, so the packed add needs no special layout; a thread's eight rows
-// are ty + 16 i and its four columns tx + 16 j, which gives all of its rows one swizzle phase (row & 7) and all of
-// its columns another: the 16-byte chunk q of a row sits at chunk q ^ phase, one XOR per chunk and operand, and
-// every load of a chunk is an immediate offset from there.  With the staging gone, the ALU pipe carries the
-// 3-input maxima, the index tracking (per 16 steps, as above) and a handful of address instructions per chunk.
+// The same reduction with the operand tiles brought in by TMA instead of through registers.  A 32-step stage of the
+// four-stage shared-memory ring is eight boxes of a (4 steps x 128 rows) and eight of the transposed copy of b
+// (4 steps x 64 rows): a box lands as [row][4 steps], so a stage is [quad of steps][row][4] — one 128-bit load
+// per row and quad, adjacent rows in adjacent 16-byte cells, the two halves of a loaded quad being the (k, k+1)
+// pairs of the packed add: as many shared-memory loads as the pair layout of the kernel above, and none of its
+// staging instructions.  `full` barriers carry the byte counts, `empty` barriers one arrival per warp.  Thread 0
+// issues the copies: after its warp has finished a stage it waits for the other warps' arrivals on that stage
+// and refills the slot with the tile four stages ahead (the other warps never wait for anything but data).
+// Reduction steps beyond K read as NaN (the tensor map's out-of-bounds fill), a term the maximum ignores, exactly
+// like the padding of the kernel above.  A thread's eight rows are ty + 16 i and its four columns tx + 16 j.
 constexpr int XS_STAGES = 4, XS_K = 32;
 struct alignas(1024) MaxTmaSmem {
   float a[XS_STAGES][BM * XS_K];
@@ -500,8 +498,11 @@ __global__ void __launch_bounds__(NT, 2) dense_max_tma_kernel(const __grid_const
   auto issue = [&](int t) {
     const int s = t % XS_STAGES;
     mbar_arrive_expect_tx(&sm.full[s], (BM + BN) * XS_K * sizeof(float));
-    tma_load_3d(sm.a[s], &map_a, &sm.full[s], t * XS_K, tc.m0, tc.bt);
-    tma_load_3d(sm.b[s], &map_bt, &sm.full[s], t * XS_K, tc.n0, tc.bt);
+#pragma unroll
+    for (int q = 0; q < XS_K / 4; ++q) {   // one box per quad of steps: [row][4 steps], 16 bytes per row
+      tma_load_3d(sm.a[s] + q * BM * 4, &map_a, &sm.full[s], t * XS_K + 4 * q, tc.m0, tc.bt);
+      tma_load_3d(sm.b[s] + q * BN * 4, &map_bt, &sm.full[s], t * XS_K + 4 * q, tc.n0, tc.bt);
+    }
   };
   if (tid == 0)
     for (int t = 0; t < XS_STAGES && t < nst; ++t) issue(t);
@@ -517,31 +518,26 @@ __global__ void __launch_bounds__(NT, 2) dense_max_tma_kernel(const __grid_const
       Y[i][j] = kFloor;
     }
   }
-  const int xph = ty & 7, yph = tx & 7;   // swizzle phases of this thread's rows and columns
   bool fail = false;
 
-  // one 16-step sub-tile: chunks q0 .. q0 + 3 of the stage; u = its index among all 16-step tiles
+  // one 16-step sub-tile: quads q0 .. q0 + 3 of the stage; u = its index among all 16-step tiles
   auto sub_tile = [&](const float* xs, const float* ys, int q0, int u, float (&acc)[8][4], const float (&prev)[8][4]) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      const float* xc = xs + (((q0 + c) ^ xph) << 2);
-      const float* yc = ys + (((q0 + c) ^ yph) << 2);
+      ulonglong2 xq[8], yq[4];
 #pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        unsigned long long xp[8], yp[4];
+      for (int i = 0; i < 8; ++i) xq[i] = *reinterpret_cast<const ulonglong2*>(xs + ((q0 + c) * BM + 16 * i) * 4);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) xp[i] = *reinterpret_cast<const unsigned long long*>(xc + i * 16 * XS_K + 2 * p);
+      for (int j = 0; j < 4; ++j) yq[j] = *reinterpret_cast<const ulonglong2*>(ys + ((q0 + c) * BN + 16 * j) * 4);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) yp[j] = *reinterpret_cast<const unsigned long long*>(yc + j * 16 * XS_K + 2 * p);
+      for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float v0, v1;
-            unpack2(MUL ? mul2(xp[i], yp[j]) : add2(xp[i], yp[j]), v0, v1);
-            acc[i][j] = max3((c == 0 && p == 0) ? prev[i][j] : acc[i][j], v0, v1);
-          }
-      }
+        for (int j = 0; j < 4; ++j) {
+          float v0, v1, v2, v3;
+          unpack2(MUL ? mul2(xq[i].x, yq[j].x) : add2(xq[i].x, yq[j].x), v0, v1);
+          unpack2(MUL ? mul2(xq[i].y, yq[j].y) : add2(xq[i].y, yq[j].y), v2, v3);
+          acc[i][j] = max3(max3(c == 0 ? prev[i][j] : acc[i][j], v0, v1), v2, v3);
+        }
     }
     // strict `>`: an equal maximum in a later tile does not move the index
 #pragma unroll
@@ -560,8 +556,8 @@ __global__ void __launch_bounds__(NT, 2) dense_max_tma_kernel(const __grid_const
       fail = true;
       break;
     }
-    const float* xs = sm.a[s] + ty * XS_K;
-    const float* ys = sm.b[s] + tx * XS_K;
+    const float* xs = sm.a[s] + ty * 4;
+    const float* ys = sm.b[s] + tx * 4;
     sub_tile(xs, ys, 0, 2 * t, X, Y);
     sub_tile(xs, ys, 4, 2 * t + 1, Y, X);
     __syncwarp();
@@ -676,18 +672,18 @@ __global__ void __launch_bounds__(NT, 2) dense_max_tma_kernel(const __grid_const
   }
 }
 
-// Tensor map of a (batch, rows, cols) fp32 array with rows `pitch` apart, fetched as (box_rows x 32) boxes with
-// the 128-byte swizzle; elements outside [0, rows) x [0, cols) read as NaN.
+// Tensor map of a (batch, rows, cols) fp32 array with rows `pitch` apart, fetched as boxes of box_rows rows x 4
+// columns (16 bytes per row, no swizzle); elements outside [0, rows) x [0, cols) read as NaN.
 bool make_max_map(CUtensorMap* map, const float* base, uint64_t batch, uint64_t rows, uint64_t cols, uint64_t pitch,
                   uint32_t box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || (pitch & 3)) return false;
   const cuuint64_t dims[3] = {cols, rows, batch};
   const cuuint64_t strides[2] = {pitch * sizeof(float), rows * pitch * sizeof(float)};
-  const cuuint32_t box[3] = {XS_K, box_rows, 1};
+  const cuuint32_t box[3] = {4, box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NAN_REQUEST_ZERO_FMA) == CUDA_SUCCESS;
 }
 
@@ -1044,8 +1040,9 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
       }
       {
         // TMA-staged kernel (GENBMM_B200_MAX_TMA=1): a's rows must be 16-byte multiples and the transposed copy of
-        // b is its B operand.  Same results; measured 3.09 ms against 3.04 ms for the register-staged kernel at
-        // 32 x 1024^3 (the ALU pipe's 3-input maxima bound both), so it is not the default.
+        // b is its B operand.  Same results; measured 3.11 ms against 3.03 ms for the register-staged kernel at
+        // 32 x 1024^3 (3.09 ms in an earlier form with k-major 128-byte-swizzled tiles and 64-bit loads): the packed
+        // adds and 3-input maxima bound both, so it is not the default.
         const char* e = getenv("GENBMM_B200_MAX_TMA");
         CUtensorMap ma, mb;
         if ((e && e[0] == '1') && b_t && pack && K % 4 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
