@@ -198,7 +198,7 @@ bool make_skew_map(CUtensorMap* map, const float* base, int64_t B, int64_t n, co
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-enum { E_SUM = 0, E_LOG = 1 };
+enum { E_SUM = 0, E_LOG = 1, E_GRADLOG = 2 };   // E_GRADLOG: out = sum * exp(src - ra[row]), src laid out like out
 
 struct BandTcArgs {
   int n, lu_out, w_out;      // result band
@@ -207,8 +207,9 @@ struct BandTcArgs {
   int nrb, ncb;              // 128-row blocks, candidate column tiles per row block
   int64_t total;             // batch * nrb * ncb
   float* out;                // (batch, n, w_out)
-  const float* ra;           // E_LOG: row maxima of a
+  const float* ra;           // E_LOG: row maxima of a; E_GRADLOG: row maxima of the operand the gradient is for
   const float* rb;           // E_LOG: row maxima of b
+  const float* src;          // E_GRADLOG: that operand, (batch, n, w_out)
   int* flags;                // E_LOG: (batch, ceil(n / 64))
   int* error;
 };
@@ -235,10 +236,11 @@ __device__ __forceinline__ bool band_tile(const BandTcArgs& g, int64_t tile, int
 }
 
 // One warp's 32 rows x TEC columns of a tile: band cells (col - row + lu_out in [0, w_out)) go to band
-// storage; lanes run along columns, so a tile row is written as one contiguous run.  The epilogue reads
-// nothing large from global memory: while the products stream the padded operands, every load of an SM
-// queues behind its TMA traffic for microseconds (the log gradients' factor exp(a - ra) is therefore
-// applied by a separate pass, band_scale_kernel).
+// storage; lanes run along columns, so a tile row is written as one contiguous run.  The epilogue reads nothing
+// large from global memory: every load it issues queues behind the SM's TMA traffic for microseconds, so the log
+// gradients' factor exp(a - ra) is applied by a separate pass (band_scale_kernel).  E_GRADLOG is the fused form
+// (one load per cell, from the operand's own band storage at the offset the result is written to), selectable
+// and measured slower (see band_fused_scale).
 template <int EPI>
 __device__ __forceinline__ void store_band32(const float (&sum)[32], float* blk, const BandTcArgs& g, int bt, int row0,
                                              int col0, int lane, float rshift, bool& bad) {
@@ -257,16 +259,18 @@ __device__ __forceinline__ void store_band32(const float (&sum)[32], float* blk,
   const int top = c - row0 + g.lu_out;  // cell at rr = 0
   const int rr_lo = max(0, top - (g.w_out - 1)), rr_hi = min(rows, top + 1);
   float* op = ob + (int64_t)row0 * g.w_out + top;
+  const float* sp = EPI == E_GRADLOG ? g.src + (int64_t)bt * g.n * g.w_out + (int64_t)row0 * g.w_out + top : nullptr;
   const int step = g.w_out - 1;
   // (not fully unrolled: 64 copies of this body do not fit the instruction cache)
 #pragma unroll 4
   for (int rr = 0; rr < 32; ++rr) {
-    const float rs = EPI == E_LOG ? __shfl_sync(0xffffffffu, rshift, rr) : 0.f;
+    const float rs = EPI != E_SUM ? __shfl_sync(0xffffffffu, rshift, rr) : 0.f;
     if (rr >= rr_lo && rr < rr_hi) {
       const float v = blk[rr * 33 + lane];
       float o = 0.f;
       if (inside) {
         if (EPI == E_SUM) o = v;
+        if (EPI == E_GRADLOG) o = v * exp_sfu(__ldg(sp + rr * step) - rs);
         if (EPI == E_LOG) {
           const float sh = rs + cshift;
           bad |= !(v >= kTiny) || !(v <= 3.0e38f) || (sh < kFloor);
@@ -283,7 +287,7 @@ __device__ __forceinline__ void store_band(const float (&sum)[TEC], float* blk, 
                                            int col0, int lane, bool& bad) {
   // shift of row row0 + lane, handed round by shuffles
   float rshift = 0.f;
-  if (EPI == E_LOG && row0 + lane < g.n) rshift = __ldg(g.ra + (int64_t)bt * g.n + row0 + lane);
+  if (EPI != E_SUM && row0 + lane < g.n) rshift = __ldg(g.ra + (int64_t)bt * g.n + row0 + lane);
 #pragma unroll
   for (int pass = 0; pass < TEC / 32; ++pass) {
     float part[32];
@@ -736,7 +740,7 @@ __global__ void __launch_bounds__(CV_NT, 1) band_cv_kernel(BandCvArgs p) {
       if (!band_tile(g, tile, bt, r0, c0, s0, nt)) continue;
       const int row0 = r0 + quad * 32;
       float rshift = 0.f;
-      if (EPI == E_LOG && row0 + lane < g.n) rshift = __ldg(g.ra + (int64_t)bt * g.n + row0 + lane);
+      if (EPI != E_SUM && row0 + lane < g.n) rshift = __ldg(g.ra + (int64_t)bt * g.n + row0 + lane);
       bool bad = false;
       if (nt == 0) {
         // the tile owns band cells that no term reaches: zeros outside the matrix; inside it (log semiring) the
@@ -965,7 +969,7 @@ __global__ void __launch_bounds__(SP_NT, 1) band_sp_kernel(const __grid_constant
       if (!band_tile(g, tile, bt, r0, c0, s0, nt)) continue;
       const int row0 = r0 + quad * 32;
       float rshift = 0.f;
-      if (EPI == E_LOG && row0 + lane < g.n) rshift = __ldg(g.ra + (int64_t)bt * g.n + row0 + lane);
+      if (EPI != E_SUM && row0 + lane < g.n) rshift = __ldg(g.ra + (int64_t)bt * g.n + row0 + lane);
       bool bad = false;
       if (nt == 0) {
         // the tile owns band cells that no term reaches: zeros outside the matrix; inside it (log semiring) the
@@ -1339,6 +1343,14 @@ int band_tc_forward(int mode, const float* a, const float* b, float* out, const 
   return launch_poison_on_error(w.error, out, B * d.n * d.Wo(), nullptr, 0, st);
 }
 
+// GENBMM_B200_BAND_SCALE=fused applies the log gradients' factor in band_sp_kernel's epilogue instead of a pass of
+// its own.  Measured at 32 x 8192 x 129 diagonals: backward 2.10 ms against 1.20 ms — a global load in the
+// epilogue still waits behind the SM's TMA traffic, with a quarter of the bytes as much as before.
+static bool band_fused_scale() {
+  const char* e = getenv("GENBMM_B200_BAND_SCALE");
+  return e && e[0] == 'f';
+}
+
 int band_tc_backward(int mode, const float* a, const float* b, const float* g, const float* part, float* grad_a,
                      float* grad_b, const BandDims& d, int64_t B, void* ws, int operands_ready, int** flags_out,
                      cudaStream_t st) {
@@ -1385,10 +1397,16 @@ int band_tc_backward(int mode, const float* a, const float* b, const float* g, c
     args.xl = r_lu; args.xu = r_ld; args.yl = d.b_ld; args.yu = d.b_lu;
     args.out = grad_a;
     args.error = w.error;
-    rc = sp ? launch_band_sp<E_SUM, false, true>(w.G, w.Bm, args, B, st)
-            : launch_band_tc<E_SUM, false, true>(w.G, w.Bm, args, B, st);
+    const bool fused_scale = lg && sp && band_fused_scale();
+    if (fused_scale) {   // log: dXa = EA (.) sum, the factor applied by the product's epilogue
+      args.ra = w.ra;
+      args.src = a;
+    }
+    rc = fused_scale ? launch_band_sp<E_GRADLOG, false, true>(w.G, w.Bm, args, B, st)
+         : sp        ? launch_band_sp<E_SUM, false, true>(w.G, w.Bm, args, B, st)
+                     : launch_band_tc<E_SUM, false, true>(w.G, w.Bm, args, B, st);
     if (rc != GBMM_OK) return rc;
-    if (lg) {  // log: dXa = EA (.) sum
+    if (lg && !fused_scale) {  // log: dXa = EA (.) sum
       band_scale_kernel<<<(unsigned)ceil_div(B * d.n, 8), 256, 0, st>>>(grad_a, a, w.ra, B * d.n, (int)d.n, d.a_lu,
                                                                       d.Wa());
       if (cudaGetLastError() != cudaSuccess) return GBMM_ERR_LAUNCH;
@@ -1403,10 +1421,16 @@ int band_tc_backward(int mode, const float* a, const float* b, const float* g, c
     args.xl = r_ld; args.xu = r_lu; args.yl = d.a_ld; args.yu = d.a_lu;
     args.out = grad_b;
     args.error = w.error;
-    rc = sp ? launch_band_sp<E_SUM, true, true>(w.G, w.A, args, B, st)
-            : launch_band_tc<E_SUM, true, true>(w.G, w.A, args, B, st);
+    const bool fused_scale = lg && sp && band_fused_scale();
+    if (fused_scale) {
+      args.ra = w.rb;
+      args.src = b;
+    }
+    rc = fused_scale ? launch_band_sp<E_GRADLOG, true, true>(w.G, w.A, args, B, st)
+         : sp        ? launch_band_sp<E_SUM, true, true>(w.G, w.A, args, B, st)
+                     : launch_band_tc<E_SUM, true, true>(w.G, w.A, args, B, st);
     if (rc != GBMM_OK) return rc;
-    if (lg) {
+    if (lg && !fused_scale) {
       band_scale_kernel<<<(unsigned)ceil_div(B * d.n, 8), 256, 0, st>>>(grad_b, b, w.rb, B * d.n, (int)d.n, d.b_lu,
                                                                       d.Wb());
       rc = launch_status();

@@ -97,13 +97,17 @@ def test_sum_semiring_both_paths(gb, case, monkeypatch, path):
 
 
 @pytest.mark.parametrize("case", [c for c in CASES if c[1] >= 128 and min(c[2] + c[3], c[4] + c[5]) >= 31])
-@pytest.mark.parametrize("feed", ["hilo", "convert"])
+@pytest.mark.parametrize("feed", ["hilo", "convert", "scale-fused"])
 def test_log_semiring_other_tensor_feeds(gb, case, monkeypatch, feed):
-    """The log product on the two tensor-core feeds that are not the default (hi + lo copies,
-    GENBMM_B200_BAND_SPLIT=0; SIMT-converted tiles, GENBMM_B200_BAND_CV=1); the default feed is what
-    test_band_products_match_oracle runs for these shapes."""
-    monkeypatch.setenv("GENBMM_B200_BAND_CV" if feed == "convert" else "GENBMM_B200_BAND_SPLIT",
-                       "1" if feed == "convert" else "0")
+    """The log product on the tensor-core feeds that are not the default (hi + lo copies,
+    GENBMM_B200_BAND_SPLIT=0; SIMT-converted tiles, GENBMM_B200_BAND_CV=1) and, on the default feed, with the
+    gradients' factor exp(x - max) applied by the product's epilogue instead of a separate pass
+    (GENBMM_B200_BAND_SCALE=fused); the default is what test_band_products_match_oracle runs for these shapes."""
+    if feed == "scale-fused":
+        monkeypatch.setenv("GENBMM_B200_BAND_SCALE", "fused")
+    else:
+        monkeypatch.setenv("GENBMM_B200_BAND_CV" if feed == "convert" else "GENBMM_B200_BAND_SPLIT",
+                           "1" if feed == "convert" else "0")
     B, n, alu, ald, blu, bld = case
     gen = torch.Generator().manual_seed(sum(case))
     a = torch.randn(B, n, alu + ald + 1, generator=gen)
