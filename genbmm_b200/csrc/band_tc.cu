@@ -259,18 +259,30 @@ __device__ __forceinline__ void store_band32(const float (&sum)[32], float* blk,
   const int top = c - row0 + g.lu_out;  // cell at rr = 0
   const int rr_lo = max(0, top - (g.w_out - 1)), rr_hi = min(rows, top + 1);
   float* op = ob + (int64_t)row0 * g.w_out + top;
-  const float* sp = EPI == E_GRADLOG ? g.src + (int64_t)bt * g.n * g.w_out + (int64_t)row0 * g.w_out + top : nullptr;
   const int step = g.w_out - 1;
+  if (EPI == E_GRADLOG) {
+    // the factor exp(src - shift[row]) of this lane's 32 cells, multiplied into the block in shared memory: all
+    // 32 loads are issued before the first is used (one round trip to memory per block instead of eight)
+    const float* sp = g.src + (int64_t)bt * g.n * g.w_out + (int64_t)row0 * g.w_out + top;
+    float sv[32];
+#pragma unroll
+    for (int rr = 0; rr < 32; ++rr)
+      sv[rr] = (inside && rr >= rr_lo && rr < rr_hi) ? __ldg(sp + rr * step) : 0.f;
+#pragma unroll
+    for (int rr = 0; rr < 32; ++rr) {
+      const float rs = __shfl_sync(0xffffffffu, rshift, rr);
+      blk[rr * 33 + lane] *= exp_sfu(sv[rr] - rs);
+    }
+  }
   // (not fully unrolled: 64 copies of this body do not fit the instruction cache)
 #pragma unroll 4
   for (int rr = 0; rr < 32; ++rr) {
-    const float rs = EPI != E_SUM ? __shfl_sync(0xffffffffu, rshift, rr) : 0.f;
+    const float rs = EPI == E_LOG ? __shfl_sync(0xffffffffu, rshift, rr) : 0.f;
     if (rr >= rr_lo && rr < rr_hi) {
       const float v = blk[rr * 33 + lane];
       float o = 0.f;
       if (inside) {
-        if (EPI == E_SUM) o = v;
-        if (EPI == E_GRADLOG) o = v * exp_sfu(__ldg(sp + rr * step) - rs);
+        if (EPI != E_LOG) o = v;
         if (EPI == E_LOG) {
           const float sh = rs + cshift;
           bad |= !(v >= kTiny) || !(v <= 3.0e38f) || (sh < kFloor);
@@ -1344,8 +1356,9 @@ int band_tc_forward(int mode, const float* a, const float* b, float* out, const 
 }
 
 // GENBMM_B200_BAND_SCALE=fused applies the log gradients' factor in band_sp_kernel's epilogue instead of a pass of
-// its own.  Measured at 32 x 8192 x 129 diagonals: backward 2.10 ms against 1.20 ms — a global load in the
-// epilogue still waits behind the SM's TMA traffic, with a quarter of the bytes as much as before.
+// its own.  Measured at 32 x 8192 x 129 diagonals: backward 1.30 ms against 1.20 ms with the pass (2.10 ms while
+// the epilogue's loads went out four at a time): the loads still wait behind the SM's TMA traffic, and the tile's
+// accumulators are held for as long.
 static bool band_fused_scale() {
   const char* e = getenv("GENBMM_B200_BAND_SCALE");
   return e && e[0] == 'f';
