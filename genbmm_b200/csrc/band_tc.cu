@@ -1008,14 +1008,18 @@ __global__ void __launch_bounds__(SP_NT, 1) band_sp_kernel(const __grid_constant
         const uint32_t col = (uint32_t)(2 * buf * TN + cbase + c * 32);
         tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + col, v);
         tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + col + TN, w);
+        if (c == TEC / 32 - 1) {
+          // the last of this warp's columns is in registers: the MMA warp may have the buffers back while
+          // these cells are still on their way to band storage
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.chunk_empty[buf])) : "memory");
+        }
 #pragma unroll
         for (int q = 0; q < 32; ++q) v[q] += w[q];
         store_band32<EPI>(v, blk, g, bt, row0, c0 + cbase + c * 32, lane, rshift, bad);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0)
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.chunk_empty[buf])) : "memory");
       ++gc;
       if (EPI == E_LOG) {
         if (__any_sync(0xffffffffu, bad) && lane == 0 && row0 < g.n)
