@@ -1,6 +1,9 @@
 """Builds the reference's own CUDA extension for sm_100a into baseline/_ref/ (git-ignored).
 
-    python baseline/build_ref.py [path to the genbmm checkout, default /root/reference]
+    python baseline/build_ref.py [path to the genbmm checkout]
+
+Without an argument the checkout is taken from $GENBMM_REFERENCE, else from a directory named `reference` beside
+this repository.
 
 This is the second baseline of bench.py (`--impl reference-cuda`): harvardnlp/genbmm's kernels, unchanged,
 recompiled for the B200, so that a speed-up can be quoted against the code this package replaces on the
@@ -25,7 +28,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 
 
-def build(src="/root/reference"):
+def default_checkout():
+    return os.environ.get("GENBMM_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(src=None):
+    src = src or default_checkout()
     if not os.path.isdir(src):
         raise RuntimeError("reference checkout not found at %s" % src)
     work = tempfile.mkdtemp(prefix="genbmm_ref_")
