@@ -8,6 +8,7 @@ in it) whose entry points are declared in include/genbmm_b200.h.  The CUDA runti
 statically so the library does not depend on which libcudart the host process loaded.
 """
 import concurrent.futures
+import contextlib
 import glob
 import os
 import shutil
@@ -59,10 +60,30 @@ def _compile(src):
     return obj, r.stderr
 
 
+@contextlib.contextmanager
+def _build_lock():
+    """One builder at a time across processes (several ranks importing a stale tree at once): the others wait and
+    then find the library up to date."""
+    import fcntl
+    with open(os.path.join(HERE, ".build.lock"), "w") as fh:
+        fcntl.flock(fh, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(fh, fcntl.LOCK_UN)
+
+
 def build(force=False, verbose=False):
     """Compile every .cu under csrc/ for sm_100a and link libgenbmm_b200.so.  Returns its path."""
     if not force and not stale():
         return LIB
+    with _build_lock():
+        if not force and not stale():
+            return LIB
+        return _build_locked(verbose)
+
+
+def _build_locked(verbose):
     os.makedirs(OBJ, exist_ok=True)
     with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:
         results = list(ex.map(_compile, sources()))
@@ -70,12 +91,14 @@ def build(force=False, verbose=False):
     if verbose:
         for _, log in results:
             sys.stderr.write(log)
+    tmp = "%s.tmp.%d" % (LIB, os.getpid())   # linked beside the library and renamed over it: never half written
     cmd = [_nvcc(), "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a",
-           "-Xcompiler", "-fPIC", "-Xlinker", "--wrap=__cudaPushCallConfiguration", "-o", LIB, *objs]
+           "-Xcompiler", "-fPIC", "-Xlinker", "--wrap=__cudaPushCallConfiguration", "-o", tmp, *objs]
     # --wrap: every kernel launch of the library goes through the counter in csrc/capi.cu (gbmm_launch_count)
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (" ".join(cmd), r.stdout + r.stderr))
+    os.replace(tmp, LIB)
     return LIB
 
 
@@ -97,6 +120,13 @@ def build_shim(force=False):
     is compiled at import time.  Returns its path."""
     if not force and not shim_stale():
         return SHIM
+    with _build_lock():
+        if not force and not shim_stale():
+            return SHIM
+        return _build_shim_locked()
+
+
+def _build_shim_locked():
     import sysconfig
 
     import torch
@@ -110,14 +140,16 @@ def build_shim(force=False):
     cuda_home = os.path.dirname(os.path.dirname(_nvcc()))
     inc = ext.include_paths() + [sysconfig.get_paths()["include"], INCLUDE, os.path.join(cuda_home, "include")]
     libdirs = [os.path.join(os.path.dirname(torch.__file__), "lib"), os.path.join(cuda_home, "lib64")]
+    tmp = "%s.tmp.%d" % (SHIM, os.getpid())
     cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-w",
            "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI), "-DTORCH_EXTENSION_NAME=_shim",
-           "-DTORCH_API_INCLUDE_EXTENSION_H", *["-I" + i for i in inc], SHIM_SRC, "-o", SHIM,
+           "-DTORCH_API_INCLUDE_EXTENSION_H", *["-I" + i for i in inc], SHIM_SRC, "-o", tmp,
            *["-L" + d for d in libdirs], "-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10_cuda",
            "-ltorch_cuda", "-lcudart", "-L" + HERE, "-l:libgenbmm_b200.so", "-Wl,-rpath,$ORIGIN"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("torch shim failed to build:\n%s\n%s" % (" ".join(cmd), (r.stdout + r.stderr)[-4000:]))
+    os.replace(tmp, SHIM)
     return SHIM
 
 

@@ -173,7 +173,9 @@ int gbmm_band_tc_backward_f32(int mode, const float* a, int a_lu, int a_ld, cons
  * bit-identical to it) for bands at least 32 wide and n >= 128 (gbmm_band_max_eligible).  It works from
  * skewed copies of the operands kept in the workspace, whose padding holds -inf: fill the workspace ONCE
  * with gbmm_band_max_workspace_init and afterwards pass it only to this function with the same B, n and
- * band widths.  Calls sharing a workspace must not overlap on the GPU.
+ * band widths.  Calls sharing a workspace must not overlap on the GPU.  The workspace's last 256 bytes hold the
+ * call's error word: a kernel whose bounded wait for its own copies ran out sets it, and the result is then
+ * overwritten with NaN before the call's work on the stream ends.
  */
 int gbmm_band_max_eligible(int64_t n, int a_lu, int a_ld, int b_lu, int b_ld);
 int64_t gbmm_band_max_workspace_bytes(int64_t B, int64_t n, int a_lu, int a_ld, int b_lu, int b_ld);
