@@ -13,6 +13,8 @@
 // accumulated in shared-memory rows/columns in ascending n (grad_a) and ascending m
 // (grad_b), the order of the reference's loops.  An index outside [0,K) routes nowhere.
 #include "dense.cuh"
+#include <cstdlib>
+
 #include "tile.cuh"
 
 namespace gbmm {
@@ -437,6 +439,64 @@ __global__ void __launch_bounds__(RB_WARPS * 32) route_grad_b_kernel(const float
   }
 }
 
+// grad_b for short reductions (K floats of shared memory per thread): one THREAD per column (batch, n).  It walks
+// m upwards — the lanes of a warp are consecutive n, so every step is one coalesced read of idx and of g — and adds
+// each cotangent to the bucket its index names in a private K-bucket histogram (odd pitch): ascending-m sums
+// with no ranking of lanes that share a bucket, which is what the kernel above spends its time on.  Eight steps
+// are fetched together and the next eight requested before these are added up.
+constexpr int RC_T = 128;   // threads per CTA at most; fewer when K is longer (K floats of shared memory each)
+template <bool MUL>
+__global__ void __launch_bounds__(RC_T) route_grad_b_cols_kernel(const float* __restrict__ a,
+                                                                 const int* __restrict__ idx,
+                                                                 const float* __restrict__ g,
+                                                                 float* __restrict__ grad_b, int M, int K, int N,
+                                                                 int64_t cols) {
+  extern __shared__ float hist_all[];
+  const int pitch = K | 1;
+  float* hist = hist_all + threadIdx.x * pitch;
+  for (int k = 0; k < K; ++k) hist[k] = 0.f;
+  const int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = col < cols;
+  const int64_t bt = live ? col / N : 0;
+  const int n = live ? (int)(col % N) : 0;
+  const int* ip = idx + bt * M * N + n;
+  const float* gp = g + bt * M * N + n;
+  const float* ab = a + bt * M * K;
+  constexpr int U = 8;
+  int kq[2][U];
+  float gq[2][U];
+  auto fetch = [&](int m0, int (&kd)[U], float (&gd)[U]) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int m = m0 + u;
+      const bool ok = live && m < M;
+      kd[u] = ok ? __ldg(ip + (int64_t)m * N) : -1;
+      gd[u] = ok ? __ldg(gp + (int64_t)m * N) : 0.f;
+    }
+    if (MUL) {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if ((unsigned)kd[u] < (unsigned)K) gd[u] = __fmul_rn(__ldg(ab + (int64_t)(m0 + u) * K + kd[u]), gd[u]);
+    }
+  };
+  auto add_up = [&](const int (&kd)[U], const float (&gd)[U]) {
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if ((unsigned)kd[u] < (unsigned)K) hist[kd[u]] = __fadd_rn(hist[kd[u]], gd[u]);
+  };
+  fetch(0, kq[0], gq[0]);
+  for (int m0 = 0; m0 < M; m0 += 2 * U) {
+    fetch(m0 + U, kq[1], gq[1]);
+    add_up(kq[0], gq[0]);
+    fetch(m0 + 2 * U, kq[0], gq[0]);
+    add_up(kq[1], gq[1]);
+  }
+  if (live) {
+    float* ob = grad_b + bt * K * N + n;
+    for (int k = 0; k < K; ++k) ob[(int64_t)k * N] = hist[k];
+  }
+}
+
 }  // namespace
 }  // namespace gbmm
 
@@ -535,6 +595,23 @@ extern "C" int gbmm_dense_backward_f32(int mode, const float* a, const float* b,
     const int64_t tiles_n = ceil_div(N, 32), blocks = B * tiles_n;
     if (blocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
     const size_t smem = sizeof(float) * 32 * (KB + 1);
+    // short reductions: one thread per column with a private histogram (GENBMM_B200_ROUTE_B=w keeps the kernel below)
+    int ct = RC_T;   // 128, 64 or 32 threads per CTA, so that a CTA's histograms stay below 100 KB
+    while (ct > 32 && sizeof(float) * ct * (size_t)(K | 1) > (size_t)100 * 1024) ct /= 2;
+    const size_t smem_cols = sizeof(float) * ct * (size_t)(K | 1);
+    const char* eb = getenv("GENBMM_B200_ROUTE_B");
+    if (smem_cols <= (size_t)100 * 1024 && !(eb && eb[0] == 'w')) {
+      const int64_t cols = B * N, cblocks = ceil_div(cols, ct);
+      if (cblocks >= (1LL << 31)) return GBMM_ERR_UNSUPPORTED;
+      if (mul) {
+        cudaFuncSetAttribute(route_grad_b_cols_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cols);
+        route_grad_b_cols_kernel<true><<<(unsigned)cblocks, ct, smem_cols, st>>>(a, idx, grad_out, grad_b, m, k, n, cols);
+      } else {
+        cudaFuncSetAttribute(route_grad_b_cols_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cols);
+        route_grad_b_cols_kernel<false><<<(unsigned)cblocks, ct, smem_cols, st>>>(a, idx, grad_out, grad_b, m, k, n, cols);
+      }
+      return launch_status();
+    }
     if (mul) {
       cudaFuncSetAttribute(route_grad_b_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       route_grad_b_kernel<true><<<(unsigned)blocks, RB_WARPS * 32, smem, st>>>(a, idx, grad_out, grad_b, m, k, n,

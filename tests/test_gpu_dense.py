@@ -67,12 +67,14 @@ def test_logbmm_matches_reference_fixture(gb, golden, ci):
 MAX_SHAPES = SHAPES + [(2, 130, 260, 70), (1, 300, 516, 200), (3, 64, 132, 64), (1, 129, 1028, 65)]
 
 
-@pytest.mark.parametrize("staging", ["auto", "tma"])
+@pytest.mark.parametrize("staging", ["auto", "tma", "warp-routing"])
 @pytest.mark.parametrize("shape", MAX_SHAPES)
 @pytest.mark.parametrize("name,mode", [("maxbmm", 1), ("prodmaxbmm", 3)])
 def test_max_semirings_bit_exact(gb, shape, name, mode, staging, monkeypatch):
     if staging == "tma":
         monkeypatch.setenv("GENBMM_B200_MAX_TMA", "1")
+    if staging == "warp-routing":   # grad_b of short reductions by the warp-per-column kernel too
+        monkeypatch.setenv("GENBMM_B200_ROUTE_B", "w")
     B, M, K, N = shape
     gen = torch.Generator().manual_seed(7 + sum(shape))
     a, b, g = tied((B, M, K), gen), tied((B, K, N), gen), torch.rand(B, M, N, generator=gen)
