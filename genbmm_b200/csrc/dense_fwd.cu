@@ -1018,6 +1018,10 @@ extern "C" int gbmm_dense_forward_f32(int mode, const float* a, const float* b, 
       const bool pack = ceil_div(K, BK) <= 255;
       int* ix = static_cast<int*>(aux);
       const bool mul = mode == GBMM_MODE_PRODMAX;
+      if (dense_max_w_eligible(a, K)) {   // short reductions: warps that do not wait for one another
+        if (int rc = launch_dense_max_w(mul, a, b, out, ix, B, M, K, N, st)) return rc;
+        break;
+      }
       if (K > 0 && ceil_div(K, BK) <= kResidentTiles) {
         // short reductions: every tile stays in shared memory and the index search reads it there
         const size_t dyn = (size_t)ceil_div(K, BK) * (kTileXr + kTileYr) * sizeof(float);
