@@ -986,6 +986,8 @@ extern "C" int64_t gbmm_dense_forward_workspace_bytes(int mode, int64_t B, int64
   if (B < 0 || M < 0 || K < 0 || N < 0) return -1;
   if (mode != GBMM_MODE_MAX && mode != GBMM_MODE_PRODMAX) return 0;
   if ((K + BK - 1) / BK <= kResidentTiles) return 0;   // short reductions search shared memory, no copy of b
+  if (dense_max_w_eligible(nullptr, K)) return 0;        // as does dense_max_w_kernel (a misaligned `a` falls back to
+                                                         // the plain index search of the kernel below)
   return (int64_t)sizeof(float) * B * N * ((K + 15) / 16 * 16);
 }
 
