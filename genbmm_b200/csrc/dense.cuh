@@ -31,7 +31,7 @@ int launch_small_log_bwd(const float* a, const float* b, const float* c, const f
 
 int rowmax_only(const float* a, float* rowmax, int64_t B, int64_t M, int64_t K, cudaStream_t st);
 
-// Max-plus / prod-max forward for short reductions (dense_max_w.cu): K a multiple of 4, at most 416, a 16-byte
+// Max-plus / prod-max forward for short reductions (dense_max_w.cu): K a multiple of 4, at most 288, a 16-byte
 // aligned; values and int32 indices as the reference's kernels give them.
 bool dense_max_w_eligible(const float* a, int64_t K);
 int launch_dense_max_w(bool mul, const float* a, const float* b, float* out, int* idx, int64_t B, int64_t M, int64_t K,

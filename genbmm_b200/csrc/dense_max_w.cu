@@ -1,4 +1,4 @@
-// Max-plus / prod-max forward for reductions of up to 416 steps (K a multiple of 4): the whole reduction of a
+// Max-plus / prod-max forward for reductions of up to 288 steps (K a multiple of 4): the whole reduction of a
 // 64 x 32 block of the result stays in shared memory, and the warps of a CTA do not wait for one another.
 //
 // This is the structure of the banded max kernel (band_max.cu, band_max_w_kernel) on dense operands.  Every thread
@@ -15,7 +15,9 @@
 // Steps beyond K and rows / columns beyond the matrices are copied from four NaNs in device memory: a NaN term is
 // ignored by the maximum under both semirings.
 // 80 registers and 6 KB of tiles per 16 steps: three CTAs (24 warps) per SM up to 176 steps.  Against the kernel
-// it replaces for K <= 128 (128 x 64 blocks in lockstep, tiles resident as well): 99 -> 79 us at 256 x 128^3.
+// it replaces for K <= 128 (128 x 64 blocks in lockstep, tiles resident as well): 99 -> 79 us at 256 x 128^3;
+// at 32 x 1024 x K x 1024: 0.57 against 0.65 ms (K = 128), 1.04 against 1.20 ms (K = 256), and 1.99 against 1.57
+// ms at K = 416, where only one CTA fits an SM — hence the limit of 288 steps.
 // GENBMM_B200_MAX_SHORT=block keeps the lockstep kernels.
 #include <cstdlib>
 
@@ -27,7 +29,7 @@ namespace {
 
 constexpr int WB = 64, WC = 32, WNT = 256, BK = 16;
 constexpr int WTX = 4 * WB * 4 + 4, WTY = 4 * WC * 4 + 4;   // floats per tile of a / of b; + 4: see the search
-constexpr int kMaxTiles = 26;
+constexpr int kMaxTiles = 18;   // two CTAs per SM; with one (up to 26 tiles fit) the lockstep kernel is faster
 
 // four NaNs: the source of every copy that has nothing to copy
 __device__ __align__(16) unsigned g_nan4[4] = {0x7fc00000u, 0x7fc00000u, 0x7fc00000u, 0x7fc00000u};

@@ -65,7 +65,7 @@ def test_logbmm_matches_reference_fixture(gb, golden, ci):
 # reductions longer than 128 steps: the register-staged kernel, or with GENBMM_B200_MAX_TMA=1 and K a multiple of 4
 # the TMA-staged one (ragged tiles, a partial last stage, a stage count that is not a multiple of the ring)
 MAX_SHAPES = SHAPES + [(2, 130, 260, 70), (1, 300, 516, 200), (3, 64, 132, 64), (1, 129, 1028, 65),
-                       (2, 70, 416, 33), (3, 65, 20, 31), (1, 200, 128, 100)]
+                       (2, 70, 416, 33), (2, 70, 288, 33), (3, 65, 20, 31), (1, 200, 128, 100)]
 
 
 @pytest.mark.parametrize("staging", ["auto", "tma", "warp-routing", "lockstep-short"])
@@ -76,7 +76,7 @@ def test_max_semirings_bit_exact(gb, shape, name, mode, staging, monkeypatch):
         monkeypatch.setenv("GENBMM_B200_MAX_TMA", "1")
     if staging == "warp-routing":   # grad_b of short reductions by the warp-per-column kernel too
         monkeypatch.setenv("GENBMM_B200_ROUTE_B", "w")
-    if staging == "lockstep-short":  # reductions of up to 416 steps on the 128 x 64 lockstep kernels as well
+    if staging == "lockstep-short":  # reductions of up to 288 steps on the 128 x 64 lockstep kernels as well
         monkeypatch.setenv("GENBMM_B200_MAX_SHORT", "block")
     B, M, K, N = shape
     gen = torch.Generator().manual_seed(7 + sum(shape))
