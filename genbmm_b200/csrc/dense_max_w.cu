@@ -226,6 +226,7 @@ __global__ void __launch_bounds__(WNT, 3) dense_max_w_kernel(const float* __rest
   }
 }
 
+
 }  // namespace
 
 // declared in dense.cuh

@@ -65,7 +65,7 @@ def test_logbmm_matches_reference_fixture(gb, golden, ci):
 # reductions longer than 128 steps: the register-staged kernel, or with GENBMM_B200_MAX_TMA=1 and K a multiple of 4
 # the TMA-staged one (ragged tiles, a partial last stage, a stage count that is not a multiple of the ring)
 MAX_SHAPES = SHAPES + [(2, 130, 260, 70), (1, 300, 516, 200), (3, 64, 132, 64), (1, 129, 1028, 65),
-                       (2, 70, 416, 33), (2, 70, 288, 33), (3, 65, 20, 31), (1, 200, 128, 100)]
+                       (2, 70, 416, 33), (2, 70, 288, 33), (3, 65, 20, 31), (1, 200, 128, 100), (1, 70, 2052, 90)]
 
 
 @pytest.mark.parametrize("staging", ["auto", "tma", "warp-routing", "lockstep-short"])
