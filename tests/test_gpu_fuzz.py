@@ -98,3 +98,30 @@ def test_logbmm_random_shapes(B, M, K, N, scale, seed):
     assert_close(c, want, what="fwd")
     assert_close(ga, dA, rtol_w, what="grad_a", term_sum=tA * (rtol_w / 1e-6))
     assert_close(gb_, dB, rtol_w, what="grad_b", term_sum=tB * (rtol_w / 1e-6))
+
+
+@settings(**SETTINGS)
+@given(B=st.integers(1, 2), n=st.integers(1, 420), alu=st.integers(0, 70), ald=st.integers(0, 70),
+       blu=st.integers(0, 70), bld=st.integers(0, 70), mode=st.sampled_from([0, 3]), seed=st.integers(0, 10 ** 6))
+def test_banded_sum_and_log_random_bands(B, n, alu, ald, blu, bld, mode, seed):
+    """multiply and multiply_log over every path the band widths and n select (direct kernels, FP32 block
+    kernels, 3xTF32 on the tensor cores from skewed copies) against the float64 oracle."""
+    import genbmm_b200 as gb
+    gen = torch.Generator().manual_seed(seed)
+    a = torch.randn(B, n, alu + ald + 1, generator=gen)
+    b = torch.randn(B, n, blu + bld + 1, generator=gen)
+    g = torch.randn(B, n, alu + ald + blu + bld + 1, generator=gen) if mode == 3 else \
+        torch.rand(B, n, alu + ald + blu + bld + 1, generator=gen)
+    ad, bd = a.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+    method = "multiply" if mode == 3 else "multiply_log"
+    r = getattr(gb.BandedMatrix(ad, alu, ald), method)(gb.BandedMatrix(bd, blu, bld))
+    ga, gb_ = torch.autograd.grad(r.data, (ad, bd), g.cuda())
+    out, _, _, dA, dB = oracle.band_fwd_bwd(mode, a, alu, ald, b, blu, bld, g, dtype=np.float64)
+    bound = (None, None, None)
+    if mode == 3:  # signed terms: the same sums over absolute values bound the rounding error
+        t_out, _, _, t_dA, t_dB = oracle.band_fwd_bwd(mode, a.abs(), alu, ald, b.abs(), blu, bld, g.abs(),
+                                                      dtype=np.float64)
+        bound = (t_out, t_dA, t_dB)
+    assert_close(r.data.detach(), out, what=method, term_sum=bound[0])
+    assert_close(ga, dA, what=method + " grad_a", term_sum=bound[1])
+    assert_close(gb_, dB, what=method + " grad_b", term_sum=bound[2])
