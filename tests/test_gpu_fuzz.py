@@ -29,8 +29,9 @@ def special(x, gen, how):
 
 
 @settings(**SETTINGS)
-@given(B=st.integers(1, 3), M=st.integers(1, 150), K=st.sampled_from([1, 3, 4, 8, 20, 60, 128, 130, 132, 288, 292, 300, 516, 1028]),
-       N=st.integers(1, 140), mode=st.sampled_from([1, 3]), how=st.integers(0, 3), seed=st.integers(0, 10 ** 6))
+@given(B=st.integers(1, 3), M=st.sampled_from([1, 7, 33, 64, 65, 100, 129, 150]),
+       K=st.sampled_from([1, 3, 4, 8, 20, 60, 128, 130, 132, 288, 292, 300, 516, 1028]),
+       N=st.sampled_from([1, 5, 31, 32, 33, 64, 97, 140]), mode=st.sampled_from([1, 3]), how=st.integers(0, 3), seed=st.integers(0, 10 ** 6))
 def test_dense_max_semirings_random_shapes(B, M, K, N, mode, how, seed):
     import genbmm_b200 as gb
     from genbmm_b200 import _native
@@ -53,8 +54,8 @@ def test_dense_max_semirings_random_shapes(B, M, K, N, mode, how, seed):
 
 
 @settings(**SETTINGS)
-@given(B=st.integers(1, 2), n=st.integers(128, 420), alu=st.integers(16, 90), ald=st.integers(15, 90),
-       blu=st.integers(16, 90), bld=st.integers(15, 90), how=st.integers(0, 3), seed=st.integers(0, 10 ** 6))
+@given(B=st.integers(1, 2), n=st.sampled_from([128, 129, 191, 256, 333, 420]), alu=st.sampled_from([16, 31, 64, 90]),
+       ald=st.sampled_from([15, 33, 64, 90]), blu=st.sampled_from([16, 40, 64, 90]), bld=st.sampled_from([15, 31, 64, 90]), how=st.integers(0, 3), seed=st.integers(0, 10 ** 6))
 def test_banded_max_random_bands(B, n, alu, ald, blu, bld, how, seed):
     import genbmm_b200 as gb
     from genbmm_b200 import _native
@@ -74,8 +75,8 @@ def test_banded_max_random_bands(B, n, alu, ald, blu, bld, how, seed):
 
 
 @settings(**SETTINGS)
-@given(B=st.integers(1, 3), M=st.integers(1, 200), K=st.sampled_from([1, 5, 16, 33, 64, 100, 128, 257, 512]),
-       N=st.integers(1, 200), scale=st.sampled_from([0.1, 1.0, 5.0]), seed=st.integers(0, 10 ** 6))
+@given(B=st.integers(1, 3), M=st.sampled_from([1, 10, 64, 65, 128, 130, 200]),
+       K=st.sampled_from([1, 5, 16, 33, 64, 100, 128, 257, 512]), N=st.sampled_from([1, 13, 64, 100, 129, 200]), scale=st.sampled_from([0.1, 1.0, 5.0]), seed=st.integers(0, 10 ** 6))
 def test_logbmm_random_shapes(B, M, K, N, scale, seed):
     """logbmm through the rule that picks its path (32x32-tile exact kernels, 128x64-tile exact kernels, 3xTF32
     tensor-core products with the underflow guard) against the float64 oracle at the stated 1e-5."""
@@ -101,8 +102,8 @@ def test_logbmm_random_shapes(B, M, K, N, scale, seed):
 
 
 @settings(**SETTINGS)
-@given(B=st.integers(1, 2), n=st.integers(1, 420), alu=st.integers(0, 70), ald=st.integers(0, 70),
-       blu=st.integers(0, 70), bld=st.integers(0, 70), mode=st.sampled_from([0, 3]), seed=st.integers(0, 10 ** 6))
+@given(B=st.integers(1, 2), n=st.sampled_from([1, 9, 70, 128, 131, 300, 420]), alu=st.sampled_from([0, 3, 20, 40, 70]),
+       ald=st.sampled_from([0, 5, 31, 64]), blu=st.sampled_from([0, 2, 33, 64]), bld=st.sampled_from([0, 7, 31, 70]), mode=st.sampled_from([0, 3]), seed=st.integers(0, 10 ** 6))
 def test_banded_sum_and_log_random_bands(B, n, alu, ald, blu, bld, mode, seed):
     """multiply and multiply_log over every path the band widths and n select (direct kernels, FP32 block
     kernels, 3xTF32 on the tensor cores from skewed copies) against the float64 oracle."""
