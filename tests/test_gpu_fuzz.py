@@ -9,7 +9,7 @@ import torch
 from hypothesis import HealthCheck, given, settings, strategies as st
 
 import oracle
-from util import assert_close, assert_equal_bits
+from util import assert_close, assert_equal_bits, assert_valid_sample
 
 pytestmark = pytest.mark.gpu
 
@@ -126,3 +126,31 @@ def test_banded_sum_and_log_random_bands(B, n, alu, ald, blu, bld, mode, seed):
     assert_close(r.data.detach(), out, what=method, term_sum=bound[0])
     assert_close(ga, dA, what=method + " grad_a", term_sum=bound[1])
     assert_close(gb_, dB, what=method + " grad_b", term_sum=bound[2])
+
+
+@settings(**dict(SETTINGS, max_examples=60))
+@given(B=st.integers(1, 2), M=st.sampled_from([1, 9, 64, 70, 130]), K=st.sampled_from([1, 4, 17, 64, 129, 256]),
+       N=st.sampled_from([1, 8, 65, 100, 128]), seed=st.integers(0, 10 ** 6))
+def test_samplebmm_random_shapes(B, M, K, N, seed):
+    """samplebmm with explicit uniforms: the index is the oracle's wherever the uniform is more than 1e-5 away
+    from a step of the float64 CDF, a bracketing index elsewhere; gradients are the one-hot routing of the
+    cotangent through the indices drawn, bit for bit."""
+    import genbmm_b200 as gb
+    from genbmm_b200 import _native, genmul
+    gen = torch.Generator().manual_seed(seed)
+    a, b = 2 * torch.randn(B, M, K, generator=gen), 2 * torch.randn(B, K, N, generator=gen)
+    u, g = torch.rand(B, M, N, generator=gen), torch.rand(B, M, N, generator=gen)
+    ad, bd = a.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+    c = gb.samplebmm(ad, bd, u.cuda())
+    ga, gb_ = torch.autograd.grad(c, (ad, bd), g.cuda())
+    assert_close(c, oracle.dense_fwd(0, a, b, dtype=np.float64)[0], what="sample value")
+    fast = genmul._log_path(M, K, N) == "tensor"
+    _, idx_gpu = _native.forward(a.cuda(), b.cuda(), 2, u.cuda(), fast_log=fast)
+    idx_gpu = idx_gpu.cpu().numpy()
+    _, idx = oracle.dense_fwd(2, a, b, u)
+    firm = oracle.sample_margin(a, b, u) > 1e-5
+    assert np.array_equal(idx_gpu[firm], idx[firm])
+    assert_valid_sample(a, b, u, idx_gpu)
+    dA, dB = oracle.dense_bwd(2, a, b, g, None, idx_gpu)
+    assert_equal_bits(ga, dA, "sample grad_a")
+    assert_equal_bits(gb_, dB, "sample grad_b")
